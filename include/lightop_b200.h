@@ -1,0 +1,202 @@
+/*
+ * lightop_b200 -- C ABI of the B200 (sm_100a) kernels behind the fused
+ * block-INT8 (W8A8, 128x128 weight blocks, 128-wide activation groups) MoE path.
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless the comment says "host";
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream);
+ *   - every function only enqueues work on `stream`: no host synchronisation and
+ *     no allocation (scratch memory is passed in by the caller);
+ *   - the return value is a status code, 0 on success; lo_last_error() returns
+ *     a thread-local, human readable description of the last failure;
+ *   - "reference" citations name files of the HYGON-AI/lightop project by their
+ *     path inside that project.
+ */
+#ifndef LIGHTOP_B200_H_
+#define LIGHTOP_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LO_OK 0
+#define LO_ERR_INVALID_ARGUMENT 1
+#define LO_ERR_CUDA 2
+#define LO_ERR_UNSUPPORTED 3
+#define LO_ERR_DEVICE_TIMEOUT 4
+
+/* element type codes used by the `*_dtype` arguments */
+#define LO_F32 0
+#define LO_F16 1
+#define LO_BF16 2
+#define LO_I32 3
+#define LO_I64 4
+#define LO_U32 5
+
+/* how the routed weight is applied in a grouped-GEMM epilogue */
+#define LO_WEIGHT_NONE 0
+#define LO_WEIGHT_FP32 1      /* acc_fp32 * w, then one rounding (reference Triton kernel, int8.py:521-530) */
+#define LO_WEIGHT_BF16_PRODUCT 2 /* round(acc) * round(w), rounded again (reference torch model, benchmark_moe_int8.py:199-201) */
+
+int lo_version(void);
+const char *lo_last_error(void);
+
+/* Number of SMs of the current device (grid sizing is done inside the library;
+ * exported for the benchmark's reporting). */
+int lo_sm_count(void);
+
+/*
+ * Softmax over experts + top-k selection (+ optional renormalisation).
+ * Replaces: topk_softmax, csrc/kernels/softmax/topk_softmax_kernels.cu:1716
+ *           (pybind export csrc/pybind/export.cpp:546,1437).
+ * gating [M,E] (LO_F32 / LO_F16 / LO_BF16, row-major), topk_weights [M,k] f32,
+ * topk_ids [M,k] (LO_I32 / LO_U32 / LO_I64), token_expert_indices [M,k] i32
+ * (= slot*M + token; may be NULL).  Ids come out in descending score order,
+ * ties go to the lower expert id.  E <= 1024, k <= 32.
+ */
+int lo_topk_softmax(const void *gating, int gating_dtype, int64_t M, int E, int k, int renormalize,
+                    float *topk_weights, void *topk_ids, int ids_dtype,
+                    int32_t *token_expert_indices, void *stream);
+
+/*
+ * Expert-major stable ordering of the flat (token, slot) indices, each expert's
+ * segment padded to block_size with the sentinel `numel`.
+ * Replaces: moe_align_block_size, csrc/kernels/moe_align_sum_kernels.cu:1210
+ *           (wrapper python/lightop/_lmslim_native/vllm_compat/moe_align_block_size.py:17).
+ * topk_ids: `numel` ids (LO_I32 / LO_I64).  expert_map (i32 [num_experts]) may be NULL.
+ *   map_mode 0: ignore expert_map;
+ *   map_mode 1: ids are mapped through expert_map before counting and ids mapping
+ *               to -1 are dropped (the wrapper's ignore_invalid_experts=True);
+ *   map_mode 2: counting uses the unmapped ids and expert_ids[] is written as
+ *               expert_map[expert] (the wrapper's default with an expert_map).
+ * sorted_ids capacity >= numel + num_experts*(block_size-1) (or numel*block_size when
+ * numel < num_experts); every slot up to the capacity is written (sentinel fill).
+ * expert_ids: one entry per block up to its capacity; blocks past the padded total get -1.
+ * num_tokens_post_pad: i32[1], stays on the device.
+ * Within an expert the flat indices are ascending (deterministic), which is the order of
+ * the reference's Python model (test/test_moe_align_block_size.py:79-87).
+ */
+int lo_moe_align_block_size(const void *topk_ids, int ids_dtype, int64_t numel, int num_experts,
+                            int block_size, const int32_t *expert_map, int map_mode,
+                            int32_t *sorted_ids, int64_t sorted_capacity,
+                            int32_t *expert_ids, int64_t expert_ids_capacity,
+                            int32_t *num_tokens_post_pad, void *stream);
+
+/*
+ * Per-token-group symmetric INT8 quantisation: per `group_size` consecutive
+ * elements amax -> scale = amax/127 -> q = trunc(clamp(x / scale, -128, 127)).
+ * Replaces: per_token_group_quant_int8,
+ *           python/lightop/_lmslim_native/layers/gemm/int8_utils.py:125 (Triton kernel :74-122).
+ * x: num_groups*group_size contiguous elements (LO_BF16 / LO_F16 / LO_F32);
+ * q: int8 same count; s: f32 [num_groups].  group_size in {64,128,256}.
+ * eps is rounded to the input type before the clamp, as the reference's torch model does
+ * (test/moe_w8a8/benchmark_moe_int8.py:76).
+ */
+int lo_group_quant_int8(const void *x, int x_dtype, int64_t num_groups, int group_size, float eps,
+                        int8_t *q, float *s, void *stream);
+
+/*
+ * out[t,:] = factor * sum_j in[t,j,:] (+ bias[t,:]), fp32 accumulation, one rounding.
+ * Replaces: moe_sum, csrc/kernels/moe_align_sum_kernels.cu:1315 (kernels :604-760),
+ *           python/lightop/moe_align_sum.py:12-29.
+ * in [M,topk,H], out [M,H], bias [M,H] or NULL, all of `dtype` (LO_BF16 / LO_F16 / LO_F32).
+ * expert_mask: optional uint8/bool [M,topk]; slot j is skipped where it is 0.
+ * num_local_tokens: optional i32[1]; tokens >= that count are left untouched.
+ * H must be a multiple of 8.
+ */
+int lo_moe_sum(const void *in, void *out, const void *bias, int dtype, int64_t M, int topk, int64_t H,
+               float factor, const uint8_t *expert_mask, const int32_t *num_local_tokens, void *stream);
+
+/*
+ * Grouped block-INT8 GEMM over expert-sorted row blocks (unfused form):
+ *   C[id, n] = sum_kb (A_q[id / top_k, kb] . B_q[e, n, kb]) * a_s[id / top_k, kb] * b_s[e, n/128, kb]
+ * for every id in sorted_ids below `numel_valid`, e = expert_ids[block of id].
+ * Replaces: fused_moe_kernel / invoke_fused_moe_kernel_int8,
+ *           python/lightop/_lmslim_native/layers/fused_moe/int8.py:320-626, and the
+ *           block-scale form of moe_gemm_w8a8, python/lightop/gemmopt.py:437-457.
+ * A [rows_a,K] int8, a_scale [rows_a,K/128] f32, B [E,N,K] int8 contiguous,
+ * b_scale [E,N/128,K/128] f32, C [numel_valid, N] bf16, topk_weights flat f32 [numel_valid] or NULL.
+ * N and K multiples of 128; block_size <= 128 or a multiple of 128.
+ * Blocks whose expert id is negative produce zero rows (int8.py:441-449).
+ * workspace: lo_grouped_gemm_workspace_bytes(max_blocks, block_size) bytes of scratch.
+ */
+size_t lo_grouped_gemm_workspace_bytes(int64_t sorted_capacity, int block_size);
+int lo_moe_grouped_gemm_i8_block(const int8_t *A, const float *a_scale, int64_t rows_a,
+                                 const int8_t *B, const float *b_scale, int E, int64_t N, int64_t K,
+                                 void *C, const float *topk_weights, int weight_mode,
+                                 const int32_t *sorted_ids, int64_t sorted_capacity,
+                                 const int32_t *expert_ids, const int32_t *num_tokens_post_pad,
+                                 int64_t numel_valid, int top_k, int block_size,
+                                 void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * The whole fused layer for one chunk of tokens: group-quantise x, sort by expert,
+ * gate_up grouped GEMM with SiLU*mul + re-quantisation in its epilogue, down grouped
+ * GEMM with the routed weight in its epilogue, top-k reduction.
+ * Replaces: fused_experts_impl_int8 with use_int8_w8a8=True, block_shape=[128,128],
+ *           python/lightop/_lmslim_native/layers/fused_moe/int8.py:628-908 (one chunk).
+ * x [M,H] bf16; w1 [E,2I,H] int8; w2 [E,H,I] int8; w1_scale [E,2I/128,H/128] f32;
+ * w2_scale [E,H/128,I/128] f32; topk_weights [M,topk] f32; topk_ids [M,topk] (LO_I32/LO_I64);
+ * expert_map i32 [global_num_experts] or NULL (ids mapping to -1 contribute nothing);
+ * cache3 [M,topk,H] bf16 scratch (the caller's cache13); shared_output [M,H] bf16 or NULL;
+ * out [M,H] bf16 = routed_scaling_factor * sum_j w_j * expert_j(x) (+ shared_output).
+ * apply_router_weight_on_input != 0 multiplies the gate_up result instead (requires topk == 1).
+ * workspace: lo_fused_moe_workspace_bytes(...) bytes, 256-byte aligned.
+ * status: optional i32[1] device word, set non-zero by a kernel whose bounded wait ran out.
+ */
+size_t lo_fused_moe_workspace_bytes(int64_t M, int E_local, int global_num_experts, int topk,
+                                    int64_t H, int64_t I);
+/* Byte offsets of the intermediates inside that workspace, for inspection and tests (host array out8):
+ * [0] header i32 {num_tokens_post_pad, num_chunks}, [1] x_q int8 [M,H], [2] x_s f32 [M,H/128],
+ * [3] sorted_ids i32 [cap], [4] chunk table, [5] act_q int8 [cap,I] and [6] act_s f32 [cap,I/128]
+ * (both in sorted order), [7] = cap, the number of sorted positions (not a byte offset).
+ * No counterpart in the reference, whose intermediates are torch tensors (int8.py:681-695). */
+int lo_fused_moe_workspace_layout(int64_t M, int E_local, int global_num_experts, int topk,
+                                  int64_t H, int64_t I, int64_t *out8);
+int lo_fused_moe_block_int8(const void *x, const int8_t *w1, const int8_t *w2,
+                            const float *w1_scale, const float *w2_scale,
+                            const float *topk_weights, const void *topk_ids, int ids_dtype,
+                            const int32_t *expert_map, int global_num_experts,
+                            int64_t M, int E_local, int topk, int64_t H, int64_t I,
+                            void *cache3, const void *shared_output, void *out,
+                            int apply_router_weight_on_input, float routed_scaling_factor,
+                            void *workspace, size_t workspace_bytes, int32_t *status, void *stream);
+
+/*
+ * Expert-parallel local permutation: copy every (token, slot) whose expert is local into the
+ * expert-contiguous, `alignment`-padded layout; record where it went.
+ * Replaces: ep_scatter, csrc/kernels/deepgemm_moe_permute.cu:1080 (export.cpp:611,1765).
+ * aq [T,H] int8; aq_scale [T,S] f32 (S = 1 as in the reference, or H/128 group scales);
+ * topk_ids [T,k] (LO_I32/LO_I64); expert_map i32 or NULL; expert_num_tokens i32 [local_E] (in: counts);
+ * aq_out [rows,H]; aq_scale_out [rows,S]; m_indices i32 [rows] (expert of the row, -1 padding);
+ * inv_perm i32 [T,k] (destination row, -1 if not local).  Placement is stable (ascending flat index).
+ */
+int lo_ep_scatter(const int8_t *aq, const float *aq_scale, int scale_cols,
+                  const void *topk_ids, int ids_dtype, const int32_t *expert_map,
+                  const int32_t *expert_num_tokens, int8_t *aq_out, float *aq_scale_out,
+                  int32_t *m_indices, int32_t *inv_perm, int64_t T, int k, int64_t H, int64_t rows,
+                  int local_num_experts, int alignment, void *stream);
+
+/*
+ * Per-row expert id of the aligned contiguous layout.
+ * Replaces: ep_build_m_indices, csrc/kernels/deepgemm_moe_permute.cu:833 (export.cpp:1137).
+ */
+int lo_ep_build_m_indices(const void *topk_ids, int ids_dtype, int64_t numel, int32_t *m_indices,
+                          int64_t rows, int local_num_experts, int alignment, void *stream);
+
+/*
+ * out[t,:] = sum over local slots j of w[t,j] * a[inv_perm[t,j], :], fp32 accumulation.
+ * Replaces: ep_gather, csrc/kernels/deepgemm_moe_permute.cu:1235 (kernel :947-1022).
+ * a [rows,H] bf16; out [T,H] bf16.
+ */
+int lo_ep_gather(const void *a, const void *topk_ids, int ids_dtype, const float *topk_weights,
+                 const int32_t *inv_perm, const int32_t *expert_map, void *out,
+                 int64_t T, int k, int64_t H, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LIGHTOP_B200_H_ */

@@ -1,0 +1,108 @@
+// Shared host-side helpers of the lightop_b200 C-ABI library.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cstdint>
+#include <cstdio>
+#include <cstdarg>
+#include "../../include/lightop_b200.h"
+
+namespace lo {
+
+// Thread-local message returned by lo_last_error().
+void set_error(const char *fmt, ...);
+
+inline int fail(int code, const char *fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  set_error("%s", buf);
+  return code;
+}
+
+#define LO_REQUIRE(cond, ...)                                             \
+  do {                                                                    \
+    if (!(cond)) return ::lo::fail(LO_ERR_INVALID_ARGUMENT, __VA_ARGS__); \
+  } while (0)
+
+#define LO_CUDA_OK(expr)                                                           \
+  do {                                                                             \
+    cudaError_t e__ = (expr);                                                      \
+    if (e__ != cudaSuccess)                                                        \
+      return ::lo::fail(LO_ERR_CUDA, "%s failed: %s", #expr, cudaGetErrorString(e__)); \
+  } while (0)
+
+#define LO_LAUNCH_OK(what)                                                            \
+  do {                                                                                \
+    cudaError_t e__ = cudaGetLastError();                                             \
+    if (e__ != cudaSuccess)                                                           \
+      return ::lo::fail(LO_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e__)); \
+  } while (0)
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+inline int64_t round_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
+
+int sm_count();
+
+// ---------------------------------------------------------------------------
+// Internal kernels shared between translation units
+// ---------------------------------------------------------------------------
+
+// One entry per unit of grouped-GEMM work along the token axis: up to 128
+// expert-sorted rows of one expert.  expert < 0 marks a chunk whose output rows
+// are to be zeroed.
+struct Chunk {
+  int32_t expert;
+  int32_t row0;   // first position in sorted_ids
+  int32_t rows;   // positions covered (<= 128); validity of each is the sentinel test
+  int32_t pad;
+};
+
+// Align + (optionally) chunk table, see routing.cu.
+int launch_align(const void *topk_ids, int ids_dtype, int64_t numel, int num_experts, int block_size,
+                 const int32_t *expert_map, int map_mode, int32_t *sorted_ids, int64_t sorted_capacity,
+                 int32_t *expert_ids, int64_t expert_ids_capacity, int32_t *num_tokens_post_pad,
+                 Chunk *chunks, int32_t *num_chunks, int64_t chunk_capacity, cudaStream_t stream);
+
+// Chunk table from an existing (expert_ids, num_tokens_post_pad) pair, see routing.cu.
+int launch_chunks_from_blocks(const int32_t *expert_ids, const int32_t *num_tokens_post_pad,
+                              int block_size, int64_t max_blocks, Chunk *chunks, int32_t *num_chunks,
+                              cudaStream_t stream);
+
+enum GemmMode { GEMM_GATE_UP = 0, GEMM_SINGLE = 1 };
+
+struct GemmArgs {
+  const int8_t *A;          // [rows_a, K] int8
+  const float *a_scale;     // [rows_a, K/128]
+  int64_t rows_a;
+  const int8_t *B;          // [E, n_rows_per_expert, K] int8
+  const float *b_scale;     // [E, n_rows_per_expert/128, K/128]
+  int E;
+  int64_t n_rows_per_expert;   // 2I for gate_up, N for single
+  int64_t K;
+  int n_tiles;              // 128-row output tiles per item: I/128 (gate_up) or N/128
+  const int32_t *sorted_ids;
+  int64_t numel_valid;      // sorted ids >= this are padding
+  int a_row_div;            // A row = sorted_id / a_row_div; 0 => A row = position in sorted_ids
+  const Chunk *chunks;
+  const int32_t *num_chunks;
+  // outputs
+  int8_t *act_q;            // gate_up: [positions, I]
+  float *act_s;             // gate_up: [positions, I/128]
+  __nv_bfloat16 *C;         // single: [numel_valid, N], row = sorted id
+  const float *topk_weights;   // flat [numel_valid] or null
+  int weight_mode;
+  float act_eps;            // eps of the fused re-quantisation, already rounded to bf16
+  int32_t *status;          // device word, set non-zero on a wait that ran out (may be null)
+};
+
+int launch_grouped_gemm(GemmMode mode, const GemmArgs &args, cudaStream_t stream);
+
+int launch_moe_sum_masked(const __nv_bfloat16 *in, __nv_bfloat16 *out, const __nv_bfloat16 *bias,
+                          int64_t M, int topk, int64_t H, float factor, const void *topk_ids,
+                          int ids_dtype, const int32_t *expert_map, cudaStream_t stream);
+
+}  // namespace lo

@@ -1,0 +1,188 @@
+// Host-side composition of the fused block-INT8 MoE layer and of the stand-alone
+// grouped GEMM entry point.  Everything here only carves the caller's workspace
+// and enqueues kernels on the caller's stream.
+#include "common.h"
+
+namespace lo {
+float round_eps_to_dtype(float eps, int dtype);   // quant.cu
+namespace {
+
+constexpr int64_t ALIGN_BYTES = 256;
+constexpr int FUSED_ALIGN_BLOCK = 16;   // expert segments start on multiples of the MMA N granule
+
+struct Carver {
+  uint8_t *base;
+  size_t off = 0;
+  explicit Carver(void *b) : base(static_cast<uint8_t *>(b)) {}
+  template <typename T> T *take(int64_t count) {
+    T *p = base ? reinterpret_cast<T *>(base + off) : nullptr;
+    off += (size_t)round_up(count * (int64_t)sizeof(T), ALIGN_BYTES);
+    return p;
+  }
+};
+
+struct FusedLayout {
+  int8_t *xq;
+  float *xs;
+  int32_t *header;      // [0] num_tokens_post_pad, [1] num_chunks
+  int32_t *sorted_ids;
+  Chunk *chunks;
+  int8_t *act_q;
+  float *act_s;
+  int64_t sorted_cap;
+  int64_t chunk_cap;
+  size_t bytes;
+};
+
+FusedLayout carve_fused(void *ws, int64_t M, int num_experts_for_align, int topk, int64_t H, int64_t I) {
+  FusedLayout L;
+  Carver c(ws);
+  const int64_t numel = M * topk;
+  L.sorted_cap = numel + (int64_t)num_experts_for_align * (FUSED_ALIGN_BLOCK - 1);
+  L.chunk_cap = numel / 128 + num_experts_for_align + 1;
+  L.header = c.take<int32_t>(64);
+  L.xq = c.take<int8_t>(M * H);
+  L.xs = c.take<float>(M * (H / 128));
+  L.sorted_ids = c.take<int32_t>(L.sorted_cap);
+  L.chunks = c.take<Chunk>(L.chunk_cap);
+  L.act_q = c.take<int8_t>(L.sorted_cap * I);
+  L.act_s = c.take<float>(L.sorted_cap * (I / 128));
+  L.bytes = c.off;
+  return L;
+}
+
+}  // namespace
+}  // namespace lo
+
+extern "C" size_t lo_fused_moe_workspace_bytes(int64_t M, int E_local, int global_num_experts, int topk, int64_t H,
+                                               int64_t I) {
+  const int e = global_num_experts > E_local ? global_num_experts : E_local;
+  return lo::carve_fused(nullptr, M, e, topk, H, I).bytes;
+}
+
+extern "C" int lo_fused_moe_workspace_layout(int64_t M, int E_local, int global_num_experts, int topk, int64_t H,
+                                            int64_t I, int64_t *out8) {
+  using namespace lo;
+  LO_REQUIRE(out8 != nullptr, "workspace layout: null output");
+  const int e = global_num_experts > E_local ? global_num_experts : E_local;
+  uint8_t *base = reinterpret_cast<uint8_t *>(uintptr_t(4096));   // any non-null base: only differences are used
+  FusedLayout L = carve_fused(base, M, e, topk, H, I);
+  out8[0] = reinterpret_cast<uint8_t *>(L.header) - base;
+  out8[1] = reinterpret_cast<uint8_t *>(L.xq) - base;
+  out8[2] = reinterpret_cast<uint8_t *>(L.xs) - base;
+  out8[3] = reinterpret_cast<uint8_t *>(L.sorted_ids) - base;
+  out8[4] = reinterpret_cast<uint8_t *>(L.chunks) - base;
+  out8[5] = reinterpret_cast<uint8_t *>(L.act_q) - base;
+  out8[6] = reinterpret_cast<uint8_t *>(L.act_s) - base;
+  out8[7] = L.sorted_cap;
+  return LO_OK;
+}
+
+extern "C" int lo_fused_moe_block_int8(const void *x, const int8_t *w1, const int8_t *w2, const float *w1_scale,
+                                       const float *w2_scale, const float *topk_weights, const void *topk_ids,
+                                       int ids_dtype, const int32_t *expert_map, int global_num_experts, int64_t M,
+                                       int E_local, int topk, int64_t H, int64_t I, void *cache3,
+                                       const void *shared_output, void *out, int apply_router_weight_on_input,
+                                       float routed_scaling_factor, void *workspace, size_t workspace_bytes,
+                                       int32_t *status, void *stream) {
+  using namespace lo;
+  LO_REQUIRE(M >= 0 && E_local >= 1 && topk >= 1, "fused moe: bad shape");
+  if (M == 0) return LO_OK;
+  LO_REQUIRE(x && w1 && w2 && w1_scale && w2_scale && topk_weights && topk_ids && cache3 && out && workspace,
+             "fused moe: null pointer");
+  LO_REQUIRE(H % 128 == 0 && I % 128 == 0, "fused moe: hidden (%lld) and intermediate (%lld) sizes must be multiples of 128",
+             (long long)H, (long long)I);
+  LO_REQUIRE(ids_dtype == LO_I32 || ids_dtype == LO_I64, "fused moe: topk_ids must be int32 or int64");
+  LO_REQUIRE(!apply_router_weight_on_input || topk == 1, "fused moe: apply_router_weight_on_input requires topk == 1");
+  LO_REQUIRE(M * topk < (1LL << 30), "fused moe: too many (token, slot) pairs; split the call into chunks");
+  if (global_num_experts <= 0) global_num_experts = E_local;
+  LO_REQUIRE(expert_map != nullptr || global_num_experts == E_local, "fused moe: global_num_experts != E needs an expert_map");
+  const int align_E = expert_map ? global_num_experts : E_local;
+  LO_REQUIRE(align_E <= 1024, "fused moe: more than 1024 experts");
+  LO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & (ALIGN_BYTES - 1)) == 0, "fused moe: workspace must be 256-byte aligned");
+  FusedLayout L = carve_fused(workspace, M, align_E, topk, H, I);
+  LO_REQUIRE(workspace_bytes >= L.bytes, "fused moe: workspace of %zu bytes, %zu needed", workspace_bytes, L.bytes);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t numel = M * topk;
+  int rc;
+
+  // 1. activations -> int8 + per-128 scales (token order)
+  rc = lo_group_quant_int8(x, LO_BF16, M * (H / 128), 128, 1e-10f, L.xq, L.xs, stream);
+  if (rc != LO_OK) return rc;
+
+  // 2. expert-major stable order + chunk table
+  rc = launch_align(topk_ids, ids_dtype, numel, align_E, FUSED_ALIGN_BLOCK, expert_map, expert_map ? 1 : 0,
+                    L.sorted_ids, L.sorted_cap, nullptr, 0, L.header, L.chunks, L.header + 1, L.chunk_cap, st);
+  if (rc != LO_OK) return rc;
+
+  // 3. gate_up GEMM, SiLU*mul and re-quantisation in the epilogue -> act_q/act_s in sorted order
+  GemmArgs g1{};
+  g1.A = L.xq; g1.a_scale = L.xs; g1.rows_a = M; g1.B = w1; g1.b_scale = w1_scale; g1.E = E_local;
+  g1.n_rows_per_expert = 2 * I; g1.K = H; g1.n_tiles = (int)(I / 128);
+  g1.sorted_ids = L.sorted_ids; g1.numel_valid = numel; g1.a_row_div = topk;
+  g1.chunks = L.chunks; g1.num_chunks = L.header + 1;
+  g1.act_q = L.act_q; g1.act_s = L.act_s; g1.C = nullptr;
+  g1.topk_weights = topk_weights;
+  g1.weight_mode = apply_router_weight_on_input ? LO_WEIGHT_FP32 : LO_WEIGHT_NONE;
+  g1.act_eps = round_eps_to_dtype(1e-10f, LO_BF16);
+  g1.status = status;
+  rc = launch_grouped_gemm(GEMM_GATE_UP, g1, st);
+  if (rc != LO_OK) return rc;
+
+  // 4. down GEMM, routed weight in the epilogue -> cache3[token, slot, :]
+  GemmArgs g2{};
+  g2.A = L.act_q; g2.a_scale = L.act_s; g2.rows_a = L.sorted_cap; g2.B = w2; g2.b_scale = w2_scale; g2.E = E_local;
+  g2.n_rows_per_expert = H; g2.K = I; g2.n_tiles = (int)(H / 128);
+  g2.sorted_ids = L.sorted_ids; g2.numel_valid = numel; g2.a_row_div = 0;
+  g2.chunks = L.chunks; g2.num_chunks = L.header + 1;
+  g2.C = static_cast<__nv_bfloat16 *>(cache3);
+  g2.topk_weights = topk_weights;
+  g2.weight_mode = apply_router_weight_on_input ? LO_WEIGHT_NONE : LO_WEIGHT_BF16_PRODUCT;
+  g2.act_eps = 0.f;
+  g2.status = status;
+  rc = launch_grouped_gemm(GEMM_SINGLE, g2, st);
+  if (rc != LO_OK) return rc;
+
+  // 5. top-k reduction (slots of non-local experts are skipped, their rows were never written)
+  return launch_moe_sum_masked(static_cast<const __nv_bfloat16 *>(cache3), static_cast<__nv_bfloat16 *>(out),
+                               static_cast<const __nv_bfloat16 *>(shared_output), M, topk, H, routed_scaling_factor,
+                               topk_ids, ids_dtype, expert_map, st);
+}
+
+extern "C" size_t lo_grouped_gemm_workspace_bytes(int64_t sorted_capacity, int block_size) {
+  if (block_size <= 0) return 0;
+  const int64_t blocks = lo::ceil_div(sorted_capacity, block_size);
+  const int per_block = block_size <= 128 ? 1 : block_size / 128;
+  return (size_t)(lo::ALIGN_BYTES + lo::round_up((blocks * per_block + 1) * (int64_t)sizeof(lo::Chunk), lo::ALIGN_BYTES));
+}
+
+extern "C" int lo_moe_grouped_gemm_i8_block(const int8_t *A, const float *a_scale, int64_t rows_a, const int8_t *B,
+                                            const float *b_scale, int E, int64_t N, int64_t K, void *C,
+                                            const float *topk_weights, int weight_mode, const int32_t *sorted_ids,
+                                            int64_t sorted_capacity, const int32_t *expert_ids,
+                                            const int32_t *num_tokens_post_pad, int64_t numel_valid, int top_k,
+                                            int block_size, void *workspace, size_t workspace_bytes, void *stream) {
+  using namespace lo;
+  LO_REQUIRE(A && a_scale && B && b_scale && C && sorted_ids && expert_ids && num_tokens_post_pad && workspace,
+             "grouped gemm: null pointer");
+  LO_REQUIRE(block_size >= 1 && (block_size <= 128 || block_size % 128 == 0),
+             "grouped gemm: block_size %d must be <= 128 or a multiple of 128", block_size);
+  LO_REQUIRE(top_k >= 1 && E >= 1 && rows_a >= 0, "grouped gemm: bad shape");
+  LO_REQUIRE(workspace_bytes >= lo_grouped_gemm_workspace_bytes(sorted_capacity, block_size),
+             "grouped gemm: workspace too small");
+  LO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & (ALIGN_BYTES - 1)) == 0, "grouped gemm: workspace must be 256-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int32_t *num_chunks = static_cast<int32_t *>(workspace);
+  Chunk *chunks = reinterpret_cast<Chunk *>(static_cast<uint8_t *>(workspace) + ALIGN_BYTES);
+  const int64_t max_blocks = ceil_div(sorted_capacity, block_size);
+  int rc = launch_chunks_from_blocks(expert_ids, num_tokens_post_pad, block_size, max_blocks, chunks, num_chunks, st);
+  if (rc != LO_OK) return rc;
+  GemmArgs g{};
+  g.A = A; g.a_scale = a_scale; g.rows_a = rows_a; g.B = B; g.b_scale = b_scale; g.E = E;
+  g.n_rows_per_expert = N; g.K = K; g.n_tiles = (int)(N / 128);
+  g.sorted_ids = sorted_ids; g.numel_valid = numel_valid; g.a_row_div = top_k;
+  g.chunks = chunks; g.num_chunks = num_chunks;
+  g.C = static_cast<__nv_bfloat16 *>(C);
+  g.topk_weights = topk_weights; g.weight_mode = weight_mode; g.act_eps = 0.f; g.status = nullptr;
+  return launch_grouped_gemm(GEMM_SINGLE, g, st);
+}

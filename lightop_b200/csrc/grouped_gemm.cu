@@ -1,0 +1,687 @@
+// Grouped block-INT8 GEMM for sm_100a: TMA-fed tcgen05 kind::i8 MMAs with int32
+// partial sums in tensor memory, promoted to fp32 once per 128-wide K block.
+//
+// Orientation ("swap-AB").  The 128 rows of a weight tile are the M side of the
+// MMA and the tokens of one expert are its N side (N = tokens rounded up to 16,
+// at most 128).  A chunk of 1..128 tokens therefore costs one pass over the
+// weight tile with no padding to 128 rows, which is what a weight-streaming
+// (HBM-bound) MoE needs, and the same kernel serves prefill and decode sizes.
+// In tensor memory a lane is an output column n and a column is a token.
+//
+// Work item = (chunk of <=128 expert-sorted rows, 128-row output tile).  Items
+// are ordered chunk-major so that CTAs running side by side share the chunk's
+// activation rows, and the chunks of one expert (adjacent in the table) read the
+// same weight tiles at about the same time out of L2.  Persistent CTAs take
+// items round-robin.
+//
+// Warp roles in a CTA of 12 warps (3 warpgroups):
+//   warp 0      : TMA producer for the weight tiles (one elected lane)
+//   warp 1      : MMA issuer (one elected lane); owns the tensor-memory allocation
+//   warps 2-3   : gather producers: token rows are fetched with 16-byte cp.async
+//                 by row index into the 128B-swizzled operand layout, the token
+//                 scales of the K block are multiplied with the weight-block
+//                 scale(s) into a per-stage table
+//   warps 4-11  : promotion / epilogue: tcgen05.ld of the int32 partial, convert,
+//                 multiply by the scale product, add into fp32 registers
+//                 (mul and add kept separate: same rounding sequence as the
+//                 reference's torch model), then the fused epilogue.
+// Pipelines: STAGES shared-memory stages (full/empty mbarriers) between the
+// producers and the MMA warp, two tensor-memory partial buffers (tmem_full /
+// tmem_empty) between the MMA warp and the promotion warps, so the MMAs of K
+// block kb+1 overlap the promotion of K block kb.
+//
+// Every wait is bounded: after about a second a waiter records a timeout in the
+// status word, raises a CTA-wide abort flag, and all roles fall through to the
+// common exit where tensor memory is released.
+#include "common.h"
+#include <cuda.h>
+#include <cudaTypedefs.h>
+#include <mutex>
+#include <map>
+#include <tuple>
+
+namespace lo {
+namespace {
+
+constexpr int TILE_N = 128;      // weight rows per accumulator (MMA M)
+constexpr int TILE_K = 128;      // int8 elements (= bytes) per K block
+constexpr int T_MAX = 128;       // tokens per chunk (MMA N upper bound)
+constexpr int KB_MAX = 128;      // K blocks supported (K <= 16384)
+constexpr int NUM_THREADS = 384;
+constexpr int GATHER_THREADS = 64;
+constexpr int EPI_WARPS = 8;
+constexpr int W_TILE_BYTES = TILE_N * TILE_K;   // 16 KiB
+constexpr int A_TILE_BYTES = T_MAX * TILE_K;    // 16 KiB
+constexpr uint32_t TMEM_COLS = 512;
+
+template <int MODE> struct Cfg;
+template <> struct Cfg<GEMM_GATE_UP> {
+  static constexpr int STAGES = 4;
+  static constexpr int NUM_W = 2;   // gate tile + up tile
+};
+template <> struct Cfg<GEMM_SINGLE> {
+  static constexpr int STAGES = 6;
+  static constexpr int NUM_W = 1;
+};
+
+template <int MODE> struct Smem {
+  static constexpr int STAGES = Cfg<MODE>::STAGES;
+  static constexpr int NUM_W = Cfg<MODE>::NUM_W;
+  // operand tiles first: each is a multiple of 1024 bytes, base is 1024-aligned
+  uint8_t w[STAGES][NUM_W][W_TILE_BYTES];
+  uint8_t a[STAGES][A_TILE_BYTES];
+  float a_s[STAGES][T_MAX];                // raw token scales of the K block (cp.async landing zone)
+  float sc[STAGES][NUM_W][T_MAX];          // token scale x weight-block scale
+  float bs[2][NUM_W][KB_MAX];              // weight-block scales of the item (double-buffered by item parity)
+  int32_t a_rows[T_MAX];                   // A row of every token of the chunk, -1 = zero fill
+  uint32_t amax[2][4][T_MAX / 2];          // gate_up epilogue: |act| maxima per (half, lane quarter, token)
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint64_t gsync;                          // rendezvous of the 64 gather threads
+  uint64_t esync[2];                       // rendezvous of the 128 epilogue threads of a token half
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+
+// ------------------------------ PTX wrappers --------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+constexpr uint64_t WAIT_LIMIT_NS = 1500ull * 1000ull * 1000ull;
+
+// Bounded wait.  Returns false when the CTA is aborting (this waiter timed out
+// or another one did); `code` identifies the waiter in the status word.
+template <class S>
+__device__ __forceinline__ bool mbar_wait(S &sm, uint64_t *bar, uint32_t parity, int32_t *status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 63u) == 0u) {
+      if (sm.abort_flag) return false;
+      if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+        sm.abort_flag = 1;
+        if (status) atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ uint64_t policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+
+// 2-D tiled TMA load global -> shared (this CTA), completion on an mbarrier.
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int32_t x, int32_t y, uint64_t *bar,
+                                            uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+      " [%0], [%1, {%2, %3}], [%4], %5;"
+      ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
+
+// 16-byte cp.async with zero fill when src_bytes == 0.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, uint32_t src_bytes, uint64_t policy) {
+  asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;" ::"r"(dst), "l"(src), "r"(src_bytes),
+               "l"(policy)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void *src, uint32_t src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, rows of 128 bytes, 128-byte
+// swizzle, 8-row groups 1024 bytes apart (tile base 1024-aligned).
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3ffffu) >> 4);   // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                     // leading byte offset (unused with swizzle), 16-byte units
+  d |= (uint64_t)(1024 >> 4) << 32;           // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                     // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                     // layout: 128-byte swizzle
+  return d;
+}
+
+// Instruction descriptor: int8 x int8 -> int32, both operands K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t make_idesc(uint32_t n) {
+  uint32_t d = 0;
+  d |= 2u << 4;            // accumulator format: S32
+  d |= 1u << 7;            // A format: signed 8-bit
+  d |= 1u << 10;           // B format: signed 8-bit
+  d |= (n >> 3) << 17;     // N / 8
+  d |= (128u >> 4) << 24;  // M / 16
+  return d;
+}
+
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// 32 consecutive tensor-memory columns of this thread's lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+struct KParams {
+  const int8_t *A;
+  const float *a_scale;
+  int64_t rows_a;
+  const float *b_scale;
+  int64_t n_rows_per_expert;
+  int64_t K;
+  int KB;
+  int n_tiles;
+  const int32_t *sorted_ids;
+  int64_t numel_valid;
+  int a_row_div;
+  const Chunk *chunks;
+  const int32_t *num_chunks;
+  int8_t *act_q;
+  float *act_s;
+  __nv_bfloat16 *C;
+  const float *topk_weights;
+  int weight_mode;
+  float act_eps;
+  int32_t *status;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const KParams p) {
+  using SM = Smem<MODE>;
+  constexpr int STAGES = SM::STAGES;
+  constexpr int NUM_W = SM::NUM_W;
+  extern __shared__ uint8_t smem_raw[];
+  SM &sm = *reinterpret_cast<SM *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+
+  // ------------------------------ set-up -----------------------------------
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&sm.full[s], GATHER_THREADS + 1);
+      mbar_init(&sm.empty[s], 1 + EPI_WARPS);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&sm.tmem_full[b], 1);
+      mbar_init(&sm.tmem_empty[b], EPI_WARPS);
+      mbar_init(&sm.esync[b], 128);
+    }
+    mbar_init(&sm.gsync, GATHER_THREADS);
+    sm.abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sm.tmem_base;
+
+  const int num_chunks = *p.num_chunks;
+  const int64_t num_items = (int64_t)num_chunks * p.n_tiles;
+  const int KB = p.KB;
+
+  if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+    if (warp == 0) {
+      // ===================== TMA producer: weight tiles ======================
+      if (lane == 0) {
+        const uint64_t pol = policy_evict_first();
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+          const Chunk ch = p.chunks[item / p.n_tiles];
+          const int nt = (int)(item % p.n_tiles);
+          if (ch.expert < 0) continue;
+          const int32_t row_g = (int32_t)(ch.expert * p.n_rows_per_expert + (int64_t)nt * TILE_N);
+          for (int kb = 0; kb < KB; ++kb, ++it) {
+            const int s = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1u;
+            if (!mbar_wait(sm, &sm.empty[s], ph ^ 1u, p.status, 1)) { ok = false; break; }
+            mbar_arrive_expect_tx(&sm.full[s], NUM_W * W_TILE_BYTES);
+            tma_load_2d(sm.w[s][0], &w_map, kb * TILE_K, row_g, &sm.full[s], pol);
+            if (NUM_W == 2)
+              tma_load_2d(sm.w[s][NUM_W - 1], &w_map, kb * TILE_K, row_g + p.n_tiles * TILE_N, &sm.full[s], pol);
+          }
+        }
+      }
+    } else if (warp == 1) {
+      // ============================ MMA issuer ===============================
+      if (lane == 0) {
+        uint32_t it = 0, ab = 0;
+        bool ok = true;
+        for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+          const Chunk ch = p.chunks[item / p.n_tiles];
+          if (ch.expert < 0) continue;
+          const uint32_t T = (uint32_t)((ch.rows + 15) & ~15);
+          const uint32_t idesc = make_idesc(T);
+          for (int kb = 0; kb < KB; ++kb, ++it, ++ab) {
+            const int s = it % STAGES;
+            const uint32_t ph = (it / STAGES) & 1u;
+            const uint32_t b = ab & 1u;
+            const uint32_t aph = (ab >> 1) & 1u;
+            if (!mbar_wait(sm, &sm.tmem_empty[b], aph ^ 1u, p.status, 2)) { ok = false; break; }
+            if (!mbar_wait(sm, &sm.full[s], ph, p.status, 3)) { ok = false; break; }
+            tc_fence_after();
+            const uint64_t bdesc = make_smem_desc(smem_u32(sm.a[s]));
+#pragma unroll
+            for (int w = 0; w < NUM_W; ++w) {
+              const uint64_t adesc = make_smem_desc(smem_u32(sm.w[s][w]));
+              const uint32_t d = tmem_base + b * 256u + (uint32_t)w * T_MAX;
+#pragma unroll
+              for (int k4 = 0; k4 < TILE_K / 32; ++k4)
+                umma_i8(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, k4 > 0 ? 1u : 0u);
+            }
+            umma_commit(&sm.empty[s]);
+            umma_commit(&sm.tmem_full[b]);
+          }
+        }
+      }
+    } else {
+      // ======================= gather producers (2 warps) ====================
+      const int g = tid - 64;            // 0..63
+      const int c16 = g & 7;             // 16-byte piece of the 128-byte row
+      const int r8 = g >> 3;             // row inside a pass of 8 rows
+      const uint64_t pol = policy_evict_last();
+      uint32_t it = 0;
+      uint32_t item_par = 0;
+      uint32_t gph = 0;
+      bool ok = true;
+      // lagged completion: stage issued at step i is published at step i + LAG
+      constexpr int LAG = 2;
+      int pend_s[LAG];
+      int pend_kb[LAG];
+      uint32_t pend_par[LAG];
+      int pend_T[LAG];
+      int npend = 0;
+      auto publish = [&](int s, int kb, uint32_t par, int T) {
+        // own cp.async data of stage s has landed: build the scale-product table
+        for (int t = g; t < T; t += GATHER_THREADS) {
+          const float as = sm.a_s[s][t];
+#pragma unroll
+          for (int w = 0; w < NUM_W; ++w) sm.sc[s][w][t] = __fmul_rn(as, sm.bs[par][w][kb]);
+        }
+        fence_proxy_async();
+        mbar_arrive(&sm.full[s]);
+      };
+      for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        const Chunk ch = p.chunks[item / p.n_tiles];
+        const int nt = (int)(item % p.n_tiles);
+        if (ch.expert < 0) continue;
+        const int T = (ch.rows + 15) & ~15;
+        // all gather threads are done issuing the previous item: safe to rewrite a_rows
+        mbar_arrive(&sm.gsync);
+        if (!mbar_wait(sm, &sm.gsync, gph, p.status, 7)) { ok = false; break; }
+        gph ^= 1u;
+        for (int t = g; t < T_MAX; t += GATHER_THREADS) {
+          int32_t r = -1;
+          if (t < ch.rows) {
+            const int32_t sid = p.sorted_ids[ch.row0 + t];
+            if (sid >= 0 && sid < p.numel_valid) r = p.a_row_div > 0 ? sid / p.a_row_div : ch.row0 + t;
+            if (r >= p.rows_a) r = -1;
+          }
+          sm.a_rows[t] = r;
+        }
+        {
+          const int64_t nblk = p.n_rows_per_expert / TILE_N;
+          const float *bsrc = p.b_scale + ((int64_t)ch.expert * nblk + nt) * KB;
+          for (int kb = g; kb < KB; kb += GATHER_THREADS) {
+            sm.bs[item_par][0][kb] = bsrc[kb];
+            if (NUM_W == 2) sm.bs[item_par][NUM_W - 1][kb] = bsrc[(int64_t)p.n_tiles * KB + kb];
+          }
+        }
+        mbar_arrive(&sm.gsync);
+        if (!mbar_wait(sm, &sm.gsync, gph, p.status, 8)) { ok = false; break; }
+        gph ^= 1u;
+        for (int kb = 0; kb < KB; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!mbar_wait(sm, &sm.empty[s], ph ^ 1u, p.status, 4)) { ok = false; break; }
+          const uint32_t a_base = smem_u32(sm.a[s]);
+          for (int r = r8; r < T; r += 8) {
+            const int32_t row = sm.a_rows[r];
+            const int8_t *src = p.A + (int64_t)(row < 0 ? 0 : row) * p.K + (int64_t)kb * TILE_K + c16 * 16;
+            const uint32_t dst = a_base + (uint32_t)r * 128u + (uint32_t)((c16 ^ (r & 7)) << 4);
+            cp_async_16(dst, src, row < 0 ? 0u : 16u, pol);
+          }
+          for (int t = g; t < T; t += GATHER_THREADS) {
+            const int32_t row = sm.a_rows[t];
+            const float *src = p.a_scale + (int64_t)(row < 0 ? 0 : row) * KB + kb;
+            cp_async_4(smem_u32(&sm.a_s[s][t]), src, row < 0 ? 0u : 4u);
+          }
+          cp_async_commit();
+          if (npend == LAG) {
+            cp_async_wait<LAG>();
+            publish(pend_s[0], pend_kb[0], pend_par[0], pend_T[0]);
+#pragma unroll
+            for (int i = 0; i + 1 < LAG; ++i) {
+              pend_s[i] = pend_s[i + 1]; pend_kb[i] = pend_kb[i + 1];
+              pend_par[i] = pend_par[i + 1]; pend_T[i] = pend_T[i + 1];
+            }
+            --npend;
+          }
+          pend_s[npend] = s; pend_kb[npend] = kb; pend_par[npend] = item_par; pend_T[npend] = T;
+          ++npend;
+        }
+        item_par ^= 1u;
+      }
+      // drain
+      cp_async_wait<0>();
+      if (ok) {
+        for (int i = 0; i < npend; ++i) publish(pend_s[i], pend_kb[i], pend_par[i], pend_T[i]);
+      }
+    }
+  } else {
+    // ====================== promotion + epilogue (8 warps) =====================
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+    const int ew = warp - 4;             // 0..7
+    const int q = warp & 3;              // lane quarter of tensor memory this warp may read
+    const int h = ew >> 2;               // token half: tokens [64h, 64h + 64)
+    const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+    uint32_t it = 0, ab = 0, eph = 0;
+    bool ok = true;
+    for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+      const Chunk ch = p.chunks[item / p.n_tiles];
+      const int nt = (int)(item % p.n_tiles);
+      const int n_local = q * 32 + lane;
+      if (ch.expert < 0) {
+        // block of a non-local expert: its output rows are zero
+        if (MODE == GEMM_SINGLE) {
+          for (int j = 0; j < 64; ++j) {
+            const int t = h * 64 + j;
+            if (t >= ch.rows) break;
+            const int32_t sid = p.sorted_ids[ch.row0 + t];
+            if (sid >= 0 && sid < p.numel_valid)
+              p.C[(int64_t)sid * p.n_rows_per_expert + (int64_t)nt * TILE_N + n_local] = __float2bfloat16_rn(0.f);
+          }
+        }
+        continue;
+      }
+      const int T = (ch.rows + 15) & ~15;
+      const int my_cols = T - h * 64;          // tokens of this half (may be <= 0)
+      float acc[NUM_W][64];
+#pragma unroll
+      for (int w = 0; w < NUM_W; ++w)
+#pragma unroll
+        for (int j = 0; j < 64; ++j) acc[w][j] = 0.f;
+
+      for (int kb = 0; kb < KB; ++kb, ++it, ++ab) {
+        const int s = it % STAGES;
+        const uint32_t ph = (it / STAGES) & 1u;
+        const uint32_t b = ab & 1u;
+        const uint32_t aph = (ab >> 1) & 1u;
+        if (!mbar_wait(sm, &sm.tmem_full[b], aph, p.status, 5)) { ok = false; break; }
+        if (!mbar_wait(sm, &sm.full[s], ph, p.status, 6)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          if (c * 32 < my_cols) {
+#pragma unroll
+            for (int w = 0; w < NUM_W; ++w) {
+              uint32_t raw[32];
+              tmem_ld32(tmem_base + lane_off + b * 256u + (uint32_t)w * T_MAX + (uint32_t)(h * 64 + c * 32), raw);
+              tmem_ld_wait();
+              const float4 *scv = reinterpret_cast<const float4 *>(&sm.sc[s][w][h * 64 + c * 32]);
+#pragma unroll
+              for (int j4 = 0; j4 < 8; ++j4) {
+                const float4 sc = scv[j4];
+                float *a = &acc[w][c * 32 + j4 * 4];
+                a[0] = __fadd_rn(a[0], __fmul_rn(__int2float_rn((int)raw[j4 * 4 + 0]), sc.x));
+                a[1] = __fadd_rn(a[1], __fmul_rn(__int2float_rn((int)raw[j4 * 4 + 1]), sc.y));
+                a[2] = __fadd_rn(a[2], __fmul_rn(__int2float_rn((int)raw[j4 * 4 + 2]), sc.z));
+                a[3] = __fadd_rn(a[3], __fmul_rn(__int2float_rn((int)raw[j4 * 4 + 3]), sc.w));
+              }
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&sm.tmem_empty[b]);
+          mbar_arrive(&sm.empty[s]);
+        }
+      }
+      if (!ok) break;
+
+      // ------------------------------ epilogue -------------------------------
+      if (MODE == GEMM_GATE_UP) {
+        const int64_t I = (int64_t)p.n_tiles * TILE_N;
+        // act = bf16(bf16(silu(bf16(gate))) * bf16(up)); kept in acc[0]
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          if (j < my_cols) {
+            float gte = acc[0][j], up = acc[NUM_W - 1][j];
+            if (p.weight_mode == LO_WEIGHT_FP32) {
+              const int t = h * 64 + j;
+              float wgt = 0.f;
+              if (t < ch.rows) {
+                const int32_t sid = p.sorted_ids[ch.row0 + t];
+                if (sid >= 0 && sid < p.numel_valid) wgt = p.topk_weights[sid];
+              }
+              gte *= wgt;
+              up *= wgt;
+            }
+            gte = bf16_round(gte);
+            up = bf16_round(up);
+            const float sl = bf16_round(gte / (1.0f + expf(-gte)));
+            const float act = bf16_round(sl * up);
+            acc[0][j] = act;
+            const uint32_t m = __reduce_max_sync(0xffffffffu, __float_as_uint(act) & 0x7fffffffu);
+            if (lane == 0) sm.amax[h][q][j] = m;
+          }
+        }
+        mbar_arrive(&sm.esync[h]);
+        if (!mbar_wait(sm, &sm.esync[h], eph, p.status, 9)) { ok = false; break; }
+        eph ^= 1u;
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          const int t = h * 64 + j;
+          if (t < ch.rows) {
+            const uint32_t m = max(max(sm.amax[h][0][j], sm.amax[h][1][j]), max(sm.amax[h][2][j], sm.amax[h][3][j]));
+            const float amax = fmaxf(__uint_as_float(m), p.act_eps);
+            const float scale = __fdiv_rn(amax, 127.0f);
+            float r = __fdiv_rn(acc[0][j], scale);
+            r = fminf(fmaxf(r, -128.0f), 127.0f);
+            const int64_t pos = (int64_t)ch.row0 + t;
+            p.act_q[pos * I + (int64_t)nt * TILE_N + n_local] = (int8_t)__float2int_rz(r);
+            if (q == 0 && lane == 0) p.act_s[pos * p.n_tiles + nt] = scale;
+          }
+        }
+        // the amax table is reused by the next item
+        mbar_arrive(&sm.esync[h]);
+        if (!mbar_wait(sm, &sm.esync[h], eph, p.status, 10)) { ok = false; break; }
+        eph ^= 1u;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          const int t = h * 64 + j;
+          if (t < ch.rows) {
+            const int32_t sid = p.sorted_ids[ch.row0 + t];
+            if (sid >= 0 && sid < p.numel_valid) {
+              float v = acc[0][j];
+              if (p.weight_mode == LO_WEIGHT_FP32) {
+                v = v * p.topk_weights[sid];
+              } else if (p.weight_mode == LO_WEIGHT_BF16_PRODUCT) {
+                v = bf16_round(v) * bf16_round(p.topk_weights[sid]);
+              }
+              p.C[(int64_t)sid * p.n_rows_per_expert + (int64_t)nt * TILE_N + n_local] = __float2bfloat16_rn(v);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ------------------------------ teardown -----------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (sm.abort_flag) {
+    // give copies that may still be in flight time to land before the CTA's shared memory is released
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) {
+    }
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------ host side ----------------------------------
+
+PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+  });
+  return fn;
+}
+
+// Tensor map of a [rows, K] int8 matrix, box 128 rows x 128 bytes, 128-byte swizzle.
+int make_weight_map(CUtensorMap *map, const int8_t *B, int64_t rows, int64_t K) {
+  static std::mutex mu;
+  static std::map<std::tuple<const void *, int64_t, int64_t>, CUtensorMap> cache;
+  std::lock_guard<std::mutex> lock(mu);
+  auto key = std::make_tuple((const void *)B, rows, K);
+  auto itc = cache.find(key);
+  if (itc != cache.end()) {
+    *map = itc->second;
+    return LO_OK;
+  }
+  auto encode = get_encode_fn();
+  if (!encode) return fail(LO_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the CUDA driver");
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K};
+  cuuint32_t box[2] = {TILE_K, TILE_N};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t *>(B), dims, strides, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(LO_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+  if (cache.size() > 256) cache.clear();
+  cache[key] = *map;
+  return LO_OK;
+}
+
+template <int MODE>
+int launch_mode(const GemmArgs &a, cudaStream_t stream) {
+  using SM = Smem<MODE>;
+  const size_t smem_bytes = sizeof(SM) + 1024;
+  static thread_local bool configured = false;
+  if (!configured) {
+    LO_CUDA_OK(cudaFuncSetAttribute(grouped_gemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+    configured = true;
+  }
+  CUtensorMap map;
+  int rc = make_weight_map(&map, a.B, (int64_t)a.E * a.n_rows_per_expert, a.K);
+  if (rc != LO_OK) return rc;
+  KParams p;
+  p.A = a.A; p.a_scale = a.a_scale; p.rows_a = a.rows_a; p.b_scale = a.b_scale;
+  p.n_rows_per_expert = a.n_rows_per_expert; p.K = a.K; p.KB = (int)(a.K / TILE_K); p.n_tiles = a.n_tiles;
+  p.sorted_ids = a.sorted_ids; p.numel_valid = a.numel_valid; p.a_row_div = a.a_row_div;
+  p.chunks = a.chunks; p.num_chunks = a.num_chunks; p.act_q = a.act_q; p.act_s = a.act_s; p.C = a.C;
+  p.topk_weights = a.topk_weights; p.weight_mode = a.weight_mode; p.act_eps = a.act_eps; p.status = a.status;
+  const int grid = sm_count();
+  if (grid <= 0) return fail(LO_ERR_CUDA, "no CUDA device");
+  grouped_gemm_kernel<MODE><<<grid, NUM_THREADS, smem_bytes, stream>>>(map, p);
+  LO_LAUNCH_OK("grouped_gemm_kernel");
+  return LO_OK;
+}
+
+}  // namespace
+
+int launch_grouped_gemm(GemmMode mode, const GemmArgs &a, cudaStream_t stream) {
+  LO_REQUIRE(a.K % TILE_K == 0 && a.K >= TILE_K && a.K / TILE_K <= KB_MAX, "grouped gemm: K=%lld must be a multiple of 128, at most %d",
+             (long long)a.K, KB_MAX * TILE_K);
+  LO_REQUIRE(a.n_rows_per_expert % TILE_N == 0, "grouped gemm: N=%lld must be a multiple of 128", (long long)a.n_rows_per_expert);
+  LO_REQUIRE((int64_t)a.E * a.n_rows_per_expert < (1LL << 31), "grouped gemm: E*N exceeds the tensor-map row range");
+  LO_REQUIRE((reinterpret_cast<uintptr_t>(a.B) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.A) & 15) == 0,
+             "grouped gemm: operands must be 16-byte aligned");
+  LO_REQUIRE(a.weight_mode == LO_WEIGHT_NONE || a.topk_weights != nullptr, "grouped gemm: weight mode %d needs topk_weights", a.weight_mode);
+  if (mode == GEMM_GATE_UP) {
+    LO_REQUIRE(a.n_rows_per_expert == 2 * (int64_t)a.n_tiles * TILE_N, "grouped gemm: gate_up needs N = 2*I");
+    return launch_mode<GEMM_GATE_UP>(a, stream);
+  }
+  LO_REQUIRE(a.n_rows_per_expert == (int64_t)a.n_tiles * TILE_N, "grouped gemm: tile count mismatch");
+  return launch_mode<GEMM_SINGLE>(a, stream);
+}
+
+}  // namespace lo

@@ -1,0 +1,336 @@
+// Top-k reduction (moe_sum) and the expert-parallel local permutation kernels
+// (ep_scatter / ep_build_m_indices / ep_gather).  All are streaming,
+// HBM-bound kernels: 16-byte vector accesses, fp32 accumulation.
+#include "common.h"
+
+namespace lo {
+namespace {
+
+template <typename T> struct Vec8;   // 8 elements of T
+template <> struct Vec8<__nv_bfloat16> {
+  uint4 raw;
+  __device__ __forceinline__ void to_float(float (&f)[8]) const {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __uint_as_float(w[i] << 16);
+      f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+  __device__ __forceinline__ void from_float(const float (&f)[8]) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 p = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+      w[i] = *reinterpret_cast<uint32_t *>(&p);
+    }
+    raw = make_uint4(w[0], w[1], w[2], w[3]);
+  }
+};
+template <> struct Vec8<__half> {
+  uint4 raw;
+  __device__ __forceinline__ void to_float(float (&f)[8]) const {
+    const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 v = __half22float2(h[i]);
+      f[2 * i] = v.x;
+      f[2 * i + 1] = v.y;
+    }
+  }
+  __device__ __forceinline__ void from_float(const float (&f)[8]) {
+    __half2 *h = reinterpret_cast<__half2 *>(&raw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+  }
+};
+template <> struct Vec8<float> {
+  float4 a, b;
+  __device__ __forceinline__ void to_float(float (&f)[8]) const {
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+  }
+  __device__ __forceinline__ void from_float(const float (&f)[8]) {
+    a = make_float4(f[0], f[1], f[2], f[3]);
+    b = make_float4(f[4], f[5], f[6], f[7]);
+  }
+};
+
+// skip rule of one (token, slot):
+//   mask     : optional bool [M, topk]
+//   ids/map  : optional routing ids + expert_map; the slot is skipped when its expert is not local
+template <typename T, typename IdT>
+__global__ void __launch_bounds__(256) moe_sum_kernel(const T *__restrict__ in, T *__restrict__ out,
+                                                      const T *__restrict__ bias, int64_t M, int topk, int64_t H8,
+                                                      float factor, const uint8_t *__restrict__ mask,
+                                                      const int32_t *__restrict__ num_local_tokens,
+                                                      const IdT *__restrict__ ids, const int32_t *__restrict__ expert_map) {
+  using V = Vec8<T>;
+  const int64_t t = blockIdx.y;
+  if (num_local_tokens && t >= *num_local_tokens) return;
+  const V *in_v = reinterpret_cast<const V *>(in) + t * topk * H8;
+  for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < H8; c += (int64_t)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < topk; ++j) {
+      if (mask && !mask[t * topk + j]) continue;
+      if (ids) {
+        const long long e = (long long)ids[t * topk + j];
+        if (e < 0 || (expert_map && expert_map[e] < 0)) continue;
+      }
+      float f[8];
+      in_v[(int64_t)j * H8 + c].to_float(f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += f[i];
+    }
+    if (bias) {
+      float b[8];
+      reinterpret_cast<const V *>(bias)[t * H8 + c].to_float(b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = acc[i] * factor + b[i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = acc[i] * factor;
+    }
+    V o;
+    o.from_float(acc);
+    reinterpret_cast<V *>(out)[t * H8 + c] = o;
+  }
+}
+
+template <typename T, typename IdT>
+int launch_sum(const void *in, void *out, const void *bias, int64_t M, int topk, int64_t H, float factor,
+               const uint8_t *mask, const int32_t *nlt, const void *ids, const int32_t *expert_map,
+               cudaStream_t st) {
+  const int64_t H8 = H / 8;
+  dim3 grid((unsigned)(ceil_div(H8, 256) > 65535 ? 65535 : ceil_div(H8, 256)), (unsigned)M);
+  moe_sum_kernel<T, IdT><<<grid, 256, 0, st>>>(static_cast<const T *>(in), static_cast<T *>(out),
+                                              static_cast<const T *>(bias), M, topk, H8, factor, mask, nlt,
+                                              static_cast<const IdT *>(ids), expert_map);
+  LO_LAUNCH_OK("moe_sum_kernel");
+  return LO_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Expert-parallel local permutation.
+// ---------------------------------------------------------------------------
+
+template <typename IdT>
+__device__ __forceinline__ int local_expert(const IdT *ids, int64_t i, const int32_t *expert_map, int local_E) {
+  long long e = (long long)ids[i];
+  if (e < 0) return -1;
+  if (expert_map) e = expert_map[e];
+  if (e < 0 || e >= local_E) return -1;
+  return (int)e;
+}
+
+// One CTA: aligned exclusive offsets from the per-expert counts, m_indices fill,
+// and the stable destination row of every (token, slot) -> inv_perm.
+// Same warp-histogram scheme as the alignment kernel (32 warps, match_any).
+template <typename IdT>
+__global__ void __launch_bounds__(1024) ep_plan_kernel(const IdT *__restrict__ ids, int64_t numel,
+                                                       const int32_t *__restrict__ expert_map,
+                                                       const int32_t *__restrict__ counts_in, int local_E,
+                                                       int alignment, int32_t *__restrict__ m_indices, int64_t rows,
+                                                       int32_t *__restrict__ inv_perm) {
+  extern __shared__ int32_t smem[];
+  int32_t *hist = smem;                 // [32][local_E]
+  int32_t *off = smem + 32 * local_E;   // [local_E + 1]
+  int32_t *cnt = off + local_E + 1;     // [local_E]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  for (int i = tid; i < 32 * local_E; i += blockDim.x) hist[i] = 0;
+  for (int64_t i = tid; i < rows; i += blockDim.x) m_indices[i] = -1;
+  __syncthreads();
+  int64_t seg_len = (numel + 31) / 32;
+  seg_len = (seg_len + 31) / 32 * 32;
+  const int64_t seg_begin = (int64_t)warp * seg_len;
+  const int64_t seg_end = seg_begin + seg_len < numel ? seg_begin + seg_len : numel;
+  int32_t *my_hist = hist + warp * local_E;
+  for (int64_t base = seg_begin; base < seg_end; base += 32) {
+    const int64_t i = base + lane;
+    const int e = i < seg_end ? local_expert<IdT>(ids, i, expert_map, local_E) : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    if (e >= 0 && lane == (__ffs(peers) - 1)) my_hist[e] += __popc(peers);
+    __syncwarp();
+  }
+  __syncthreads();
+  for (int e = tid; e < local_E; e += blockDim.x) {
+    int run = 0;
+    for (int w = 0; w < 32; ++w) {
+      const int c = hist[w * local_E + e];
+      hist[w * local_E + e] = run;
+      run += c;
+    }
+    cnt[e] = counts_in ? counts_in[e] : run;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int run = 0;
+    for (int e = 0; e < local_E; ++e) {
+      off[e] = run;
+      run += (cnt[e] + alignment - 1) / alignment * alignment;
+    }
+    off[local_E] = run;
+  }
+  __syncthreads();
+  for (int e = warp; e < local_E; e += 32)
+    for (int r = lane; r < cnt[e]; r += 32)
+      if (off[e] + r < rows) m_indices[off[e] + r] = e;
+  if (inv_perm == nullptr) return;
+  for (int64_t base = seg_begin; base < seg_end; base += 32) {
+    const int64_t i = base + lane;
+    const int e = i < seg_end ? local_expert<IdT>(ids, i, expert_map, local_E) : -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    int before = 0;
+    if (e >= 0) before = my_hist[e];
+    __syncwarp();
+    if (i < seg_end) inv_perm[i] = e >= 0 ? off[e] + before + rank : -1;
+    if (e >= 0 && lane == (__ffs(peers) - 1)) my_hist[e] = before + __popc(peers);
+    __syncwarp();
+  }
+}
+
+// One CTA per (token, slot): copy the int8 row and its scales to inv_perm[token, slot].
+__global__ void __launch_bounds__(128) ep_copy_rows_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as,
+                                                           int scale_cols, const int32_t *__restrict__ inv_perm,
+                                                           int8_t *__restrict__ aq_out, float *__restrict__ as_out,
+                                                           int k, int64_t H, int64_t rows) {
+  const int64_t flat = blockIdx.x;
+  const int32_t dst = inv_perm[flat];
+  if (dst < 0 || dst >= rows) return;
+  const int64_t t = flat / k;
+  const uint4 *src = reinterpret_cast<const uint4 *>(aq + t * H);
+  uint4 *d = reinterpret_cast<uint4 *>(aq_out + (int64_t)dst * H);
+  for (int64_t c = threadIdx.x; c < H / 16; c += blockDim.x) d[c] = src[c];
+  for (int c = threadIdx.x; c < scale_cols; c += blockDim.x) as_out[(int64_t)dst * scale_cols + c] = as[t * scale_cols + c];
+}
+
+template <typename IdT>
+__global__ void __launch_bounds__(256) ep_gather_kernel(const __nv_bfloat16 *__restrict__ a, const IdT *__restrict__ ids,
+                                                        const float *__restrict__ w, const int32_t *__restrict__ inv_perm,
+                                                        const int32_t *__restrict__ expert_map,
+                                                        __nv_bfloat16 *__restrict__ out, int k, int64_t H8) {
+  using V = Vec8<__nv_bfloat16>;
+  const int64_t t = blockIdx.y;
+  for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < H8; c += (int64_t)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < k; ++j) {
+      const long long e = (long long)ids[t * k + j];
+      if (e < 0 || (expert_map && expert_map[e] < 0)) continue;
+      const int32_t r = inv_perm[t * k + j];
+      if (r < 0) continue;
+      const float wj = w[t * k + j];
+      float f[8];
+      reinterpret_cast<const V *>(a)[(int64_t)r * H8 + c].to_float(f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = fmaf(wj, f[i], acc[i]);
+    }
+    V o;
+    o.from_float(acc);
+    reinterpret_cast<V *>(out)[t * H8 + c] = o;
+  }
+}
+
+}  // namespace
+
+int launch_moe_sum_masked(const __nv_bfloat16 *in, __nv_bfloat16 *out, const __nv_bfloat16 *bias, int64_t M,
+                          int topk, int64_t H, float factor, const void *topk_ids, int ids_dtype,
+                          const int32_t *expert_map, cudaStream_t stream) {
+  if (M == 0) return LO_OK;
+  if (ids_dtype == LO_I64)
+    return launch_sum<__nv_bfloat16, int64_t>(in, out, bias, M, topk, H, factor, nullptr, nullptr, topk_ids, expert_map, stream);
+  return launch_sum<__nv_bfloat16, int32_t>(in, out, bias, M, topk, H, factor, nullptr, nullptr, topk_ids, expert_map, stream);
+}
+
+}  // namespace lo
+
+extern "C" int lo_moe_sum(const void *in, void *out, const void *bias, int dtype, int64_t M, int topk, int64_t H,
+                          float factor, const uint8_t *expert_mask, const int32_t *num_local_tokens, void *stream) {
+  using namespace lo;
+  LO_REQUIRE(M >= 0 && topk >= 1 && H >= 0, "moe_sum: bad shape");
+  if (M == 0 || H == 0) return LO_OK;
+  LO_REQUIRE(in && out, "moe_sum: null pointer");
+  LO_REQUIRE(H % 8 == 0, "moe_sum: hidden size %lld is not a multiple of 8", (long long)H);
+  LO_REQUIRE(M <= 0x7fffffffLL, "moe_sum: too many tokens");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case LO_BF16: return launch_sum<__nv_bfloat16, int32_t>(in, out, bias, M, topk, H, factor, expert_mask, num_local_tokens, nullptr, nullptr, st);
+    case LO_F16: return launch_sum<__half, int32_t>(in, out, bias, M, topk, H, factor, expert_mask, num_local_tokens, nullptr, nullptr, st);
+    case LO_F32: return launch_sum<float, int32_t>(in, out, bias, M, topk, H, factor, expert_mask, num_local_tokens, nullptr, nullptr, st);
+    default: return fail(LO_ERR_UNSUPPORTED, "moe_sum: unsupported dtype code %d", dtype);
+  }
+}
+
+extern "C" int lo_ep_build_m_indices(const void *topk_ids, int ids_dtype, int64_t numel, int32_t *m_indices,
+                                     int64_t rows, int local_num_experts, int alignment, void *stream) {
+  using namespace lo;
+  LO_REQUIRE(local_num_experts >= 1 && local_num_experts <= 1024, "ep_build_m_indices: local_num_experts out of range");
+  LO_REQUIRE(alignment >= 1 && m_indices && (topk_ids || numel == 0), "ep_build_m_indices: bad argument");
+  const size_t smem = sizeof(int32_t) * (34 * (size_t)local_num_experts + 1);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (ids_dtype == LO_I64) {
+    LO_CUDA_OK(cudaFuncSetAttribute(ep_plan_kernel<int64_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    ep_plan_kernel<int64_t><<<1, 1024, smem, st>>>(static_cast<const int64_t *>(topk_ids), numel, nullptr, nullptr,
+                                                  local_num_experts, alignment, m_indices, rows, nullptr);
+  } else if (ids_dtype == LO_I32) {
+    LO_CUDA_OK(cudaFuncSetAttribute(ep_plan_kernel<int32_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    ep_plan_kernel<int32_t><<<1, 1024, smem, st>>>(static_cast<const int32_t *>(topk_ids), numel, nullptr, nullptr,
+                                                  local_num_experts, alignment, m_indices, rows, nullptr);
+  } else {
+    return fail(LO_ERR_UNSUPPORTED, "ep_build_m_indices: unsupported id dtype code %d", ids_dtype);
+  }
+  LO_LAUNCH_OK("ep_plan_kernel");
+  return LO_OK;
+}
+
+extern "C" int lo_ep_scatter(const int8_t *aq, const float *aq_scale, int scale_cols, const void *topk_ids,
+                             int ids_dtype, const int32_t *expert_map, const int32_t *expert_num_tokens,
+                             int8_t *aq_out, float *aq_scale_out, int32_t *m_indices, int32_t *inv_perm, int64_t T,
+                             int k, int64_t H, int64_t rows, int local_num_experts, int alignment, void *stream) {
+  using namespace lo;
+  LO_REQUIRE(local_num_experts >= 1 && local_num_experts <= 1024, "ep_scatter: local_num_experts out of range");
+  LO_REQUIRE(alignment >= 1 && k >= 1 && T >= 0 && rows >= 0, "ep_scatter: bad shape");
+  LO_REQUIRE(H % 16 == 0, "ep_scatter: hidden size %lld is not a multiple of 16", (long long)H);
+  LO_REQUIRE(aq && aq_scale && topk_ids && aq_out && aq_scale_out && m_indices && inv_perm, "ep_scatter: null pointer");
+  LO_REQUIRE(T * k <= 0x7fffffffLL, "ep_scatter: too many (token, slot) pairs");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t smem = sizeof(int32_t) * (34 * (size_t)local_num_experts + 1);
+  if (ids_dtype == LO_I64) {
+    LO_CUDA_OK(cudaFuncSetAttribute(ep_plan_kernel<int64_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    ep_plan_kernel<int64_t><<<1, 1024, smem, st>>>(static_cast<const int64_t *>(topk_ids), T * k, expert_map,
+                                                  expert_num_tokens, local_num_experts, alignment, m_indices, rows, inv_perm);
+  } else if (ids_dtype == LO_I32) {
+    LO_CUDA_OK(cudaFuncSetAttribute(ep_plan_kernel<int32_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    ep_plan_kernel<int32_t><<<1, 1024, smem, st>>>(static_cast<const int32_t *>(topk_ids), T * k, expert_map,
+                                                  expert_num_tokens, local_num_experts, alignment, m_indices, rows, inv_perm);
+  } else {
+    return fail(LO_ERR_UNSUPPORTED, "ep_scatter: unsupported id dtype code %d", ids_dtype);
+  }
+  LO_LAUNCH_OK("ep_plan_kernel");
+  if (T * k > 0) {
+    ep_copy_rows_kernel<<<(unsigned)(T * k), 128, 0, st>>>(aq, aq_scale, scale_cols, inv_perm, aq_out, aq_scale_out, k, H, rows);
+    LO_LAUNCH_OK("ep_copy_rows_kernel");
+  }
+  return LO_OK;
+}
+
+extern "C" int lo_ep_gather(const void *a, const void *topk_ids, int ids_dtype, const float *topk_weights,
+                            const int32_t *inv_perm, const int32_t *expert_map, void *out, int64_t T, int k,
+                            int64_t H, void *stream) {
+  using namespace lo;
+  LO_REQUIRE(T >= 0 && k >= 1 && H % 8 == 0, "ep_gather: bad shape");
+  if (T == 0) return LO_OK;
+  LO_REQUIRE(a && topk_ids && topk_weights && inv_perm && out, "ep_gather: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t H8 = H / 8;
+  dim3 grid((unsigned)(ceil_div(H8, 256)), (unsigned)T);
+  if (ids_dtype == LO_I64)
+    ep_gather_kernel<int64_t><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(a), static_cast<const int64_t *>(topk_ids),
+                                                   topk_weights, inv_perm, expert_map, static_cast<__nv_bfloat16 *>(out), k, H8);
+  else if (ids_dtype == LO_I32)
+    ep_gather_kernel<int32_t><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16 *>(a), static_cast<const int32_t *>(topk_ids),
+                                                   topk_weights, inv_perm, expert_map, static_cast<__nv_bfloat16 *>(out), k, H8);
+  else
+    return fail(LO_ERR_UNSUPPORTED, "ep_gather: unsupported id dtype code %d", ids_dtype);
+  LO_LAUNCH_OK("ep_gather_kernel");
+  return LO_OK;
+}

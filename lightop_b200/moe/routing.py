@@ -1,0 +1,141 @@
+"""Routing, expert alignment and top-k reduction (reference: python/lightop/moe/routing.py)."""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from .. import _lib
+
+
+def _cdiv(a: int, b: int) -> int:
+    return (a + b - 1) // b
+
+
+def _round_up(a: int, b: int) -> int:
+    return _cdiv(a, b) * b
+
+
+def topk_softmax(topk_weights: torch.Tensor, topk_indices: torch.Tensor,
+                 token_expert_indices: Optional[torch.Tensor], gating_output: torch.Tensor,
+                 Is_renormalize: bool = False) -> None:
+    """Softmax over experts + top-k, written into the caller's tensors.
+
+    Signature of the reference's ``op.topk_softmax`` (csrc/pybind/export.cpp:546,1437;
+    host csrc/kernels/softmax/topk_softmax_kernels.cu:1716-1791).  ``topk_weights`` fp32
+    ``[M,k]``; ``topk_indices`` int32 / uint32 / int64 ``[M,k]`` in descending score order;
+    ``token_expert_indices`` int32 ``[M,k]`` receives ``slot * M + token``.
+    """
+    _lib.require_cuda(topk_weights, topk_indices, token_expert_indices, gating_output)
+    if gating_output.dim() != 2:
+        raise RuntimeError("gating_output must be [num_tokens, num_experts]")
+    M, E = gating_output.shape
+    k = topk_indices.shape[-1]
+    if topk_weights.dtype != torch.float32:
+        raise RuntimeError("topk_weights must be float32")
+    if tuple(topk_weights.shape) != (M, k) or tuple(topk_indices.shape) != (M, k):
+        raise RuntimeError("topk_weights / topk_indices must be [num_tokens, topk]")
+    if token_expert_indices is not None and token_expert_indices.dtype != torch.int32:
+        raise RuntimeError("token_expert_indices must be int32")
+    if not (gating_output.is_contiguous() and topk_weights.is_contiguous() and topk_indices.is_contiguous()):
+        raise RuntimeError("topk_softmax expects contiguous tensors")
+    with torch.cuda.device(gating_output.device):
+        st = _lib.load().lo_topk_softmax(_lib.ptr(gating_output), _lib.dtype_code(gating_output.dtype), M, E, k,
+                                         int(bool(Is_renormalize)), _lib.ptr(topk_weights), _lib.ptr(topk_indices),
+                                         _lib.dtype_code(topk_indices.dtype), _lib.ptr(token_expert_indices),
+                                         _lib.current_stream(gating_output.device))
+    _lib.check(st, "topk_softmax")
+
+
+def moe_align_block_size_out(topk_ids, num_experts, block_size, sorted_ids, expert_ids, num_tokens_post_pad,
+                             expert_map=None, expert_mask=None, num_local_tokens=None, is_ep=False,
+                             is_fuse_fill=True):
+    """Expert alignment into caller-provided tensors (reference: python/lightop/moe/routing.py:23-50).
+
+    With an ``expert_map`` the ids are mapped before counting and ids mapping to -1 are
+    dropped, as the reference's native kernel does when it is handed a map.  ``expert_mask``,
+    ``num_local_tokens`` and ``is_ep`` select HCU-specific variants and are not supported;
+    the sentinel fill is always done (``is_fuse_fill``).
+    """
+    if expert_mask is not None or num_local_tokens is not None:
+        raise NotImplementedError("expert_mask / num_local_tokens variants are not part of this path")
+    _lib.require_cuda(topk_ids, sorted_ids, expert_ids, num_tokens_post_pad, expert_map)
+    if sorted_ids.dtype != torch.int32 or expert_ids.dtype != torch.int32 or num_tokens_post_pad.dtype != torch.int32:
+        raise RuntimeError("sorted_ids, expert_ids and num_tokens_post_pad must be int32")
+    ids = topk_ids if topk_ids.is_contiguous() else topk_ids.contiguous()
+    if expert_map is not None and expert_map.dtype != torch.int32:
+        expert_map = expert_map.to(torch.int32)
+    with torch.cuda.device(ids.device):
+        st = _lib.load().lo_moe_align_block_size(
+            _lib.ptr(ids), _lib.dtype_code(ids.dtype), ids.numel(), int(num_experts), int(block_size),
+            _lib.ptr(expert_map), 1 if expert_map is not None else 0, _lib.ptr(sorted_ids), sorted_ids.numel(),
+            _lib.ptr(expert_ids), expert_ids.numel(), _lib.ptr(num_tokens_post_pad), _lib.current_stream(ids.device))
+    _lib.check(st, "moe_align_block_size")
+
+
+def moe_align_block_size(topk_ids: torch.Tensor, block_size: int, num_experts: int,
+                         expert_map: Optional[torch.Tensor] = None, pad_sorted_ids: bool = False,
+                         ignore_invalid_experts: bool = False
+                         ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Sort the flat ``(token, slot)`` indices by expert and pad every expert to ``block_size``.
+
+    Signature, buffer sizes and the sentinel convention follow the reference wrapper
+    (python/lightop/_lmslim_native/vllm_compat/moe_align_block_size.py:17-120).  With an
+    ``expert_map``: ``ignore_invalid_experts=True`` drops ids that map to -1 before counting
+    and returns local expert ids; otherwise all ids are counted and ``expert_ids`` holds
+    ``expert_map[expert]`` (-1 for blocks of non-local experts).  Inside an expert the
+    indices are ascending, the order of the reference's Python model
+    (test/test_moe_align_block_size.py:79-87).
+    """
+    _lib.require_cuda(topk_ids, expert_map)
+    numel = topk_ids.numel()
+    max_num_tokens_padded = numel + num_experts * (block_size - 1)
+    if pad_sorted_ids:
+        max_num_tokens_padded = _round_up(max_num_tokens_padded, block_size)
+    if numel < num_experts:
+        max_num_tokens_padded = min(numel * block_size, max_num_tokens_padded)
+    sorted_ids = torch.empty((max_num_tokens_padded,), dtype=torch.int32, device=topk_ids.device)
+    expert_ids = torch.empty((_cdiv(max_num_tokens_padded, block_size),), dtype=torch.int32, device=topk_ids.device)
+    num_tokens_post_pad = torch.empty((1,), dtype=torch.int32, device=topk_ids.device)
+    ids = topk_ids if topk_ids.is_contiguous() else topk_ids.contiguous()
+    mode = 0
+    if expert_map is not None:
+        if expert_map.dtype != torch.int32:
+            expert_map = expert_map.to(torch.int32)
+        mode = 1 if ignore_invalid_experts else 2
+    with torch.cuda.device(ids.device):
+        st = _lib.load().lo_moe_align_block_size(
+            _lib.ptr(ids), _lib.dtype_code(ids.dtype), numel, int(num_experts), int(block_size),
+            _lib.ptr(expert_map), mode, _lib.ptr(sorted_ids), sorted_ids.numel(), _lib.ptr(expert_ids),
+            expert_ids.numel(), _lib.ptr(num_tokens_post_pad), _lib.current_stream(ids.device))
+    _lib.check(st, "moe_align_block_size")
+    return sorted_ids, expert_ids, num_tokens_post_pad
+
+
+def moe_sum(input: torch.Tensor, output: torch.Tensor, bias: Optional[torch.Tensor] = None,
+            expert_mask: Optional[torch.Tensor] = None, num_local_tokens: Optional[torch.Tensor] = None,
+            factor: float = 1.0, expect_m: int = -1) -> None:
+    """``output[t] = factor * sum_j input[t, j] (+ bias[t])`` (reference: python/lightop/moe_align_sum.py:12-29).
+
+    fp32 accumulation and one rounding, as the reference kernel
+    (csrc/kernels/moe_align_sum_kernels.cu:604-760).  ``expert_mask`` (bool ``[M, topk]``)
+    skips slots; ``num_local_tokens`` (int32 ``[1]``) limits the tokens written; ``expect_m``
+    is a launch hint of the reference and is ignored.
+    """
+    _lib.require_cuda(input, output, bias, expert_mask, num_local_tokens)
+    if input.dim() != 3:
+        raise RuntimeError("moe_sum input must be [num_tokens, topk, hidden]")
+    M, topk, H = input.shape
+    if tuple(output.shape) != (M, H) or output.dtype != input.dtype:
+        raise RuntimeError("moe_sum output must be [num_tokens, hidden] of the input dtype")
+    if not (input.is_contiguous() and output.is_contiguous()):
+        raise RuntimeError("moe_sum expects contiguous tensors")
+    if bias is not None and (tuple(bias.shape) != (M, H) or bias.dtype != input.dtype or not bias.is_contiguous()):
+        raise RuntimeError("moe_sum bias must be a contiguous [num_tokens, hidden] tensor of the input dtype")
+    if expert_mask is not None:
+        expert_mask = expert_mask.to(torch.bool).contiguous()
+    with torch.cuda.device(input.device):
+        st = _lib.load().lo_moe_sum(_lib.ptr(input), _lib.ptr(output), _lib.ptr(bias), _lib.dtype_code(input.dtype),
+                                    M, topk, H, float(factor), _lib.ptr(expert_mask), _lib.ptr(num_local_tokens),
+                                    _lib.current_stream(input.device))
+    _lib.check(st, "moe_sum")

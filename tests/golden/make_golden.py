@@ -1,0 +1,77 @@
+"""Generate the golden fixtures of tests/golden/ from the reference's own torch functions.
+
+Run where a reference checkout is available (``$LIGHTOP_REF`` or ``/root/reference``):
+    python tests/golden/make_golden.py
+The outputs are produced by the reference code itself (loaded by oracle/ref_extract.py),
+not by the restatement in oracle/moe_block_int8.py; the tests then hold both the oracle
+and the CUDA kernels to these files.  Inputs are not stored: they are regenerated from
+their seeds by lightop_b200.synthetic.
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+from lightop_b200 import synthetic  # noqa: E402
+from oracle import ref_extract  # noqa: E402
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def main() -> None:
+    quant, blockmm = ref_extract.reference_block_functions()
+    align = ref_extract.reference_align_python()
+    moe = ref_extract.reference_composed_moe()
+
+    # --- config 0: the reference-runnable tiny MoE -------------------------------------
+    cfg = synthetic.CONFIGS["c0_tiny"]
+    w1, w2, w1_s, w2_s = synthetic.make_weights(cfg["E"], cfg["H"], cfg["I"], seed=0)
+    x, logits = synthetic.make_activations(cfg["M"], cfg["H"], cfg["E"], seed=1)
+    # routing the way the reference's tests do (test_native_categorized_moe_api.py:188-190,
+    # fuse_moegemm.py:449-450)
+    w, ids = torch.topk(torch.softmax(logits.float(), dim=-1), cfg["topk"])
+    w = w / w.sum(dim=-1, keepdim=True)
+    y = moe(x, w1, w2, w1_s, w2_s, w, ids, cfg["topk"])
+    xq, xs = quant(x, 128)
+    sorted_ids, expert_ids, npost = align(ids.reshape(-1), cfg["E"], 16)
+    # one expert's first GEMM, to pin the block matmul alone
+    e0 = int(ids.reshape(-1)[0])
+    rows = torch.nonzero(ids.reshape(-1) == e0).reshape(-1) // cfg["topk"]
+    h0 = blockmm(xq[rows], w1[e0], xs[rows], w1_s[e0], [128, 128], torch.bfloat16)
+    torch.save(dict(topk_weights=w, topk_ids=ids.to(torch.int32), y=y, xq=xq, xs=xs,
+                    sorted_ids=sorted_ids, expert_ids=expert_ids, num_tokens_post_pad=npost,
+                    gemm1_expert=e0, gemm1_rows=rows, gemm1_out=h0),
+               os.path.join(HERE, "c0_tiny.pt"))
+
+    # --- the reference's own pinned small cases ----------------------------------------
+    # group quant, [3,256] bf16, seed 6, group 128 (test/test_quant_per_token_quant_int8.py:59-72)
+    torch.manual_seed(6)
+    xq6 = torch.randn(3, 256).to(torch.bfloat16)
+    q6, s6 = quant(xq6, 128)
+    # an all-zero group and a saturating group
+    xe = torch.zeros(2, 256, dtype=torch.bfloat16)
+    xe[1, :128] = torch.linspace(-3, 3, 128).to(torch.bfloat16)
+    xe[1, 128:] = 1e-12
+    qe, se = quant(xe, 128)
+    # alignment example of the wrapper's docstring (moe_align_block_size.py:65-78), 1-based ids
+    doc_ids = torch.tensor([[2, 3, 4], [1, 2, 4], [1, 3, 4], [1, 2, 3]])
+    d_sorted, d_eids, d_npost = align(doc_ids.reshape(-1), 5, 4)
+    # a ragged alignment case with empty experts
+    g = torch.Generator().manual_seed(3)
+    rag = torch.randint(0, 16, (37 * 3,), generator=g)
+    rag[rag == 5] = 6
+    r_sorted, r_eids, r_npost = align(rag, 16, 16)
+    torch.save(dict(x6=xq6, q6=q6, s6=s6, xe=xe, qe=qe, se=se,
+                    doc_ids=doc_ids, doc_sorted=d_sorted, doc_expert_ids=d_eids, doc_npost=d_npost,
+                    rag_ids=rag, rag_sorted=r_sorted, rag_expert_ids=r_eids, rag_npost=r_npost),
+               os.path.join(HERE, "small_cases.pt"))
+    print("wrote", os.listdir(HERE))
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,91 @@
+"""CPU tests of the C-ABI boundary: the library loads, exports what the header declares,
+and rejects bad arguments before touching a device."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "lightop_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(lo_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported():
+    from lightop_b200 import _lib
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    names = _declared_symbols()
+    assert len(names) >= 13
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in the header but not exported"
+
+
+def test_binding_covers_header():
+    from lightop_b200 import _lib
+    assert sorted(_lib.PROTOTYPES) == _declared_symbols()
+
+
+def test_version_and_error_string():
+    from lightop_b200 import _lib
+    lib = _lib.load()
+    assert lib.lo_version() == 1
+    assert isinstance(lib.lo_last_error(), bytes)
+
+
+def test_argument_validation_needs_no_device():
+    from lightop_b200 import _lib
+    lib = _lib.load()
+    # null pointers
+    assert lib.lo_group_quant_int8(0, _lib.LO_BF16, 4, 128, 1e-10, 0, 0, 0) == 1
+    assert b"null" in lib.lo_last_error()
+    # zero work is a no-op that succeeds
+    assert lib.lo_group_quant_int8(0, _lib.LO_BF16, 0, 128, 1e-10, 0, 0, 0) == 0
+    assert lib.lo_topk_softmax(0, _lib.LO_F32, 0, 8, 2, 1, 0, 0, _lib.LO_I32, 0, 0) == 0
+    # expert count outside the supported range
+    assert lib.lo_topk_softmax(16, _lib.LO_F32, 4, 4096, 2, 1, 16, 16, _lib.LO_I32, 0, 0) == 1
+    assert lib.lo_moe_sum(16, 16, 0, _lib.LO_BF16, 4, 2, 12, 1.0, 0, 0, 0) == 1   # H not a multiple of 8
+    assert lib.lo_fused_moe_workspace_bytes(32, 8, 8, 2, 256, 512) > 32 * 256
+    with pytest.raises(_lib.LightopError):
+        _lib.check(1, "probe")
+
+
+def test_python_api_refuses_cpu_tensors():
+    from lightop_b200 import moe, quant
+    x = torch.zeros(4, 256, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        quant.per_token_group_quant_int8(x, 128)
+    with pytest.raises(AssertionError):
+        quant.per_token_group_quant_int8(torch.zeros(4, 100, dtype=torch.bfloat16), 128)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        moe.moe_align_block_size(torch.zeros(4, 2, dtype=torch.int32), 16, 8)
+
+
+def test_fused_experts_contract_checks():
+    from lightop_b200 import moe
+    x = torch.zeros(4, 256, dtype=torch.bfloat16)
+    w1 = torch.zeros(2, 512, 256, dtype=torch.int8)
+    w2 = torch.zeros(2, 256, 256, dtype=torch.int8)
+    tw = torch.zeros(4, 2)
+    ti = torch.zeros(4, 2, dtype=torch.int32)
+    with pytest.raises(AssertionError):            # neither int8 nor fp8 requested
+        moe.fused_experts_impl_int8(x, w1, w2, tw, ti, None)
+    with pytest.raises(AssertionError, match="Hidden size"):
+        moe.fused_experts_impl_int8(x[:, :128], w1, w2, tw, ti, None, use_int8_w8a8=True, block_shape=[128, 128])
+    with pytest.raises(NotImplementedError):       # per-channel mode is not this path
+        moe.fused_experts_impl_int8(x, w1, w2, tw, ti, None, use_int8_w8a8=True, per_channel_quant=True)
+    with pytest.raises(ValueError, match="activation"):
+        moe.fused_experts_impl_int8(x, w1, w2, tw, ti, None, use_int8_w8a8=True, block_shape=[128, 128],
+                                    activation="gelu", w1_scale=tw, w2_scale=tw)
+
+
+def test_api_names_present():
+    import lightop_b200
+    for name in ["topk_softmax", "moe_align_block_size", "moe_align_block_size_out", "moe_sum", "moe_gemm_w8a8",
+                 "fused_experts_impl_int8", "ep_scatter", "ep_gather", "ep_build_m_indices"]:
+        assert hasattr(lightop_b200.moe, name)
+    assert hasattr(lightop_b200.quant, "per_token_group_quant_int8")
