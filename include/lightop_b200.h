@@ -121,9 +121,10 @@ int lo_moe_sum(const void *in, void *out, const void *bias, int dtype, int64_t M
  * b_scale [E,N/128,K/128] f32, C [numel_valid, N] bf16, topk_weights flat f32 [numel_valid] or NULL.
  * N and K multiples of 128; block_size <= 128 or a multiple of 128.
  * Blocks whose expert id is negative produce zero rows (int8.py:441-449).
- * workspace: lo_grouped_gemm_workspace_bytes(max_blocks, block_size) bytes of scratch.
+ * workspace: lo_grouped_gemm_workspace_bytes(sorted_capacity, block_size, K) bytes of scratch, 256-byte aligned
+ * (the block table and a copy of the activation rows in sorted order, which the kernel reads by TMA).
  */
-size_t lo_grouped_gemm_workspace_bytes(int64_t sorted_capacity, int block_size);
+size_t lo_grouped_gemm_workspace_bytes(int64_t sorted_capacity, int block_size, int64_t K);
 int lo_moe_grouped_gemm_i8_block(const int8_t *A, const float *a_scale, int64_t rows_a,
                                  const int8_t *B, const float *b_scale, int E, int64_t N, int64_t K,
                                  void *C, const float *topk_weights, int weight_mode,
@@ -150,9 +151,10 @@ int lo_moe_grouped_gemm_i8_block(const int8_t *A, const float *a_scale, int64_t 
 size_t lo_fused_moe_workspace_bytes(int64_t M, int E_local, int global_num_experts, int topk,
                                     int64_t H, int64_t I);
 /* Byte offsets of the intermediates inside that workspace, for inspection and tests (host array out8):
- * [0] header i32 {num_tokens_post_pad, num_chunks}, [1] x_q int8 [M,H], [2] x_s f32 [M,H/128],
- * [3] sorted_ids i32 [cap], [4] chunk table, [5] act_q int8 [cap,I] and [6] act_s f32 [cap,I/128]
- * (both in sorted order), [7] = cap, the number of sorted positions (not a byte offset).
+ * [0] header i32 {num_tokens_post_pad, num_chunks}, [1] x_q int8 [cap,H] and [2] x_s f32 [cap,H/128]
+ * (stage-1 quantisation, one row per sorted position), [3] sorted_ids i32 [cap], [4] chunk table,
+ * [5] act_q int8 [cap,I] and [6] act_s f32 [cap,I/128] (stage-2 quantisation, sorted order),
+ * [7] = cap, the number of sorted positions (not a byte offset).
  * No counterpart in the reference, whose intermediates are torch tensors (int8.py:681-695). */
 int lo_fused_moe_workspace_layout(int64_t M, int E_local, int global_num_experts, int topk,
                                   int64_t H, int64_t I, int64_t *out8);
@@ -164,6 +166,16 @@ int lo_fused_moe_block_int8(const void *x, const int8_t *w1, const int8_t *w2,
                             void *cache3, const void *shared_output, void *out,
                             int apply_router_weight_on_input, float routed_scaling_factor,
                             void *workspace, size_t workspace_bytes, int32_t *status, void *stream);
+
+/*
+ * Per-stage timing of lo_fused_moe_block_int8 for benchmarks: while enabled (per host thread), the
+ * call records CUDA events between its five kernels (align, group quant, gate_up GEMM, down GEMM,
+ * top-k sum); lo_profile_read waits for the last one and returns the five durations in
+ * milliseconds (host array).  No counterpart in the reference, which times with
+ * triton.testing.do_bench around the whole call (test/moe_w8a8/moe_benchmark.py:918-932).
+ */
+int lo_profile_enable(int on);
+int lo_profile_read(float *ms5);
 
 /*
  * Expert-parallel local permutation: copy every (token, slot) whose expert is local into the

@@ -35,7 +35,7 @@ PROTOTYPES = {
     "lo_group_quant_int8": (c_int, [c_void_p, c_int, c_int64, c_int, c_float, c_void_p, c_void_p, c_void_p]),
     "lo_moe_sum": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int64, c_int, c_int64, c_float, c_void_p,
                            c_void_p, c_void_p]),
-    "lo_grouped_gemm_workspace_bytes": (c_size_t, [c_int64, c_int]),
+    "lo_grouped_gemm_workspace_bytes": (c_size_t, [c_int64, c_int, c_int64]),
     "lo_moe_grouped_gemm_i8_block": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int64,
                                              c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p,
                                              c_void_p, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p]),
@@ -45,6 +45,8 @@ PROTOTYPES = {
                                         c_int, c_void_p, c_int, c_int64, c_int, c_int, c_int64, c_int64,
                                         c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_size_t,
                                         c_void_p, c_void_p]),
+    "lo_profile_enable": (c_int, [c_int]),
+    "lo_profile_read": (c_int, [c_void_p]),
     "lo_ep_scatter": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                               c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int64, c_int64, c_int, c_int,
                               c_void_p]),

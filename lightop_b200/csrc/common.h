@@ -65,7 +65,18 @@ struct Chunk {
 int launch_align(const void *topk_ids, int ids_dtype, int64_t numel, int num_experts, int block_size,
                  const int32_t *expert_map, int map_mode, int32_t *sorted_ids, int64_t sorted_capacity,
                  int32_t *expert_ids, int64_t expert_ids_capacity, int32_t *num_tokens_post_pad,
-                 Chunk *chunks, int32_t *num_chunks, int64_t chunk_capacity, cudaStream_t stream);
+                 Chunk *chunks, int32_t *num_chunks, int64_t chunk_capacity, int32_t *inv_pos,
+                 cudaStream_t stream);
+
+// Group quantisation of bf16 rows [M, H] written straight into the expert-sorted layout:
+// the int8 row and its scales of token t go to every position inv_pos[t * topk + j] >= 0.  quant.cu
+int launch_group_quant_scatter(const void *x, int64_t M, int64_t H, int topk, const int32_t *inv_pos, float eps,
+                               int8_t *q_sorted, float *s_sorted, cudaStream_t stream);
+
+// Copy int8 rows and their scales into sorted-position order: row(pos) = sorted_ids[pos] / top_k.  reduce.cu
+int launch_permute_rows(const int8_t *A, const float *a_scale, int64_t rows_a, int64_t K, const int32_t *sorted_ids,
+                        int64_t sorted_capacity, const int32_t *num_tokens_post_pad, int64_t numel_valid, int top_k,
+                        int8_t *A_sorted, float *a_scale_sorted, cudaStream_t stream);
 
 // Chunk table from an existing (expert_ids, num_tokens_post_pad) pair, see routing.cu.
 int launch_chunks_from_blocks(const int32_t *expert_ids, const int32_t *num_tokens_post_pad,
@@ -75,7 +86,7 @@ int launch_chunks_from_blocks(const int32_t *expert_ids, const int32_t *num_toke
 enum GemmMode { GEMM_GATE_UP = 0, GEMM_SINGLE = 1 };
 
 struct GemmArgs {
-  const int8_t *A;          // [rows_a, K] int8
+  const int8_t *A;          // [rows_a, K] int8, rows in sorted-position order (row = position in sorted_ids)
   const float *a_scale;     // [rows_a, K/128]
   int64_t rows_a;
   const int8_t *B;          // [E, n_rows_per_expert, K] int8
@@ -86,7 +97,6 @@ struct GemmArgs {
   int n_tiles;              // 128-row output tiles per item: I/128 (gate_up) or N/128
   const int32_t *sorted_ids;
   int64_t numel_valid;      // sorted ids >= this are padding
-  int a_row_div;            // A row = sorted_id / a_row_div; 0 => A row = position in sorted_ids
   const Chunk *chunks;
   const int32_t *num_chunks;
   // outputs

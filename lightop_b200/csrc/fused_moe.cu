@@ -22,10 +22,11 @@ struct Carver {
 };
 
 struct FusedLayout {
-  int8_t *xq;
-  float *xs;
+  int8_t *xq;           // [sorted_cap, H] quantised activations in sorted-position order
+  float *xs;            // [sorted_cap, H/128]
   int32_t *header;      // [0] num_tokens_post_pad, [1] num_chunks
   int32_t *sorted_ids;
+  int32_t *inv_pos;     // [M*topk] position of every (token, slot), -1 if dropped
   Chunk *chunks;
   int8_t *act_q;
   float *act_s;
@@ -41,9 +42,10 @@ FusedLayout carve_fused(void *ws, int64_t M, int num_experts_for_align, int topk
   L.sorted_cap = numel + (int64_t)num_experts_for_align * (FUSED_ALIGN_BLOCK - 1);
   L.chunk_cap = numel / 128 + num_experts_for_align + 1;
   L.header = c.take<int32_t>(64);
-  L.xq = c.take<int8_t>(M * H);
-  L.xs = c.take<float>(M * (H / 128));
+  L.xq = c.take<int8_t>(L.sorted_cap * H);
+  L.xs = c.take<float>(L.sorted_cap * (H / 128));
   L.sorted_ids = c.take<int32_t>(L.sorted_cap);
+  L.inv_pos = c.take<int32_t>(numel);
   L.chunks = c.take<Chunk>(L.chunk_cap);
   L.act_q = c.take<int8_t>(L.sorted_cap * I);
   L.act_s = c.take<float>(L.sorted_cap * (I / 128));
@@ -51,8 +53,41 @@ FusedLayout carve_fused(void *ws, int64_t M, int num_experts_for_align, int topk
   return L;
 }
 
+// Optional per-stage timing of the fused call (cudaEvents recorded between its five kernels).
+struct StageProfile {
+  bool enabled = false;
+  bool created = false;
+  bool recorded = false;
+  cudaEvent_t ev[6];
+};
+thread_local StageProfile g_prof;
+
+inline void prof_mark(int i, cudaStream_t st) {
+  if (g_prof.enabled && g_prof.created) cudaEventRecord(g_prof.ev[i], st);
+}
+
 }  // namespace
 }  // namespace lo
+
+extern "C" int lo_profile_enable(int on) {
+  using namespace lo;
+  if (on && !g_prof.created) {
+    for (int i = 0; i < 6; ++i) LO_CUDA_OK(cudaEventCreate(&g_prof.ev[i]));
+    g_prof.created = true;
+  }
+  g_prof.enabled = on != 0;
+  g_prof.recorded = false;
+  return LO_OK;
+}
+
+extern "C" int lo_profile_read(float *ms5) {
+  using namespace lo;
+  LO_REQUIRE(ms5 != nullptr, "profile read: null output");
+  LO_REQUIRE(g_prof.created && g_prof.recorded, "profile read: no fused call was recorded on this thread");
+  LO_CUDA_OK(cudaEventSynchronize(g_prof.ev[5]));
+  for (int i = 0; i < 5; ++i) LO_CUDA_OK(cudaEventElapsedTime(&ms5[i], g_prof.ev[i], g_prof.ev[i + 1]));
+  return LO_OK;
+}
 
 extern "C" size_t lo_fused_moe_workspace_bytes(int64_t M, int E_local, int global_num_experts, int topk, int64_t H,
                                                int64_t I) {
@@ -106,20 +141,25 @@ extern "C" int lo_fused_moe_block_int8(const void *x, const int8_t *w1, const in
   const int64_t numel = M * topk;
   int rc;
 
-  // 1. activations -> int8 + per-128 scales (token order)
-  rc = lo_group_quant_int8(x, LO_BF16, M * (H / 128), 128, 1e-10f, L.xq, L.xs, stream);
+  // 1. expert-major stable order, chunk table, position of every (token, slot)
+  prof_mark(0, st);
+  rc = launch_align(topk_ids, ids_dtype, numel, align_E, FUSED_ALIGN_BLOCK, expert_map, expert_map ? 1 : 0,
+                    L.sorted_ids, L.sorted_cap, nullptr, 0, L.header, L.chunks, L.header + 1, L.chunk_cap, L.inv_pos,
+                    st);
   if (rc != LO_OK) return rc;
 
-  // 2. expert-major stable order + chunk table
-  rc = launch_align(topk_ids, ids_dtype, numel, align_E, FUSED_ALIGN_BLOCK, expert_map, expert_map ? 1 : 0,
-                    L.sorted_ids, L.sorted_cap, nullptr, 0, L.header, L.chunks, L.header + 1, L.chunk_cap, st);
+  // 2. activations -> int8 + per-128 scales, written once per routed slot into sorted order so
+  //    that every chunk of the grouped GEMM is a run of consecutive rows (one TMA box)
+  prof_mark(1, st);
+  rc = launch_group_quant_scatter(x, M, H, topk, L.inv_pos, 1e-10f, L.xq, L.xs, st);
   if (rc != LO_OK) return rc;
 
   // 3. gate_up GEMM, SiLU*mul and re-quantisation in the epilogue -> act_q/act_s in sorted order
+  prof_mark(2, st);
   GemmArgs g1{};
-  g1.A = L.xq; g1.a_scale = L.xs; g1.rows_a = M; g1.B = w1; g1.b_scale = w1_scale; g1.E = E_local;
+  g1.A = L.xq; g1.a_scale = L.xs; g1.rows_a = L.sorted_cap; g1.B = w1; g1.b_scale = w1_scale; g1.E = E_local;
   g1.n_rows_per_expert = 2 * I; g1.K = H; g1.n_tiles = (int)(I / 128);
-  g1.sorted_ids = L.sorted_ids; g1.numel_valid = numel; g1.a_row_div = topk;
+  g1.sorted_ids = L.sorted_ids; g1.numel_valid = numel;
   g1.chunks = L.chunks; g1.num_chunks = L.header + 1;
   g1.act_q = L.act_q; g1.act_s = L.act_s; g1.C = nullptr;
   g1.topk_weights = topk_weights;
@@ -130,10 +170,11 @@ extern "C" int lo_fused_moe_block_int8(const void *x, const int8_t *w1, const in
   if (rc != LO_OK) return rc;
 
   // 4. down GEMM, routed weight in the epilogue -> cache3[token, slot, :]
+  prof_mark(3, st);
   GemmArgs g2{};
   g2.A = L.act_q; g2.a_scale = L.act_s; g2.rows_a = L.sorted_cap; g2.B = w2; g2.b_scale = w2_scale; g2.E = E_local;
   g2.n_rows_per_expert = H; g2.K = I; g2.n_tiles = (int)(H / 128);
-  g2.sorted_ids = L.sorted_ids; g2.numel_valid = numel; g2.a_row_div = 0;
+  g2.sorted_ids = L.sorted_ids; g2.numel_valid = numel;
   g2.chunks = L.chunks; g2.num_chunks = L.header + 1;
   g2.C = static_cast<__nv_bfloat16 *>(cache3);
   g2.topk_weights = topk_weights;
@@ -144,16 +185,42 @@ extern "C" int lo_fused_moe_block_int8(const void *x, const int8_t *w1, const in
   if (rc != LO_OK) return rc;
 
   // 5. top-k reduction (slots of non-local experts are skipped, their rows were never written)
-  return launch_moe_sum_masked(static_cast<const __nv_bfloat16 *>(cache3), static_cast<__nv_bfloat16 *>(out),
-                               static_cast<const __nv_bfloat16 *>(shared_output), M, topk, H, routed_scaling_factor,
-                               topk_ids, ids_dtype, expert_map, st);
+  prof_mark(4, st);
+  rc = launch_moe_sum_masked(static_cast<const __nv_bfloat16 *>(cache3), static_cast<__nv_bfloat16 *>(out),
+                             static_cast<const __nv_bfloat16 *>(shared_output), M, topk, H, routed_scaling_factor,
+                             topk_ids, ids_dtype, expert_map, st);
+  prof_mark(5, st);
+  if (g_prof.enabled && g_prof.created) g_prof.recorded = true;
+  return rc;
 }
 
-extern "C" size_t lo_grouped_gemm_workspace_bytes(int64_t sorted_capacity, int block_size) {
-  if (block_size <= 0) return 0;
-  const int64_t blocks = lo::ceil_div(sorted_capacity, block_size);
+namespace lo {
+namespace {
+struct GemmWs {
+  int32_t *num_chunks;
+  Chunk *chunks;
+  int8_t *a_sorted;
+  float *as_sorted;
+  size_t bytes;
+};
+GemmWs carve_gemm(void *ws, int64_t sorted_capacity, int block_size, int64_t K) {
+  GemmWs W;
+  Carver c(ws);
+  const int64_t blocks = ceil_div(sorted_capacity, block_size);
   const int per_block = block_size <= 128 ? 1 : block_size / 128;
-  return (size_t)(lo::ALIGN_BYTES + lo::round_up((blocks * per_block + 1) * (int64_t)sizeof(lo::Chunk), lo::ALIGN_BYTES));
+  W.num_chunks = c.take<int32_t>(64);
+  W.chunks = c.take<Chunk>(blocks * per_block + 1);
+  W.a_sorted = c.take<int8_t>(sorted_capacity * K);
+  W.as_sorted = c.take<float>(sorted_capacity * (K / 128));
+  W.bytes = c.off;
+  return W;
+}
+}  // namespace
+}  // namespace lo
+
+extern "C" size_t lo_grouped_gemm_workspace_bytes(int64_t sorted_capacity, int block_size, int64_t K) {
+  if (block_size <= 0 || sorted_capacity <= 0 || K <= 0) return 0;
+  return lo::carve_gemm(nullptr, sorted_capacity, block_size, K).bytes;
 }
 
 extern "C" int lo_moe_grouped_gemm_i8_block(const int8_t *A, const float *a_scale, int64_t rows_a, const int8_t *B,
@@ -167,21 +234,23 @@ extern "C" int lo_moe_grouped_gemm_i8_block(const int8_t *A, const float *a_scal
              "grouped gemm: null pointer");
   LO_REQUIRE(block_size >= 1 && (block_size <= 128 || block_size % 128 == 0),
              "grouped gemm: block_size %d must be <= 128 or a multiple of 128", block_size);
-  LO_REQUIRE(top_k >= 1 && E >= 1 && rows_a >= 0, "grouped gemm: bad shape");
-  LO_REQUIRE(workspace_bytes >= lo_grouped_gemm_workspace_bytes(sorted_capacity, block_size),
-             "grouped gemm: workspace too small");
+  LO_REQUIRE(top_k >= 1 && E >= 1 && rows_a >= 0 && sorted_capacity >= 1, "grouped gemm: bad shape");
+  LO_REQUIRE(K % 128 == 0 && N % 128 == 0, "grouped gemm: N and K must be multiples of 128");
   LO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & (ALIGN_BYTES - 1)) == 0, "grouped gemm: workspace must be 256-byte aligned");
+  GemmWs W = carve_gemm(workspace, sorted_capacity, block_size, K);
+  LO_REQUIRE(workspace_bytes >= W.bytes, "grouped gemm: workspace of %zu bytes, %zu needed", workspace_bytes, W.bytes);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int32_t *num_chunks = static_cast<int32_t *>(workspace);
-  Chunk *chunks = reinterpret_cast<Chunk *>(static_cast<uint8_t *>(workspace) + ALIGN_BYTES);
   const int64_t max_blocks = ceil_div(sorted_capacity, block_size);
-  int rc = launch_chunks_from_blocks(expert_ids, num_tokens_post_pad, block_size, max_blocks, chunks, num_chunks, st);
+  int rc = launch_chunks_from_blocks(expert_ids, num_tokens_post_pad, block_size, max_blocks, W.chunks, W.num_chunks, st);
+  if (rc != LO_OK) return rc;
+  rc = launch_permute_rows(A, a_scale, rows_a, K, sorted_ids, sorted_capacity, num_tokens_post_pad, numel_valid, top_k,
+                           W.a_sorted, W.as_sorted, st);
   if (rc != LO_OK) return rc;
   GemmArgs g{};
-  g.A = A; g.a_scale = a_scale; g.rows_a = rows_a; g.B = B; g.b_scale = b_scale; g.E = E;
+  g.A = W.a_sorted; g.a_scale = W.as_sorted; g.rows_a = sorted_capacity; g.B = B; g.b_scale = b_scale; g.E = E;
   g.n_rows_per_expert = N; g.K = K; g.n_tiles = (int)(N / 128);
-  g.sorted_ids = sorted_ids; g.numel_valid = numel_valid; g.a_row_div = top_k;
-  g.chunks = chunks; g.num_chunks = num_chunks;
+  g.sorted_ids = sorted_ids; g.numel_valid = numel_valid;
+  g.chunks = W.chunks; g.num_chunks = W.num_chunks;
   g.C = static_cast<__nv_bfloat16 *>(C);
   g.topk_weights = topk_weights; g.weight_mode = weight_mode; g.act_eps = 0.f; g.status = nullptr;
   return launch_grouped_gemm(GEMM_SINGLE, g, st);

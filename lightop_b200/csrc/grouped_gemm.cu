@@ -15,14 +15,16 @@
 // items round-robin.
 //
 // Warp roles in a CTA of 12 warps (3 warpgroups):
-//   warp 0      : TMA producer for the weight tiles (one elected lane)
+//   warp 0      : TMA producer (one elected lane): weight tiles and the chunk's token rows.
+//                 Token rows are read from an expert-sorted copy of the activations, so a
+//                 chunk is a run of consecutive rows and one tiled TMA load fetches it.
 //   warp 1      : MMA issuer (one elected lane); owns the tensor-memory allocation
-//   warps 2-3   : gather producers: token rows are fetched with 16-byte cp.async
-//                 by row index into the 128B-swizzled operand layout, the token
-//                 scales of the K block are multiplied with the weight-block
-//                 scale(s) into a per-stage table
-//   warps 4-11  : promotion / epilogue: tcgen05.ld of the int32 partial, convert,
-//                 multiply by the scale product, add into fp32 registers
+//   warps 2-3   : scale producers: the token scales of the K block (prefetched four K
+//                 blocks ahead) times the weight-block scale(s) -> per-step table in
+//                 shared memory
+//   warps 4-11  : promotion / epilogue: tcgen05.ld of the int32 partial, exact
+//                 int->float conversion by the 2^23+2^22 offset trick, multiply by the
+//                 scale product, add into fp32 registers with packed f32x2 operations
 //                 (mul and add kept separate: same rounding sequence as the
 //                 reference's torch model), then the fused epilogue.
 // Pipelines: STAGES shared-memory stages (full/empty mbarriers) between the
@@ -46,13 +48,21 @@ namespace {
 constexpr int TILE_N = 128;      // weight rows per accumulator (MMA M)
 constexpr int TILE_K = 128;      // int8 elements (= bytes) per K block
 constexpr int T_MAX = 128;       // tokens per chunk (MMA N upper bound)
-constexpr int KB_MAX = 128;      // K blocks supported (K <= 16384)
 constexpr int NUM_THREADS = 384;
-constexpr int GATHER_THREADS = 64;
+constexpr int SCALE_THREADS = 64;
 constexpr int EPI_WARPS = 8;
 constexpr int W_TILE_BYTES = TILE_N * TILE_K;   // 16 KiB
 constexpr int A_TILE_BYTES = T_MAX * TILE_K;    // 16 KiB
 constexpr uint32_t TMEM_COLS = 512;
+// Ring of scale-product tables.  A slot written for K-block step i was last read at step
+// i - SC_SLOTS; the producer of step i has seen the MMAs of step i - STAGES complete, which were
+// issued after the promotion of step i - STAGES - 2 finished, so SC_SLOTS >= STAGES + 2 is enough.
+constexpr int SC_SLOTS = 8;
+// 2^23 + 2^22: adding it to an int32 of magnitude < 2^22 and reading the bits as fp32 gives
+// 12582912 + value exactly, so (that - 12582912.0f) is the exact int->float conversion
+// (|128-long int8 dot| <= 128 * 127 * 127 < 2^21).
+constexpr uint32_t MAGIC_I = 0x4B400000u;
+constexpr float MAGIC_F = 12582912.0f;
 
 template <int MODE> struct Cfg;
 template <> struct Cfg<GEMM_GATE_UP> {
@@ -70,16 +80,12 @@ template <int MODE> struct Smem {
   // operand tiles first: each is a multiple of 1024 bytes, base is 1024-aligned
   uint8_t w[STAGES][NUM_W][W_TILE_BYTES];
   uint8_t a[STAGES][A_TILE_BYTES];
-  float a_s[STAGES][T_MAX];                // raw token scales of the K block (cp.async landing zone)
-  float sc[STAGES][NUM_W][T_MAX];          // token scale x weight-block scale
-  float bs[2][NUM_W][KB_MAX];              // weight-block scales of the item (double-buffered by item parity)
-  int32_t a_rows[T_MAX];                   // A row of every token of the chunk, -1 = zero fill
+  float sc[SC_SLOTS][NUM_W][T_MAX];        // token scale x weight-block scale, ring indexed by the K-block counter
   uint32_t amax[2][4][T_MAX / 2];          // gate_up epilogue: |act| maxima per (half, lane quarter, token)
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
-  uint64_t gsync;                          // rendezvous of the 64 gather threads
   uint64_t esync[2];                       // rendezvous of the 128 epilogue threads of a token half
   uint32_t tmem_base;
   volatile int abort_flag;
@@ -138,7 +144,6 @@ __device__ __forceinline__ bool mbar_wait(S &sm, uint64_t *bar, uint32_t parity,
 }
 
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
@@ -161,20 +166,6 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, i
       " [%0], [%1, {%2, %3}], [%4], %5;"
       ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
       : "memory");
-}
-
-// 16-byte cp.async with zero fill when src_bytes == 0.
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, uint32_t src_bytes, uint64_t policy) {
-  asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2, %3;" ::"r"(dst), "l"(src), "r"(src_bytes),
-               "l"(policy)
-               : "memory");
-}
-__device__ __forceinline__ void cp_async_4(uint32_t dst, const void *src, uint32_t src_bytes) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // Shared-memory matrix descriptor: K-major operand, rows of 128 bytes, 128-byte
@@ -212,35 +203,53 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-// 32 consecutive tensor-memory columns of this thread's lane.
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+// 16 consecutive tensor-memory columns of this thread's lane.
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// Packed fp32 pair arithmetic (two IEEE round-to-nearest operations per instruction).
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+// Rounded product as ONE instruction: fma(a, b, -0.0) == round(a * b).  A separate mul.rn.f32x2
+// followed by add.rn.f32x2 was observed to be contracted into a fused multiply-add by the
+// assembler (results differed from the scalar mul-then-add sequence in the last bit); an fma is
+// never merged with a following add.  `negzero2` comes from a kernel parameter so that the
+// addend is not a compile-time constant.
+__device__ __forceinline__ uint64_t mul2_rounded(uint64_t a, uint64_t b, uint64_t negzero2) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(negzero2));
+  return r;
+}
+
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 
 struct KParams {
-  const int8_t *A;
-  const float *a_scale;
-  int64_t rows_a;
+  const float *a_scale;     // [positions, KB]
   const float *b_scale;
   int64_t n_rows_per_expert;
-  int64_t K;
   int KB;
   int n_tiles;
   const int32_t *sorted_ids;
   int64_t numel_valid;
-  int a_row_div;
   const Chunk *chunks;
   const int32_t *num_chunks;
   int8_t *act_q;
@@ -250,11 +259,19 @@ struct KParams {
   int weight_mode;
   float act_eps;
   int32_t *status;
+  float neg_zero;           // -0.0f, see mul2_rounded
 };
+
+// Four tensor maps of the sorted activation matrix, box heights 16 / 32 / 64 / 128 rows.
+struct AMaps {
+  CUtensorMap m[4];
+};
+
+__device__ __forceinline__ int a_map_index(int T) { return T <= 16 ? 0 : (T <= 32 ? 1 : (T <= 64 ? 2 : 3)); }
 
 template <int MODE>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const KParams p) {
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ AMaps a_maps, const KParams p) {
   using SM = Smem<MODE>;
   constexpr int STAGES = SM::STAGES;
   constexpr int NUM_W = SM::NUM_W;
@@ -268,15 +285,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const KParams p) 
   // ------------------------------ set-up -----------------------------------
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&sm.full[s], GATHER_THREADS + 1);
-      mbar_init(&sm.empty[s], 1 + EPI_WARPS);
+      mbar_init(&sm.full[s], 1 + SCALE_THREADS / 32);   // TMA thread (arrive.expect_tx) + one arrive per scale warp
+      mbar_init(&sm.empty[s], 1);                        // tcgen05.commit of the MMA thread
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&sm.tmem_full[b], 1);
       mbar_init(&sm.tmem_empty[b], EPI_WARPS);
       mbar_init(&sm.esync[b], 128);
     }
-    mbar_init(&sm.gsync, GATHER_THREADS);
     sm.abort_flag = 0;
     fence_barrier_init();
   }
@@ -294,27 +310,35 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const KParams p) 
   const int64_t num_items = (int64_t)num_chunks * p.n_tiles;
   const int KB = p.KB;
 
+  // Register re-partitioning.  The CTA owns NUM_THREADS * 168 = 64512 registers (launch bound);
+  // setmaxnreg.inc blocks (unboundedly) until the pool has room, so the producers' decrease must
+  // free at least what the two epilogue warpgroups take: 128 * 72 + 256 * 216 = 64512.
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     if (warp == 0) {
-      // ===================== TMA producer: weight tiles ======================
+      // ============ TMA producer: weight tiles + the chunk's token rows ============
       if (lane == 0) {
-        const uint64_t pol = policy_evict_first();
+        const uint64_t pol_w = policy_evict_first();
+        const uint64_t pol_a = policy_evict_last();
         uint32_t it = 0;
         bool ok = true;
         for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
           const Chunk ch = p.chunks[item / p.n_tiles];
           const int nt = (int)(item % p.n_tiles);
           if (ch.expert < 0) continue;
+          const int T = (ch.rows + 15) & ~15;
+          const int mi = a_map_index(T);
+          const uint32_t a_bytes = (16u << mi) * TILE_K;
           const int32_t row_g = (int32_t)(ch.expert * p.n_rows_per_expert + (int64_t)nt * TILE_N);
           for (int kb = 0; kb < KB; ++kb, ++it) {
             const int s = it % STAGES;
             const uint32_t ph = (it / STAGES) & 1u;
             if (!mbar_wait(sm, &sm.empty[s], ph ^ 1u, p.status, 1)) { ok = false; break; }
-            mbar_arrive_expect_tx(&sm.full[s], NUM_W * W_TILE_BYTES);
-            tma_load_2d(sm.w[s][0], &w_map, kb * TILE_K, row_g, &sm.full[s], pol);
+            mbar_arrive_expect_tx(&sm.full[s], NUM_W * W_TILE_BYTES + a_bytes);
+            tma_load_2d(sm.w[s][0], &w_map, kb * TILE_K, row_g, &sm.full[s], pol_w);
             if (NUM_W == 2)
-              tma_load_2d(sm.w[s][NUM_W - 1], &w_map, kb * TILE_K, row_g + p.n_tiles * TILE_N, &sm.full[s], pol);
+              tma_load_2d(sm.w[s][NUM_W - 1], &w_map, kb * TILE_K, row_g + p.n_tiles * TILE_N, &sm.full[s], pol_w);
+            tma_load_2d(sm.a[s], &a_maps.m[mi], kb * TILE_K, ch.row0, &sm.full[s], pol_a);
           }
         }
       }
@@ -351,97 +375,83 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const KParams p) 
         }
       }
     } else {
-      // ======================= gather producers (2 warps) ====================
+      // ========================= scale producers (2 warps) ====================
+      // Thread g owns tokens g and g + 64 of the chunk.  Token scales and weight-block scales are
+      // read four K blocks at a time and one group ahead, so the loop never waits on memory.
       const int g = tid - 64;            // 0..63
-      const int c16 = g & 7;             // 16-byte piece of the 128-byte row
-      const int r8 = g >> 3;             // row inside a pass of 8 rows
-      const uint64_t pol = policy_evict_last();
       uint32_t it = 0;
-      uint32_t item_par = 0;
-      uint32_t gph = 0;
       bool ok = true;
-      // lagged completion: stage issued at step i is published at step i + LAG
-      constexpr int LAG = 2;
-      int pend_s[LAG];
-      int pend_kb[LAG];
-      uint32_t pend_par[LAG];
-      int pend_T[LAG];
-      int npend = 0;
-      auto publish = [&](int s, int kb, uint32_t par, int T) {
-        // own cp.async data of stage s has landed: build the scale-product table
-        for (int t = g; t < T; t += GATHER_THREADS) {
-          const float as = sm.a_s[s][t];
-#pragma unroll
-          for (int w = 0; w < NUM_W; ++w) sm.sc[s][w][t] = __fmul_rn(as, sm.bs[par][w][kb]);
-        }
-        fence_proxy_async();
-        mbar_arrive(&sm.full[s]);
-      };
+      const bool vec4 = (KB & 3) == 0;
+      const int64_t nblk = p.n_rows_per_expert / TILE_N;
       for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
         const Chunk ch = p.chunks[item / p.n_tiles];
         const int nt = (int)(item % p.n_tiles);
         if (ch.expert < 0) continue;
         const int T = (ch.rows + 15) & ~15;
-        // all gather threads are done issuing the previous item: safe to rewrite a_rows
-        mbar_arrive(&sm.gsync);
-        if (!mbar_wait(sm, &sm.gsync, gph, p.status, 7)) { ok = false; break; }
-        gph ^= 1u;
-        for (int t = g; t < T_MAX; t += GATHER_THREADS) {
-          int32_t r = -1;
-          if (t < ch.rows) {
-            const int32_t sid = p.sorted_ids[ch.row0 + t];
-            if (sid >= 0 && sid < p.numel_valid) r = p.a_row_div > 0 ? sid / p.a_row_div : ch.row0 + t;
-            if (r >= p.rows_a) r = -1;
-          }
-          sm.a_rows[t] = r;
+        const float *as_ptr[2];
+        bool live[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int t = g + u * SCALE_THREADS;
+          live[u] = t < ch.rows;
+          as_ptr[u] = p.a_scale + (int64_t)(ch.row0 + (live[u] ? t : 0)) * KB;
         }
-        {
-          const int64_t nblk = p.n_rows_per_expert / TILE_N;
-          const float *bsrc = p.b_scale + ((int64_t)ch.expert * nblk + nt) * KB;
-          for (int kb = g; kb < KB; kb += GATHER_THREADS) {
-            sm.bs[item_par][0][kb] = bsrc[kb];
-            if (NUM_W == 2) sm.bs[item_par][NUM_W - 1][kb] = bsrc[(int64_t)p.n_tiles * KB + kb];
-          }
+        const float *bs_ptr[NUM_W];
+#pragma unroll
+        for (int w = 0; w < NUM_W; ++w)
+          bs_ptr[w] = p.b_scale + ((int64_t)ch.expert * nblk + nt + (int64_t)w * p.n_tiles) * KB;
+        float4 cur_a[2], nxt_a[2], cur_b[NUM_W], nxt_b[NUM_W];
+        const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (vec4) {
+#pragma unroll
+          for (int u = 0; u < 2; ++u) nxt_a[u] = live[u] ? __ldg(reinterpret_cast<const float4 *>(as_ptr[u])) : zero4;
+#pragma unroll
+          for (int w = 0; w < NUM_W; ++w) nxt_b[w] = __ldg(reinterpret_cast<const float4 *>(bs_ptr[w]));
         }
-        mbar_arrive(&sm.gsync);
-        if (!mbar_wait(sm, &sm.gsync, gph, p.status, 8)) { ok = false; break; }
-        gph ^= 1u;
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
-          if (!mbar_wait(sm, &sm.empty[s], ph ^ 1u, p.status, 4)) { ok = false; break; }
-          const uint32_t a_base = smem_u32(sm.a[s]);
-          for (int r = r8; r < T; r += 8) {
-            const int32_t row = sm.a_rows[r];
-            const int8_t *src = p.A + (int64_t)(row < 0 ? 0 : row) * p.K + (int64_t)kb * TILE_K + c16 * 16;
-            const uint32_t dst = a_base + (uint32_t)r * 128u + (uint32_t)((c16 ^ (r & 7)) << 4);
-            cp_async_16(dst, src, row < 0 ? 0u : 16u, pol);
-          }
-          for (int t = g; t < T; t += GATHER_THREADS) {
-            const int32_t row = sm.a_rows[t];
-            const float *src = p.a_scale + (int64_t)(row < 0 ? 0 : row) * KB + kb;
-            cp_async_4(smem_u32(&sm.a_s[s][t]), src, row < 0 ? 0u : 4u);
-          }
-          cp_async_commit();
-          if (npend == LAG) {
-            cp_async_wait<LAG>();
-            publish(pend_s[0], pend_kb[0], pend_par[0], pend_T[0]);
+          float as_now[2], bs_now[NUM_W];
+          if (vec4) {
+            if ((kb & 3) == 0) {
 #pragma unroll
-            for (int i = 0; i + 1 < LAG; ++i) {
-              pend_s[i] = pend_s[i + 1]; pend_kb[i] = pend_kb[i + 1];
-              pend_par[i] = pend_par[i + 1]; pend_T[i] = pend_T[i + 1];
+              for (int u = 0; u < 2; ++u) {
+                cur_a[u] = nxt_a[u];
+                if (kb + 4 < KB && live[u]) nxt_a[u] = __ldg(reinterpret_cast<const float4 *>(as_ptr[u] + kb + 4));
+              }
+#pragma unroll
+              for (int w = 0; w < NUM_W; ++w) {
+                cur_b[w] = nxt_b[w];
+                if (kb + 4 < KB) nxt_b[w] = __ldg(reinterpret_cast<const float4 *>(bs_ptr[w] + kb + 4));
+              }
             }
-            --npend;
+            const int sel = kb & 3;
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+              as_now[u] = sel == 0 ? cur_a[u].x : (sel == 1 ? cur_a[u].y : (sel == 2 ? cur_a[u].z : cur_a[u].w));
+#pragma unroll
+            for (int w = 0; w < NUM_W; ++w)
+              bs_now[w] = sel == 0 ? cur_b[w].x : (sel == 1 ? cur_b[w].y : (sel == 2 ? cur_b[w].z : cur_b[w].w));
+          } else {
+#pragma unroll
+            for (int u = 0; u < 2; ++u) as_now[u] = live[u] ? __ldg(as_ptr[u] + kb) : 0.f;
+#pragma unroll
+            for (int w = 0; w < NUM_W; ++w) bs_now[w] = __ldg(bs_ptr[w] + kb);
           }
-          pend_s[npend] = s; pend_kb[npend] = kb; pend_par[npend] = item_par; pend_T[npend] = T;
-          ++npend;
+          // the slot of this step is free once the stage is (see SC_SLOTS)
+          if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.empty[s], ph ^ 1u, p.status, 4))) { ok = false; break; }
+          const int slot = it % SC_SLOTS;
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            const int t = g + u * SCALE_THREADS;
+            if (t < T) {
+#pragma unroll
+              for (int w = 0; w < NUM_W; ++w) sm.sc[slot][w][t] = __fmul_rn(as_now[u], bs_now[w]);
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sm.full[s]);
         }
-        item_par ^= 1u;
-      }
-      // drain
-      cp_async_wait<0>();
-      if (ok) {
-        for (int i = 0; i < npend; ++i) publish(pend_s[i], pend_kb[i], pend_par[i], pend_T[i]);
       }
     }
   } else {
@@ -451,6 +461,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const KParams p) 
     const int q = warp & 3;              // lane quarter of tensor memory this warp may read
     const int h = ew >> 2;               // token half: tokens [64h, 64h + 64)
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
+    const uint64_t neg_magic2 = pack2(-MAGIC_F, -MAGIC_F);
+    const uint64_t negzero2 = pack2(p.neg_zero, p.neg_zero);
     uint32_t it = 0, ab = 0, eph = 0;
     bool ok = true;
     for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
@@ -472,79 +484,104 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const KParams p) 
       }
       const int T = (ch.rows + 15) & ~15;
       const int my_cols = T - h * 64;          // tokens of this half (may be <= 0)
-      float acc[NUM_W][64];
+      uint64_t acc2[NUM_W][32];                // fp32 running sums, two tokens per 64-bit register
 #pragma unroll
       for (int w = 0; w < NUM_W; ++w)
 #pragma unroll
-        for (int j = 0; j < 64; ++j) acc[w][j] = 0.f;
+        for (int j = 0; j < 32; ++j) acc2[w][j] = 0ull;
 
       for (int kb = 0; kb < KB; ++kb, ++it, ++ab) {
-        const int s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1u;
+        const int slot = it % SC_SLOTS;
         const uint32_t b = ab & 1u;
         const uint32_t aph = (ab >> 1) & 1u;
-        if (!mbar_wait(sm, &sm.tmem_full[b], aph, p.status, 5)) { ok = false; break; }
-        if (!mbar_wait(sm, &sm.full[s], ph, p.status, 6)) { ok = false; break; }
+        // The scale products of this step were written to shared memory before the stage's full
+        // barrier completed, which the MMA thread observed before it issued the MMAs whose
+        // completion this wait observes.  Warp-uniform outcome: the loads below are warp-collective.
+        if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.tmem_full[b], aph, p.status, 5))) { ok = false; break; }
         tc_fence_after();
+        // NUM_W * 4 pieces of 16 columns, software-pipelined: the load of piece i+1 is in flight
+        // while piece i is promoted.
+        constexpr int PIECES = NUM_W * 4;
+        const uint32_t t_base = tmem_base + lane_off + b * 256u + (uint32_t)(h * 64);
+        uint32_t raw[2][16];
+        if (my_cols > 0) tmem_ld16(t_base, raw[0]);
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          if (c * 32 < my_cols) {
+        for (int pc = 0; pc < PIECES; ++pc) {
+          const int c = pc / NUM_W;          // 16-column piece of this half
+          const int w = pc % NUM_W;          // gate / up
+          if (c * 16 < my_cols) {
+            tmem_ld_wait();
+            if (pc + 1 < PIECES) {
+              const int cn = (pc + 1) / NUM_W, wn = (pc + 1) % NUM_W;
+              if (cn * 16 < my_cols) tmem_ld16(t_base + (uint32_t)wn * T_MAX + (uint32_t)(cn * 16), raw[(pc + 1) & 1]);
+            }
+            const ulonglong2 *scv = reinterpret_cast<const ulonglong2 *>(&sm.sc[slot][w][h * 64 + c * 16]);
 #pragma unroll
-            for (int w = 0; w < NUM_W; ++w) {
-              uint32_t raw[32];
-              tmem_ld32(tmem_base + lane_off + b * 256u + (uint32_t)w * T_MAX + (uint32_t)(h * 64 + c * 32), raw);
-              tmem_ld_wait();
-              const float4 *scv = reinterpret_cast<const float4 *>(&sm.sc[s][w][h * 64 + c * 32]);
-#pragma unroll
-              for (int j4 = 0; j4 < 8; ++j4) {
-                const float4 sc = scv[j4];
-                float *a = &acc[w][c * 32 + j4 * 4];
-                a[0] = __fadd_rn(a[0], __fmul_rn(__int2float_rn((int)raw[j4 * 4 + 0]), sc.x));
-                a[1] = __fadd_rn(a[1], __fmul_rn(__int2float_rn((int)raw[j4 * 4 + 1]), sc.y));
-                a[2] = __fadd_rn(a[2], __fmul_rn(__int2float_rn((int)raw[j4 * 4 + 2]), sc.z));
-                a[3] = __fadd_rn(a[3], __fmul_rn(__int2float_rn((int)raw[j4 * 4 + 3]), sc.w));
-              }
+            for (int j4 = 0; j4 < 4; ++j4) {
+              const ulonglong2 sc = scv[j4];     // scale products of four tokens
+              const uint32_t *r = &raw[pc & 1][j4 * 4];
+              // exact int -> float: bits(int + MAGIC_I) read as fp32, minus MAGIC_F
+              const uint64_t f01 = add2(pack2(__uint_as_float(r[0] + MAGIC_I), __uint_as_float(r[1] + MAGIC_I)), neg_magic2);
+              const uint64_t f23 = add2(pack2(__uint_as_float(r[2] + MAGIC_I), __uint_as_float(r[3] + MAGIC_I)), neg_magic2);
+              uint64_t *a = &acc2[w][c * 8 + j4 * 2];
+              a[0] = add2(a[0], mul2_rounded(f01, sc.x, negzero2));
+              a[1] = add2(a[1], mul2_rounded(f23, sc.y, negzero2));
             }
           }
         }
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(&sm.tmem_empty[b]);
-          mbar_arrive(&sm.empty[s]);
-        }
+        if (lane == 0) mbar_arrive(&sm.tmem_empty[b]);
       }
       if (!ok) break;
 
       // ------------------------------ epilogue -------------------------------
+      // row ids and routed weights of this half's 64 tokens: two per lane, broadcast by shuffle
+      int32_t sid_r[2];
+      float wgt_r[2];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int t = h * 64 + u * 32 + lane;
+        int32_t sid = -1;
+        if (t < ch.rows) {
+          sid = p.sorted_ids[ch.row0 + t];
+          if (sid < 0 || sid >= p.numel_valid) sid = -1;
+        }
+        sid_r[u] = sid;
+        wgt_r[u] = (sid >= 0 && p.weight_mode != LO_WEIGHT_NONE) ? p.topk_weights[sid] : 0.f;
+      }
       if (MODE == GEMM_GATE_UP) {
         const int64_t I = (int64_t)p.n_tiles * TILE_N;
-        // act = bf16(bf16(silu(bf16(gate))) * bf16(up)); kept in acc[0]
+        float act[64];
+        // act = bf16(bf16(silu(bf16(gate))) * bf16(up))
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {
-          if (j < my_cols) {
-            float gte = acc[0][j], up = acc[NUM_W - 1][j];
-            if (p.weight_mode == LO_WEIGHT_FP32) {
-              const int t = h * 64 + j;
-              float wgt = 0.f;
-              if (t < ch.rows) {
-                const int32_t sid = p.sorted_ids[ch.row0 + t];
-                if (sid >= 0 && sid < p.numel_valid) wgt = p.topk_weights[sid];
+        for (int j2 = 0; j2 < 32; ++j2) {
+          float gv[2], uv[2];
+          unpack2(acc2[0][j2], gv[0], gv[1]);
+          unpack2(acc2[NUM_W - 1][j2], uv[0], uv[1]);
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int j = j2 * 2 + e;
+            float a = 0.f;
+            if (j < my_cols) {
+              float gte = gv[e], up = uv[e];
+              if (p.weight_mode == LO_WEIGHT_FP32) {
+                const float wgt = __shfl_sync(0xffffffffu, wgt_r[j >> 5], j & 31);
+                gte *= wgt;
+                up *= wgt;
               }
-              gte *= wgt;
-              up *= wgt;
+              gte = bf16_round(gte);
+              up = bf16_round(up);
+              const float sl = bf16_round(gte / (1.0f + expf(-gte)));
+              a = bf16_round(sl * up);
+              const uint32_t m = __reduce_max_sync(0xffffffffu, __float_as_uint(a) & 0x7fffffffu);
+              if (lane == 0) sm.amax[h][q][j] = m;
             }
-            gte = bf16_round(gte);
-            up = bf16_round(up);
-            const float sl = bf16_round(gte / (1.0f + expf(-gte)));
-            const float act = bf16_round(sl * up);
-            acc[0][j] = act;
-            const uint32_t m = __reduce_max_sync(0xffffffffu, __float_as_uint(act) & 0x7fffffffu);
-            if (lane == 0) sm.amax[h][q][j] = m;
+            act[j] = a;
           }
         }
         mbar_arrive(&sm.esync[h]);
-        if (!mbar_wait(sm, &sm.esync[h], eph, p.status, 9)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.esync[h], eph, p.status, 9))) { ok = false; break; }
         eph ^= 1u;
 #pragma unroll
         for (int j = 0; j < 64; ++j) {
@@ -553,7 +590,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const KParams p) 
             const uint32_t m = max(max(sm.amax[h][0][j], sm.amax[h][1][j]), max(sm.amax[h][2][j], sm.amax[h][3][j]));
             const float amax = fmaxf(__uint_as_float(m), p.act_eps);
             const float scale = __fdiv_rn(amax, 127.0f);
-            float r = __fdiv_rn(acc[0][j], scale);
+            float r = __fdiv_rn(act[j], scale);
             r = fminf(fmaxf(r, -128.0f), 127.0f);
             const int64_t pos = (int64_t)ch.row0 + t;
             p.act_q[pos * I + (int64_t)nt * TILE_N + n_local] = (int8_t)__float2int_rz(r);
@@ -562,20 +599,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const KParams p) 
         }
         // the amax table is reused by the next item
         mbar_arrive(&sm.esync[h]);
-        if (!mbar_wait(sm, &sm.esync[h], eph, p.status, 10)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.esync[h], eph, p.status, 10))) { ok = false; break; }
         eph ^= 1u;
       } else {
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {
-          const int t = h * 64 + j;
-          if (t < ch.rows) {
-            const int32_t sid = p.sorted_ids[ch.row0 + t];
-            if (sid >= 0 && sid < p.numel_valid) {
-              float v = acc[0][j];
+        for (int j2 = 0; j2 < 32; ++j2) {
+          float v2[2];
+          unpack2(acc2[0][j2], v2[0], v2[1]);
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int j = j2 * 2 + e;
+            const int32_t sid = __shfl_sync(0xffffffffu, sid_r[j >> 5], j & 31);
+            const float wgt = __shfl_sync(0xffffffffu, wgt_r[j >> 5], j & 31);
+            if (sid >= 0) {
+              float v = v2[e];
               if (p.weight_mode == LO_WEIGHT_FP32) {
-                v = v * p.topk_weights[sid];
+                v = v * wgt;
               } else if (p.weight_mode == LO_WEIGHT_BF16_PRODUCT) {
-                v = bf16_round(v) * bf16_round(p.topk_weights[sid]);
+                v = bf16_round(v) * bf16_round(wgt);
               }
               p.C[(int64_t)sid * p.n_rows_per_expert + (int64_t)nt * TILE_N + n_local] = __float2bfloat16_rn(v);
             }
@@ -615,12 +656,13 @@ PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
   return fn;
 }
 
-// Tensor map of a [rows, K] int8 matrix, box 128 rows x 128 bytes, 128-byte swizzle.
-int make_weight_map(CUtensorMap *map, const int8_t *B, int64_t rows, int64_t K) {
+// Tensor map of a [rows, K] int8 matrix, box `box_rows` x 128 bytes, 128-byte swizzle.
+// Encoded maps are cached by (base, rows, K, box_rows).
+int make_tile_map(CUtensorMap *map, const int8_t *base, int64_t rows, int64_t K, int box_rows) {
   static std::mutex mu;
-  static std::map<std::tuple<const void *, int64_t, int64_t>, CUtensorMap> cache;
+  static std::map<std::tuple<const void *, int64_t, int64_t, int>, CUtensorMap> cache;
   std::lock_guard<std::mutex> lock(mu);
-  auto key = std::make_tuple((const void *)B, rows, K);
+  auto key = std::make_tuple((const void *)base, rows, K, box_rows);
   auto itc = cache.find(key);
   if (itc != cache.end()) {
     *map = itc->second;
@@ -630,13 +672,13 @@ int make_weight_map(CUtensorMap *map, const int8_t *B, int64_t rows, int64_t K) 
   if (!encode) return fail(LO_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the CUDA driver");
   cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)K};
-  cuuint32_t box[2] = {TILE_K, TILE_N};
+  cuuint32_t box[2] = {TILE_K, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t *>(B), dims, strides, box, estr,
+  CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t *>(base), dims, strides, box, estr,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(LO_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
-  if (cache.size() > 256) cache.clear();
+  if (cache.size() > 1024) cache.clear();
   cache[key] = *map;
   return LO_OK;
 }
@@ -650,18 +692,23 @@ int launch_mode(const GemmArgs &a, cudaStream_t stream) {
     LO_CUDA_OK(cudaFuncSetAttribute(grouped_gemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
     configured = true;
   }
-  CUtensorMap map;
-  int rc = make_weight_map(&map, a.B, (int64_t)a.E * a.n_rows_per_expert, a.K);
+  CUtensorMap wmap;
+  int rc = make_tile_map(&wmap, a.B, (int64_t)a.E * a.n_rows_per_expert, a.K, TILE_N);
   if (rc != LO_OK) return rc;
+  AMaps amaps;
+  for (int i = 0; i < 4; ++i) {
+    rc = make_tile_map(&amaps.m[i], a.A, a.rows_a, a.K, 16 << i);
+    if (rc != LO_OK) return rc;
+  }
   KParams p;
-  p.A = a.A; p.a_scale = a.a_scale; p.rows_a = a.rows_a; p.b_scale = a.b_scale;
-  p.n_rows_per_expert = a.n_rows_per_expert; p.K = a.K; p.KB = (int)(a.K / TILE_K); p.n_tiles = a.n_tiles;
-  p.sorted_ids = a.sorted_ids; p.numel_valid = a.numel_valid; p.a_row_div = a.a_row_div;
+  p.a_scale = a.a_scale; p.b_scale = a.b_scale;
+  p.n_rows_per_expert = a.n_rows_per_expert; p.KB = (int)(a.K / TILE_K); p.n_tiles = a.n_tiles;
+  p.sorted_ids = a.sorted_ids; p.numel_valid = a.numel_valid;
   p.chunks = a.chunks; p.num_chunks = a.num_chunks; p.act_q = a.act_q; p.act_s = a.act_s; p.C = a.C;
-  p.topk_weights = a.topk_weights; p.weight_mode = a.weight_mode; p.act_eps = a.act_eps; p.status = a.status;
+  p.topk_weights = a.topk_weights; p.weight_mode = a.weight_mode; p.act_eps = a.act_eps; p.status = a.status; p.neg_zero = -0.0f;
   const int grid = sm_count();
   if (grid <= 0) return fail(LO_ERR_CUDA, "no CUDA device");
-  grouped_gemm_kernel<MODE><<<grid, NUM_THREADS, smem_bytes, stream>>>(map, p);
+  grouped_gemm_kernel<MODE><<<grid, NUM_THREADS, smem_bytes, stream>>>(wmap, amaps, p);
   LO_LAUNCH_OK("grouped_gemm_kernel");
   return LO_OK;
 }
@@ -669,12 +716,13 @@ int launch_mode(const GemmArgs &a, cudaStream_t stream) {
 }  // namespace
 
 int launch_grouped_gemm(GemmMode mode, const GemmArgs &a, cudaStream_t stream) {
-  LO_REQUIRE(a.K % TILE_K == 0 && a.K >= TILE_K && a.K / TILE_K <= KB_MAX, "grouped gemm: K=%lld must be a multiple of 128, at most %d",
-             (long long)a.K, KB_MAX * TILE_K);
+  LO_REQUIRE(a.K % TILE_K == 0 && a.K >= TILE_K, "grouped gemm: K=%lld must be a positive multiple of 128", (long long)a.K);
   LO_REQUIRE(a.n_rows_per_expert % TILE_N == 0, "grouped gemm: N=%lld must be a multiple of 128", (long long)a.n_rows_per_expert);
   LO_REQUIRE((int64_t)a.E * a.n_rows_per_expert < (1LL << 31), "grouped gemm: E*N exceeds the tensor-map row range");
-  LO_REQUIRE((reinterpret_cast<uintptr_t>(a.B) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.A) & 15) == 0,
-             "grouped gemm: operands must be 16-byte aligned");
+  LO_REQUIRE(a.rows_a >= 1 && a.rows_a < (1LL << 31), "grouped gemm: activation row count out of range");
+  LO_REQUIRE((reinterpret_cast<uintptr_t>(a.B) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.A) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(a.a_scale) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.b_scale) & 15) == 0,
+             "grouped gemm: operands and scales must be 16-byte aligned");
   LO_REQUIRE(a.weight_mode == LO_WEIGHT_NONE || a.topk_weights != nullptr, "grouped gemm: weight mode %d needs topk_weights", a.weight_mode);
   if (mode == GEMM_GATE_UP) {
     LO_REQUIRE(a.n_rows_per_expert == 2 * (int64_t)a.n_tiles * TILE_N, "grouped gemm: gate_up needs N = 2*I");

@@ -79,6 +79,46 @@ __global__ void __launch_bounds__(256) group_quant_kernel(const T *__restrict__ 
   if (lane_in_group == 0) s[group] = scale;
 }
 
+// bf16 rows [M, H], group 128: quantise once, store to each of the token's sorted positions.
+__global__ void __launch_bounds__(256) group_quant_scatter_kernel(const __nv_bfloat16 *__restrict__ x, int64_t M,
+                                                                  int64_t groups_per_row, int topk,
+                                                                  const int32_t *__restrict__ inv_pos, float eps_t,
+                                                                  int8_t *__restrict__ q_sorted,
+                                                                  float *__restrict__ s_sorted) {
+  const int64_t gthread = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t group = gthread / 16;
+  const int lane_in_group = (int)(gthread % 16);
+  const bool active = group < M * groups_per_row;
+  float v[8];
+  float amax = 0.f;
+  if (active) {
+    Load8<__nv_bfloat16>::load(x + group * 128 + lane_in_group * 8, v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  }
+#pragma unroll
+  for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  if (!active) return;
+  amax = fmaxf(amax, eps_t);
+  const float scale = __fdiv_rn(amax, 127.0f);
+  uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float r = __fdiv_rn(v[i], scale);
+    r = fminf(fmaxf(r, -128.0f), 127.0f);
+    packed[i >> 2] |= (uint32_t)(__float2int_rz(r) & 0xff) << (8 * (i & 3));
+  }
+  const int64_t token = group / groups_per_row;
+  const int64_t gi = group % groups_per_row;
+  for (int j = 0; j < topk; ++j) {
+    const int32_t pos = inv_pos[token * topk + j];
+    if (pos < 0) continue;
+    *reinterpret_cast<uint2 *>(q_sorted + ((int64_t)pos * groups_per_row + gi) * 128 + lane_in_group * 8) =
+        make_uint2(packed[0], packed[1]);
+    if (lane_in_group == 0) s_sorted[(int64_t)pos * groups_per_row + gi] = scale;
+  }
+}
+
 template <typename T>
 int launch_typed(const void *x, int64_t num_groups, int group_size, float eps_t, int8_t *q, float *s,
                  cudaStream_t stream) {
@@ -106,6 +146,20 @@ float round_eps_to_dtype(float eps, int dtype) {
   if (dtype == LO_BF16) return __bfloat162float(__float2bfloat16_rn(eps));
   if (dtype == LO_F16) return __half2float(__float2half_rn(eps));
   return eps;
+}
+
+int launch_group_quant_scatter(const void *x, int64_t M, int64_t H, int topk, const int32_t *inv_pos, float eps,
+                               int8_t *q_sorted, float *s_sorted, cudaStream_t stream) {
+  if (M == 0) return LO_OK;
+  LO_REQUIRE(H % 128 == 0, "group quant: hidden size must be a multiple of 128");
+  const int64_t total_threads = M * (H / 128) * 16;
+  const int64_t blocks = ceil_div(total_threads, 256);
+  LO_REQUIRE(blocks <= 0x7fffffffLL, "group quant: too many groups");
+  group_quant_scatter_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(x), M, H / 128, topk,
+                                                                   inv_pos, round_eps_to_dtype(eps, LO_BF16), q_sorted,
+                                                                   s_sorted);
+  LO_LAUNCH_OK("group_quant_scatter_kernel");
+  return LO_OK;
 }
 
 }  // namespace lo

@@ -230,7 +230,37 @@ __global__ void __launch_bounds__(256) ep_gather_kernel(const __nv_bfloat16 *__r
   }
 }
 
+// One CTA per sorted position: copy the int8 row and its scales of token sorted_ids[pos] / top_k.
+__global__ void __launch_bounds__(128) permute_rows_kernel(const int8_t *__restrict__ A, const float *__restrict__ a_scale,
+                                                           int64_t rows_a, int64_t K, const int32_t *__restrict__ sorted_ids,
+                                                           const int32_t *__restrict__ num_tokens_post_pad,
+                                                           int64_t numel_valid, int top_k, int8_t *__restrict__ A_sorted,
+                                                           float *__restrict__ a_scale_sorted) {
+  const int64_t pos = blockIdx.x;
+  if (pos >= *num_tokens_post_pad) return;
+  const int32_t sid = sorted_ids[pos];
+  if (sid < 0 || sid >= numel_valid) return;
+  const int64_t row = sid / top_k;
+  if (row >= rows_a) return;
+  const uint4 *src = reinterpret_cast<const uint4 *>(A + row * K);
+  uint4 *dst = reinterpret_cast<uint4 *>(A_sorted + pos * K);
+  for (int64_t c = threadIdx.x; c < K / 16; c += blockDim.x) dst[c] = src[c];
+  const int64_t kb = K / 128;
+  for (int64_t c = threadIdx.x; c < kb; c += blockDim.x) a_scale_sorted[pos * kb + c] = a_scale[row * kb + c];
+}
+
 }  // namespace
+
+int launch_permute_rows(const int8_t *A, const float *a_scale, int64_t rows_a, int64_t K, const int32_t *sorted_ids,
+                        int64_t sorted_capacity, const int32_t *num_tokens_post_pad, int64_t numel_valid, int top_k,
+                        int8_t *A_sorted, float *a_scale_sorted, cudaStream_t stream) {
+  if (sorted_capacity <= 0) return LO_OK;
+  LO_REQUIRE(sorted_capacity <= 0x7fffffffLL, "permute rows: too many positions");
+  permute_rows_kernel<<<(unsigned)sorted_capacity, 128, 0, stream>>>(A, a_scale, rows_a, K, sorted_ids, num_tokens_post_pad,
+                                                                     numel_valid, top_k, A_sorted, a_scale_sorted);
+  LO_LAUNCH_OK("permute_rows_kernel");
+  return LO_OK;
+}
 
 int launch_moe_sum_masked(const __nv_bfloat16 *in, __nv_bfloat16 *out, const __nv_bfloat16 *bias, int64_t M,
                           int topk, int64_t H, float factor, const void *topk_ids, int ids_dtype,

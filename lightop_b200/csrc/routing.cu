@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(ALIGN_WARPS * 32) align_kernel(
     const IdT *__restrict__ ids, int64_t numel, int E, int block_size, const int32_t *__restrict__ expert_map,
     int map_mode, int32_t *__restrict__ sorted_ids, int64_t sorted_capacity, int32_t *__restrict__ expert_ids,
     int64_t expert_ids_capacity, int32_t *__restrict__ num_tokens_post_pad, Chunk *__restrict__ chunks,
-    int32_t *__restrict__ num_chunks, int64_t chunk_capacity) {
+    int32_t *__restrict__ num_chunks, int64_t chunk_capacity, int32_t *__restrict__ inv_pos) {
   extern __shared__ int32_t smem[];
   int32_t *hist = smem;                       // [ALIGN_WARPS][E]
   int32_t *seg_off = smem + ALIGN_WARPS * E;  // [E + 1] padded exclusive offsets
@@ -244,14 +244,18 @@ __global__ void __launch_bounds__(ALIGN_WARPS * 32) align_kernel(
   // chunk table for the fused path: <=128 consecutive rows of one expert each
   if (chunks) {
     for (int e = tid; e < E; e += blockDim.x) {
+      // the rows of an expert are cut into equal chunks (rounded up to the MMA N granule of 16):
+      // chunks of one expert then take about the same time and read the weight tiles together
       const int c = count[e];
+      const int nch = (c + 127) / 128;
+      const int per = nch > 0 ? (((c + nch - 1) / nch) + 15) / 16 * 16 : 0;
       int ci = chunk_off[e];
-      for (int r = 0; r < c; r += 128, ++ci) {
+      for (int r = 0; r < c; r += per, ++ci) {
         if (ci < chunk_capacity) {
           Chunk ch;
           ch.expert = e;
           ch.row0 = seg_off[e] + r;
-          ch.rows = c - r < 128 ? c - r : 128;
+          ch.rows = c - r < per ? c - r : per;
           ch.pad = 0;
           chunks[ci] = ch;
         }
@@ -270,7 +274,10 @@ __global__ void __launch_bounds__(ALIGN_WARPS * 32) align_kernel(
     if (e >= 0) {
       const int64_t pos = (int64_t)seg_off[e] + before + rank;
       if (pos < sorted_capacity) sorted_ids[pos] = (int32_t)(base + lane);
+      if (inv_pos) inv_pos[base + lane] = (int32_t)pos;
       if (lane == (__ffs(peers) - 1)) my_hist[e] = before + __popc(peers);
+    } else if (inv_pos && base + lane < seg_end) {
+      inv_pos[base + lane] = -1;
     }
     __syncwarp();
   }
@@ -301,7 +308,8 @@ __global__ void chunks_from_blocks_kernel(const int32_t *__restrict__ expert_ids
 int launch_align(const void *topk_ids, int ids_dtype, int64_t numel, int num_experts, int block_size,
                  const int32_t *expert_map, int map_mode, int32_t *sorted_ids, int64_t sorted_capacity,
                  int32_t *expert_ids, int64_t expert_ids_capacity, int32_t *num_tokens_post_pad,
-                 Chunk *chunks, int32_t *num_chunks, int64_t chunk_capacity, cudaStream_t stream) {
+                 Chunk *chunks, int32_t *num_chunks, int64_t chunk_capacity, int32_t *inv_pos,
+                 cudaStream_t stream) {
   LO_REQUIRE(num_experts >= 1 && num_experts <= 1024, "moe_align: num_experts %d outside [1,1024]", num_experts);
   LO_REQUIRE(block_size >= 1, "moe_align: block_size must be positive");
   LO_REQUIRE(numel >= 0 && numel < (1LL << 30), "moe_align: numel out of range");
@@ -318,7 +326,7 @@ int launch_align(const void *topk_ids, int ids_dtype, int64_t numel, int num_exp
     }
     align_kernel<int32_t><<<1, ALIGN_WARPS * 32, smem, stream>>>(
         static_cast<const int32_t *>(topk_ids), numel, num_experts, block_size, expert_map, map_mode, sorted_ids,
-        sorted_capacity, expert_ids, expert_ids_capacity, num_tokens_post_pad, chunks, num_chunks, chunk_capacity);
+        sorted_capacity, expert_ids, expert_ids_capacity, num_tokens_post_pad, chunks, num_chunks, chunk_capacity, inv_pos);
   } else if (ids_dtype == LO_I64) {
     static thread_local size_t set64 = 0;
     if (smem > 48 * 1024 && smem > set64) {
@@ -328,7 +336,7 @@ int launch_align(const void *topk_ids, int ids_dtype, int64_t numel, int num_exp
     }
     align_kernel<int64_t><<<1, ALIGN_WARPS * 32, smem, stream>>>(
         static_cast<const int64_t *>(topk_ids), numel, num_experts, block_size, expert_map, map_mode, sorted_ids,
-        sorted_capacity, expert_ids, expert_ids_capacity, num_tokens_post_pad, chunks, num_chunks, chunk_capacity);
+        sorted_capacity, expert_ids, expert_ids_capacity, num_tokens_post_pad, chunks, num_chunks, chunk_capacity, inv_pos);
   } else {
     return fail(LO_ERR_UNSUPPORTED, "moe_align: unsupported id dtype code %d", ids_dtype);
   }
@@ -374,5 +382,5 @@ extern "C" int lo_moe_align_block_size(const void *topk_ids, int ids_dtype, int6
                                        int64_t expert_ids_capacity, int32_t *num_tokens_post_pad, void *stream) {
   return lo::launch_align(topk_ids, ids_dtype, numel, num_experts, block_size, expert_map, map_mode, sorted_ids,
                           sorted_capacity, expert_ids, expert_ids_capacity, num_tokens_post_pad, nullptr, nullptr,
-                          0, static_cast<cudaStream_t>(stream));
+                          0, nullptr, static_cast<cudaStream_t>(stream));
 }

@@ -42,7 +42,7 @@ def moe_gemm_w8a8(input: torch.Tensor, b_qweight: torch.Tensor, output: torch.Te
         block_size = max(1, -(-sorted_token_ids.numel() // max(1, experts_ids.numel())))
     numel_valid = output.numel() // N
     lib = _lib.load()
-    ws_bytes = lib.lo_grouped_gemm_workspace_bytes(sorted_token_ids.numel(), int(block_size))
+    ws_bytes = lib.lo_grouped_gemm_workspace_bytes(sorted_token_ids.numel(), int(block_size), K)
     ws = torch.empty(ws_bytes, dtype=torch.uint8, device=input.device)
     w = topk_weights.reshape(-1).contiguous() if topk_weights is not None else None
     with torch.cuda.device(input.device):

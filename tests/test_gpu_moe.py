@@ -133,8 +133,8 @@ def _stage2_from_workspace(lo, M, E, k, H, I, x, w1, w2, w1_s, w2_s, w, ids):
     cap = off[7]
     wsc = ws.cpu()
     header = wsc[off[0]:off[0] + 8].view(torch.int32)
-    xq = wsc[off[1]:off[1] + M * H].view(torch.int8).view(M, H)
-    xs = wsc[off[2]:off[2] + M * (H // 128) * 4].view(torch.float32).view(M, H // 128)
+    xq = wsc[off[1]:off[1] + cap * H].view(torch.int8).view(cap, H)
+    xs = wsc[off[2]:off[2] + cap * (H // 128) * 4].view(torch.float32).view(cap, H // 128)
     sorted_ids = wsc[off[3]:off[3] + cap * 4].view(torch.int32)
     act_q = wsc[off[5]:off[5] + cap * I].view(torch.int8).view(cap, I)
     act_s = wsc[off[6]:off[6] + cap * (I // 128) * 4].view(torch.float32).view(cap, I // 128)
@@ -149,14 +149,15 @@ def test_fused_intermediates_bit_exact(lo, name, shape):
     w, ids = _route(logits, k)
     y_ref, inter = O.fused_moe_block_int8(x, w1, w2, w1_s, w2_s, w, ids, return_intermediates=True)
     y, header, xq, xs, sorted_ids, act_q, act_s = _stage2_from_workspace(lo, M, E, k, H, I, x, w1, w2, w1_s, w2_s, w, ids)
-    # stage 1 quantisation and the sort: bit-exact
-    assert torch.equal(xq, inter["a_q"]) and torch.equal(xs, inter["a_s"])
+    # the sort: bit-exact
     s_ref, _, n_ref = O.align_block_size(ids, E, 16)
     assert header[0].item() == n_ref.item()
     assert torch.equal(sorted_ids[: n_ref.item()], s_ref)
-    # stage 2 quantisation (after gate_up GEMM, SiLU*mul in bf16): compared row by row through the sort
     pos = torch.nonzero(s_ref < M * k).reshape(-1)
     sid = s_ref[pos].long()
+    # stage 1 quantisation (stored once per routed slot, in sorted order): bit-exact
+    assert torch.equal(xq[pos], inter["a_q"][sid // k]) and torch.equal(xs[pos], inter["a_s"][sid // k])
+    # stage 2 quantisation (after gate_up GEMM, SiLU*mul in bf16): compared row by row through the sort
     dq = (act_q[pos].int() - inter["act_q"][sid].int()).abs()
     frac_exact = float((dq == 0).float().mean())
     assert int(dq.max()) <= 1, f"stage-2 codes differ by {int(dq.max())}"
