@@ -11,7 +11,8 @@ from ctypes import c_char_p, c_float, c_int, c_int32, c_int64, c_size_t, c_void_
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "liblightop_b200.so")
+# LIGHTOP_B200_LIB overrides the location of the shared library (e.g. an instrumented build)
+LIB_PATH = os.environ.get("LIGHTOP_B200_LIB") or os.path.join(_HERE, "liblightop_b200.so")
 
 LO_F32, LO_F16, LO_BF16, LO_I32, LO_I64, LO_U32 = 0, 1, 2, 3, 4, 5
 LO_WEIGHT_NONE, LO_WEIGHT_FP32, LO_WEIGHT_BF16_PRODUCT = 0, 1, 2

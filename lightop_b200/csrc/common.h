@@ -89,6 +89,7 @@ struct GemmArgs {
   const int8_t *A;          // [rows_a, K] int8, rows in sorted-position order (row = position in sorted_ids)
   const float *a_scale;     // [rows_a, K/128]
   int64_t rows_a;
+  int max_chunk_rows;       // upper bound of Chunk::rows (0 = 128); selects the shared-memory staging depth
   const int8_t *B;          // [E, n_rows_per_expert, K] int8
   const float *b_scale;     // [E, n_rows_per_expert/128, K/128]
   int E;

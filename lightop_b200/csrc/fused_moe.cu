@@ -157,7 +157,9 @@ extern "C" int lo_fused_moe_block_int8(const void *x, const int8_t *w1, const in
   // 3. gate_up GEMM, SiLU*mul and re-quantisation in the epilogue -> act_q/act_s in sorted order
   prof_mark(2, st);
   GemmArgs g1{};
-  g1.A = L.xq; g1.a_scale = L.xs; g1.rows_a = L.sorted_cap; g1.B = w1; g1.b_scale = w1_scale; g1.E = E_local;
+  g1.A = L.xq; g1.a_scale = L.xs; g1.rows_a = L.sorted_cap;
+  g1.max_chunk_rows = (int)(M < 128 ? M : 128);   // an expert receives at most one row per token
+  g1.B = w1; g1.b_scale = w1_scale; g1.E = E_local;
   g1.n_rows_per_expert = 2 * I; g1.K = H; g1.n_tiles = (int)(I / 128);
   g1.sorted_ids = L.sorted_ids; g1.numel_valid = numel;
   g1.chunks = L.chunks; g1.num_chunks = L.header + 1;
@@ -172,7 +174,8 @@ extern "C" int lo_fused_moe_block_int8(const void *x, const int8_t *w1, const in
   // 4. down GEMM, routed weight in the epilogue -> cache3[token, slot, :]
   prof_mark(3, st);
   GemmArgs g2{};
-  g2.A = L.act_q; g2.a_scale = L.act_s; g2.rows_a = L.sorted_cap; g2.B = w2; g2.b_scale = w2_scale; g2.E = E_local;
+  g2.A = L.act_q; g2.a_scale = L.act_s; g2.rows_a = L.sorted_cap;
+  g2.max_chunk_rows = g1.max_chunk_rows; g2.B = w2; g2.b_scale = w2_scale; g2.E = E_local;
   g2.n_rows_per_expert = H; g2.K = I; g2.n_tiles = (int)(H / 128);
   g2.sorted_ids = L.sorted_ids; g2.numel_valid = numel;
   g2.chunks = L.chunks; g2.num_chunks = L.header + 1;
@@ -247,7 +250,8 @@ extern "C" int lo_moe_grouped_gemm_i8_block(const int8_t *A, const float *a_scal
                            W.a_sorted, W.as_sorted, st);
   if (rc != LO_OK) return rc;
   GemmArgs g{};
-  g.A = W.a_sorted; g.a_scale = W.as_sorted; g.rows_a = sorted_capacity; g.B = B; g.b_scale = b_scale; g.E = E;
+  g.A = W.a_sorted; g.a_scale = W.as_sorted; g.rows_a = sorted_capacity;
+  g.max_chunk_rows = block_size < 128 ? block_size : 128; g.B = B; g.b_scale = b_scale; g.E = E;
   g.n_rows_per_expert = N; g.K = K; g.n_tiles = (int)(N / 128);
   g.sorted_ids = sorted_ids; g.numel_valid = numel_valid;
   g.chunks = W.chunks; g.num_chunks = W.num_chunks;

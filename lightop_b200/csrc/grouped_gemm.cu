@@ -52,40 +52,43 @@ constexpr int NUM_THREADS = 384;
 constexpr int SCALE_THREADS = 64;
 constexpr int EPI_WARPS = 8;
 constexpr int W_TILE_BYTES = TILE_N * TILE_K;   // 16 KiB
-constexpr int A_TILE_BYTES = T_MAX * TILE_K;    // 16 KiB
 constexpr uint32_t TMEM_COLS = 512;
-// Ring of scale-product tables.  A slot written for K-block step i was last read at step
-// i - SC_SLOTS; the producer of step i has seen the MMAs of step i - STAGES complete, which were
-// issued after the promotion of step i - STAGES - 2 finished, so SC_SLOTS >= STAGES + 2 is enough.
-constexpr int SC_SLOTS = 8;
 // 2^23 + 2^22: adding it to an int32 of magnitude < 2^22 and reading the bits as fp32 gives
 // 12582912 + value exactly, so (that - 12582912.0f) is the exact int->float conversion
 // (|128-long int8 dot| <= 128 * 127 * 127 < 2^21).
 constexpr uint32_t MAGIC_I = 0x4B400000u;
 constexpr float MAGIC_F = 12582912.0f;
 
-template <int MODE> struct Cfg;
-template <> struct Cfg<GEMM_GATE_UP> {
-  static constexpr int STAGES = 4;
-  static constexpr int NUM_W = 2;   // gate tile + up tile
-};
-template <> struct Cfg<GEMM_SINGLE> {
-  static constexpr int STAGES = 6;
-  static constexpr int NUM_W = 1;
+// A_ROWS is the largest chunk (token count) the instantiation accepts: with few tokens per call no
+// expert can receive more than that many rows, the activation tile of a stage shrinks and more
+// stages fit into shared memory (more weight bytes in flight per SM).
+template <int MODE, int A_ROWS> struct Cfg {
+  static constexpr int NUM_W = MODE == GEMM_GATE_UP ? 2 : 1;   // gate tile + up tile
+  static constexpr int STAGE_BYTES = NUM_W * W_TILE_BYTES + A_ROWS * TILE_K;
+  static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 10 ? 10 : (200 * 1024) / STAGE_BYTES;
+  // tensor-memory partial buffers: NUM_W accumulators of A_ROWS columns each, as many as fit (at most 8)
+  static constexpr int BUF_COLS = NUM_W * A_ROWS;
+  static constexpr int NBUF = (int)TMEM_COLS / BUF_COLS > 8 ? 8 : (int)TMEM_COLS / BUF_COLS;
+  // Ring of scale-product tables.  A slot written for K-block step i was last read at step
+  // i - SC_SLOTS; the producer of step i has seen the MMAs of step i - STAGES complete, which were
+  // issued after the promotion of step i - STAGES - NBUF finished, so STAGES + NBUF slots suffice.
+  static constexpr int SC_SLOTS = STAGES + NBUF;
 };
 
-template <int MODE> struct Smem {
-  static constexpr int STAGES = Cfg<MODE>::STAGES;
-  static constexpr int NUM_W = Cfg<MODE>::NUM_W;
+template <int MODE, int A_ROWS> struct Smem {
+  static constexpr int STAGES = Cfg<MODE, A_ROWS>::STAGES;
+  static constexpr int NUM_W = Cfg<MODE, A_ROWS>::NUM_W;
+  static constexpr int NBUF = Cfg<MODE, A_ROWS>::NBUF;
   // operand tiles first: each is a multiple of 1024 bytes, base is 1024-aligned
   uint8_t w[STAGES][NUM_W][W_TILE_BYTES];
-  uint8_t a[STAGES][A_TILE_BYTES];
-  float sc[SC_SLOTS][NUM_W][T_MAX];        // token scale x weight-block scale, ring indexed by the K-block counter
+  uint8_t a[STAGES][A_ROWS * TILE_K];
+  static constexpr int SC_SLOTS = Cfg<MODE, A_ROWS>::SC_SLOTS;
+  float sc[SC_SLOTS][NUM_W][A_ROWS];       // token scale x weight-block scale, ring indexed by the K-block counter
   uint32_t amax[2][4][T_MAX / 2];          // gate_up epilogue: |act| maxima per (half, lane quarter, token)
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
-  uint64_t tmem_full[2];
-  uint64_t tmem_empty[2];
+  uint64_t tmem_full[NBUF];
+  uint64_t tmem_empty[NBUF];
   uint64_t esync[2];                       // rendezvous of the 128 epilogue threads of a token half
   uint32_t tmem_base;
   volatile int abort_flag;
@@ -115,26 +118,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ uint64_t globaltimer_ns() {
-  uint64_t t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
+// Upper bound of one wait, in SM clock cycles (about 1.5 s at 1.9 GHz).
+constexpr long long WAIT_LIMIT_CYCLES = 3000000000ll;
 
-constexpr uint64_t WAIT_LIMIT_NS = 1500ull * 1000ull * 1000ull;
-
-// Bounded wait.  Returns false when the CTA is aborting (this waiter timed out
-// or another one did); `code` identifies the waiter in the status word.
+// Bounded wait.  Returns false when the CTA is aborting (this waiter timed out or another one
+// did); `code` identifies the waiter in the status word.  The clock is only consulted every
+// 256 failed polls, so a wait that completes quickly costs nothing but the polls.
 template <class S>
 __device__ __forceinline__ bool mbar_wait(S &sm, uint64_t *bar, uint32_t parity, int32_t *status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  long long t0 = 0;
   uint32_t spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 63u) == 0u) {
+    if ((++spins & 255u) == 0u) {
       if (sm.abort_flag) return false;
-      if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+      const long long now = clock64();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > WAIT_LIMIT_CYCLES) {
         sm.abort_flag = 1;
         if (status) atomicCAS(status, 0, code);
         return false;
@@ -269,12 +270,15 @@ struct AMaps {
 
 __device__ __forceinline__ int a_map_index(int T) { return T <= 16 ? 0 : (T <= 32 ? 1 : (T <= 64 ? 2 : 3)); }
 
-template <int MODE>
+template <int MODE, int A_ROWS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ AMaps a_maps, const KParams p) {
-  using SM = Smem<MODE>;
+  using SM = Smem<MODE, A_ROWS>;
+  constexpr int SC_SLOTS = SM::SC_SLOTS;
   constexpr int STAGES = SM::STAGES;
   constexpr int NUM_W = SM::NUM_W;
+  constexpr int NBUF = SM::NBUF;
+  constexpr uint32_t BUF_COLS = Cfg<MODE, A_ROWS>::BUF_COLS;
   extern __shared__ uint8_t smem_raw[];
   SM &sm = *reinterpret_cast<SM *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -288,11 +292,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       mbar_init(&sm.full[s], 1 + SCALE_THREADS / 32);   // TMA thread (arrive.expect_tx) + one arrive per scale warp
       mbar_init(&sm.empty[s], 1);                        // tcgen05.commit of the MMA thread
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < NBUF; ++b) {
       mbar_init(&sm.tmem_full[b], 1);
       mbar_init(&sm.tmem_empty[b], EPI_WARPS);
-      mbar_init(&sm.esync[b], 128);
     }
+    for (int b = 0; b < 2; ++b) mbar_init(&sm.esync[b], 128);
     sm.abort_flag = 0;
     fence_barrier_init();
   }
@@ -355,8 +359,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           for (int kb = 0; kb < KB; ++kb, ++it, ++ab) {
             const int s = it % STAGES;
             const uint32_t ph = (it / STAGES) & 1u;
-            const uint32_t b = ab & 1u;
-            const uint32_t aph = (ab >> 1) & 1u;
+            const uint32_t b = ab % NBUF;
+            const uint32_t aph = (ab / NBUF) & 1u;
             if (!mbar_wait(sm, &sm.tmem_empty[b], aph ^ 1u, p.status, 2)) { ok = false; break; }
             if (!mbar_wait(sm, &sm.full[s], ph, p.status, 3)) { ok = false; break; }
             tc_fence_after();
@@ -364,7 +368,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
 #pragma unroll
             for (int w = 0; w < NUM_W; ++w) {
               const uint64_t adesc = make_smem_desc(smem_u32(sm.w[s][w]));
-              const uint32_t d = tmem_base + b * 256u + (uint32_t)w * T_MAX;
+              const uint32_t d = tmem_base + b * BUF_COLS + (uint32_t)w * A_ROWS;
 #pragma unroll
               for (int k4 = 0; k4 < TILE_K / 32; ++k4)
                 umma_i8(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, k4 > 0 ? 1u : 0u);
@@ -492,8 +496,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
 
       for (int kb = 0; kb < KB; ++kb, ++it, ++ab) {
         const int slot = it % SC_SLOTS;
-        const uint32_t b = ab & 1u;
-        const uint32_t aph = (ab >> 1) & 1u;
+        const uint32_t b = ab % NBUF;
+        const uint32_t aph = (ab / NBUF) & 1u;
         // The scale products of this step were written to shared memory before the stage's full
         // barrier completed, which the MMA thread observed before it issued the MMAs whose
         // completion this wait observes.  Warp-uniform outcome: the loads below are warp-collective.
@@ -502,7 +506,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         // NUM_W * 4 pieces of 16 columns, software-pipelined: the load of piece i+1 is in flight
         // while piece i is promoted.
         constexpr int PIECES = NUM_W * 4;
-        const uint32_t t_base = tmem_base + lane_off + b * 256u + (uint32_t)(h * 64);
+        const uint32_t t_base = tmem_base + lane_off + b * BUF_COLS + (uint32_t)(h * 64);
         uint32_t raw[2][16];
         if (my_cols > 0) tmem_ld16(t_base, raw[0]);
 #pragma unroll
@@ -513,7 +517,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
             tmem_ld_wait();
             if (pc + 1 < PIECES) {
               const int cn = (pc + 1) / NUM_W, wn = (pc + 1) % NUM_W;
-              if (cn * 16 < my_cols) tmem_ld16(t_base + (uint32_t)wn * T_MAX + (uint32_t)(cn * 16), raw[(pc + 1) & 1]);
+              if (cn * 16 < my_cols) tmem_ld16(t_base + (uint32_t)wn * A_ROWS + (uint32_t)(cn * 16), raw[(pc + 1) & 1]);
             }
             const ulonglong2 *scv = reinterpret_cast<const ulonglong2 *>(&sm.sc[slot][w][h * 64 + c * 16]);
 #pragma unroll
@@ -631,8 +635,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   __syncthreads();
   if (sm.abort_flag) {
     // give copies that may still be in flight time to land before the CTA's shared memory is released
-    const uint64_t t0 = globaltimer_ns();
-    while (globaltimer_ns() - t0 < 200000ull) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 400000ll) {
     }
   }
   if (warp == 1) {
@@ -683,13 +687,13 @@ int make_tile_map(CUtensorMap *map, const int8_t *base, int64_t rows, int64_t K,
   return LO_OK;
 }
 
-template <int MODE>
+template <int MODE, int A_ROWS>
 int launch_mode(const GemmArgs &a, cudaStream_t stream) {
-  using SM = Smem<MODE>;
+  using SM = Smem<MODE, A_ROWS>;
   const size_t smem_bytes = sizeof(SM) + 1024;
   static thread_local bool configured = false;
   if (!configured) {
-    LO_CUDA_OK(cudaFuncSetAttribute(grouped_gemm_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
+    LO_CUDA_OK(cudaFuncSetAttribute(grouped_gemm_kernel<MODE, A_ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
     configured = true;
   }
   CUtensorMap wmap;
@@ -708,7 +712,7 @@ int launch_mode(const GemmArgs &a, cudaStream_t stream) {
   p.topk_weights = a.topk_weights; p.weight_mode = a.weight_mode; p.act_eps = a.act_eps; p.status = a.status; p.neg_zero = -0.0f;
   const int grid = sm_count();
   if (grid <= 0) return fail(LO_ERR_CUDA, "no CUDA device");
-  grouped_gemm_kernel<MODE><<<grid, NUM_THREADS, smem_bytes, stream>>>(wmap, amaps, p);
+  grouped_gemm_kernel<MODE, A_ROWS><<<grid, NUM_THREADS, smem_bytes, stream>>>(wmap, amaps, p);
   LO_LAUNCH_OK("grouped_gemm_kernel");
   return LO_OK;
 }
@@ -724,12 +728,18 @@ int launch_grouped_gemm(GemmMode mode, const GemmArgs &a, cudaStream_t stream) {
                  (reinterpret_cast<uintptr_t>(a.a_scale) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.b_scale) & 15) == 0,
              "grouped gemm: operands and scales must be 16-byte aligned");
   LO_REQUIRE(a.weight_mode == LO_WEIGHT_NONE || a.topk_weights != nullptr, "grouped gemm: weight mode %d needs topk_weights", a.weight_mode);
+  // no chunk can hold more rows than max_chunk_rows (a bound the caller derives from the token count)
+  const int cap = a.max_chunk_rows <= 0 ? T_MAX : a.max_chunk_rows;
   if (mode == GEMM_GATE_UP) {
     LO_REQUIRE(a.n_rows_per_expert == 2 * (int64_t)a.n_tiles * TILE_N, "grouped gemm: gate_up needs N = 2*I");
-    return launch_mode<GEMM_GATE_UP>(a, stream);
+    if (cap <= 32) return launch_mode<GEMM_GATE_UP, 32>(a, stream);
+    if (cap <= 64) return launch_mode<GEMM_GATE_UP, 64>(a, stream);
+    return launch_mode<GEMM_GATE_UP, 128>(a, stream);
   }
   LO_REQUIRE(a.n_rows_per_expert == (int64_t)a.n_tiles * TILE_N, "grouped gemm: tile count mismatch");
-  return launch_mode<GEMM_SINGLE>(a, stream);
+  if (cap <= 32) return launch_mode<GEMM_SINGLE, 32>(a, stream);
+  if (cap <= 64) return launch_mode<GEMM_SINGLE, 64>(a, stream);
+  return launch_mode<GEMM_SINGLE, 128>(a, stream);
 }
 
 }  // namespace lo
