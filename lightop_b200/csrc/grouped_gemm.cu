@@ -84,7 +84,7 @@ template <int MODE, int A_ROWS> struct Smem {
   uint8_t a[STAGES][A_ROWS * TILE_K];
   static constexpr int SC_SLOTS = Cfg<MODE, A_ROWS>::SC_SLOTS;
   float sc[SC_SLOTS][NUM_W][A_ROWS];       // token scale x weight-block scale, ring indexed by the K-block counter
-  uint32_t amax[2][4][T_MAX / 2];          // gate_up epilogue: |act| maxima per (half, lane quarter, token)
+  uint32_t amax[2][2][4][T_MAX / 2];       // gate_up epilogue: |act| maxima per (item parity, half, lane quarter, token)
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
   uint64_t tmem_full[NBUF];
@@ -463,11 +463,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
     asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     const int ew = warp - 4;             // 0..7
     const int q = warp & 3;              // lane quarter of tensor memory this warp may read
-    const int h = ew >> 2;               // token half: tokens [64h, 64h + 64)
+    const int h = ew >> 2;               // which half of the chunk's tokens this warp promotes
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const uint64_t neg_magic2 = pack2(-MAGIC_F, -MAGIC_F);
     const uint64_t negzero2 = pack2(p.neg_zero, p.neg_zero);
-    uint32_t it = 0, ab = 0, eph = 0;
+    uint32_t it = 0, ab = 0, eph = 0, item_par = 0;
     bool ok = true;
     for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
       const Chunk ch = p.chunks[item / p.n_tiles];
@@ -486,8 +486,31 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         }
         continue;
       }
+      // The chunk's T columns are split between the two warp sets in multiples of 16, as evenly
+      // as that allows (T = 80 -> 48 + 32), so that both finish a K block at about the same time.
       const int T = (ch.rows + 15) & ~15;
-      const int my_cols = T - h * 64;          // tokens of this half (may be <= 0)
+      const int cols0 = ((T >> 4) + 1) / 2 * 16;
+      const int col_begin = h == 0 ? 0 : cols0;
+      const int my_cols = h == 0 ? cols0 : T - cols0;     // <= 64, may be 0
+
+      // Row ids and routed weights of this warp's tokens, two per lane (token col_begin + u*32 + lane),
+      // fetched now so that the latency is hidden behind the K loop; broadcast by shuffle later.
+      int32_t sid_r[2] = {-1, -1};
+      float wgt_r[2] = {0.f, 0.f};
+      if (MODE == GEMM_SINGLE || p.weight_mode != LO_WEIGHT_NONE) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          const int j = u * 32 + lane;
+          const int t = col_begin + j;
+          if (j < my_cols && t < ch.rows) {
+            int32_t sid = p.sorted_ids[ch.row0 + t];
+            if (sid < 0 || sid >= p.numel_valid) sid = -1;
+            sid_r[u] = sid;
+            if (sid >= 0 && p.weight_mode != LO_WEIGHT_NONE) wgt_r[u] = p.topk_weights[sid];
+          }
+        }
+      }
+
       uint64_t acc2[NUM_W][32];                // fp32 running sums, two tokens per 64-bit register
 #pragma unroll
       for (int w = 0; w < NUM_W; ++w)
@@ -506,12 +529,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         // NUM_W * 4 pieces of 16 columns, software-pipelined: the load of piece i+1 is in flight
         // while piece i is promoted.
         constexpr int PIECES = NUM_W * 4;
-        const uint32_t t_base = tmem_base + lane_off + b * BUF_COLS + (uint32_t)(h * 64);
+        const uint32_t t_base = tmem_base + lane_off + b * BUF_COLS + (uint32_t)col_begin;
         uint32_t raw[2][16];
         if (my_cols > 0) tmem_ld16(t_base, raw[0]);
 #pragma unroll
         for (int pc = 0; pc < PIECES; ++pc) {
-          const int c = pc / NUM_W;          // 16-column piece of this half
+          const int c = pc / NUM_W;          // 16-column piece of this warp's columns
           const int w = pc % NUM_W;          // gate / up
           if (c * 16 < my_cols) {
             tmem_ld_wait();
@@ -519,7 +542,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
               const int cn = (pc + 1) / NUM_W, wn = (pc + 1) % NUM_W;
               if (cn * 16 < my_cols) tmem_ld16(t_base + (uint32_t)wn * A_ROWS + (uint32_t)(cn * 16), raw[(pc + 1) & 1]);
             }
-            const ulonglong2 *scv = reinterpret_cast<const ulonglong2 *>(&sm.sc[slot][w][h * 64 + c * 16]);
+            const ulonglong2 *scv = reinterpret_cast<const ulonglong2 *>(&sm.sc[slot][w][col_begin + c * 16]);
 #pragma unroll
             for (int j4 = 0; j4 < 4; ++j4) {
               const ulonglong2 sc = scv[j4];     // scale products of four tokens
@@ -540,24 +563,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       if (!ok) break;
 
       // ------------------------------ epilogue -------------------------------
-      // row ids and routed weights of this half's 64 tokens: two per lane, broadcast by shuffle
-      int32_t sid_r[2];
-      float wgt_r[2];
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int t = h * 64 + u * 32 + lane;
-        int32_t sid = -1;
-        if (t < ch.rows) {
-          sid = p.sorted_ids[ch.row0 + t];
-          if (sid < 0 || sid >= p.numel_valid) sid = -1;
-        }
-        sid_r[u] = sid;
-        wgt_r[u] = (sid >= 0 && p.weight_mode != LO_WEIGHT_NONE) ? p.topk_weights[sid] : 0.f;
-      }
       if (MODE == GEMM_GATE_UP) {
         const int64_t I = (int64_t)p.n_tiles * TILE_N;
+        // Phase 1 (independent per token, no cross-lane traffic: the compiler can interleave
+        // the chains): act = bf16(bf16(silu(bf16(gate))) * bf16(up))
         float act[64];
-        // act = bf16(bf16(silu(bf16(gate))) * bf16(up))
 #pragma unroll
         for (int j2 = 0; j2 < 32; ++j2) {
           float gv[2], uv[2];
@@ -576,35 +586,54 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
               }
               gte = bf16_round(gte);
               up = bf16_round(up);
-              const float sl = bf16_round(gte / (1.0f + expf(-gte)));
+              const float sl = bf16_round(__fdiv_rn(gte, 1.0f + expf(-gte)));
               a = bf16_round(sl * up);
-              const uint32_t m = __reduce_max_sync(0xffffffffu, __float_as_uint(a) & 0x7fffffffu);
-              if (lane == 0) sm.amax[h][q][j] = m;
             }
             act[j] = a;
           }
         }
+        // Phase 2: maximum of |act| over this warp's 32 output columns, per token; lane (j mod 32)
+        // keeps the result of token j.
+        uint32_t own[2] = {0u, 0u};
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          if (j < my_cols) {
+            const uint32_t m = __reduce_max_sync(0xffffffffu, __float_as_uint(act[j]) & 0x7fffffffu);
+            if ((j & 31) == lane) own[j >> 5] = m;
+          }
+        }
+        uint32_t(*amax_tab)[T_MAX / 2] = sm.amax[item_par][h];
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+          if (u * 32 + lane < my_cols) amax_tab[q][u * 32 + lane] = own[u];
+        // Phase 3: the four warps of this half exchange their maxima (the table alternates between
+        // two copies from item to item, so one rendezvous per item is enough).
         mbar_arrive(&sm.esync[h]);
         if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.esync[h], eph, p.status, 9))) { ok = false; break; }
         eph ^= 1u;
+        // Phase 4: the owning lane forms the group scale of its tokens: amax / 127
+        float scale_r[2] = {1.f, 1.f};
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {
-          const int t = h * 64 + j;
-          if (t < ch.rows) {
-            const uint32_t m = max(max(sm.amax[h][0][j], sm.amax[h][1][j]), max(sm.amax[h][2][j], sm.amax[h][3][j]));
-            const float amax = fmaxf(__uint_as_float(m), p.act_eps);
-            const float scale = __fdiv_rn(amax, 127.0f);
-            float r = __fdiv_rn(act[j], scale);
-            r = fminf(fmaxf(r, -128.0f), 127.0f);
-            const int64_t pos = (int64_t)ch.row0 + t;
-            p.act_q[pos * I + (int64_t)nt * TILE_N + n_local] = (int8_t)__float2int_rz(r);
-            if (q == 0 && lane == 0) p.act_s[pos * p.n_tiles + nt] = scale;
+        for (int u = 0; u < 2; ++u) {
+          const int j = u * 32 + lane;
+          if (j < my_cols) {
+            const uint32_t m = max(max(amax_tab[0][j], amax_tab[1][j]), max(amax_tab[2][j], amax_tab[3][j]));
+            scale_r[u] = __fdiv_rn(fmaxf(__uint_as_float(m), p.act_eps), 127.0f);
+            const int t = col_begin + j;
+            if (q == 0 && t < ch.rows) p.act_s[((int64_t)ch.row0 + t) * p.n_tiles + nt] = scale_r[u];
           }
         }
-        // the amax table is reused by the next item
-        mbar_arrive(&sm.esync[h]);
-        if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.esync[h], eph, p.status, 10))) { ok = false; break; }
-        eph ^= 1u;
+        // Phase 5: q = trunc(clamp(act / scale)), one byte per (token, column)
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          const int t = col_begin + j;
+          if (j < my_cols && t < ch.rows) {
+            const float scale = __shfl_sync(0xffffffffu, scale_r[j >> 5], j & 31);
+            float r = __fdiv_rn(act[j], scale);
+            r = fminf(fmaxf(r, -128.0f), 127.0f);
+            p.act_q[((int64_t)ch.row0 + t) * I + (int64_t)nt * TILE_N + n_local] = (int8_t)__float2int_rz(r);
+          }
+        }
       } else {
 #pragma unroll
         for (int j2 = 0; j2 < 32; ++j2) {
@@ -613,20 +642,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int j = j2 * 2 + e;
-            const int32_t sid = __shfl_sync(0xffffffffu, sid_r[j >> 5], j & 31);
-            const float wgt = __shfl_sync(0xffffffffu, wgt_r[j >> 5], j & 31);
-            if (sid >= 0) {
-              float v = v2[e];
-              if (p.weight_mode == LO_WEIGHT_FP32) {
-                v = v * wgt;
-              } else if (p.weight_mode == LO_WEIGHT_BF16_PRODUCT) {
-                v = bf16_round(v) * bf16_round(wgt);
+            if (j < my_cols) {
+              const int32_t sid = __shfl_sync(0xffffffffu, sid_r[j >> 5], j & 31);
+              const float wgt = __shfl_sync(0xffffffffu, wgt_r[j >> 5], j & 31);
+              if (sid >= 0) {
+                float v = v2[e];
+                if (p.weight_mode == LO_WEIGHT_FP32) {
+                  v = v * wgt;
+                } else if (p.weight_mode == LO_WEIGHT_BF16_PRODUCT) {
+                  v = bf16_round(v) * bf16_round(wgt);
+                }
+                p.C[(int64_t)sid * p.n_rows_per_expert + (int64_t)nt * TILE_N + n_local] = __float2bfloat16_rn(v);
               }
-              p.C[(int64_t)sid * p.n_rows_per_expert + (int64_t)nt * TILE_N + n_local] = __float2bfloat16_rn(v);
             }
           }
         }
       }
+      item_par ^= 1u;
     }
   }
 
