@@ -168,6 +168,33 @@ int lo_fused_moe_block_int8(const void *x, const int8_t *w1, const int8_t *w2,
                             void *workspace, size_t workspace_bytes, int32_t *status, void *stream);
 
 /*
+ * lo_fused_moe_block_int8 for callers that can neither allocate device memory nor are given any:
+ * for example a latency-critical serving thread (cudaMalloc synchronises the whole device), a plugin
+ * that only receives raw pointers from a runtime owning the allocator, or a cgo / JNI / Rust FFI
+ * binding without an allocator handle.  It has no counterpart in the reference, whose Python layer
+ * always allocates its intermediates with torch (int8.py:681-695).
+ * Same arguments and results as lo_fused_moe_block_int8, minus the workspace: the scratch is a fixed
+ * array of LO_NOALLOC_SCRATCH_BYTES inside the library image, reserved on every GPU that loads the
+ * library until the process exits.  Limit: lo_fused_moe_workspace_bytes(M, E_local, global_num_experts,
+ * topk, H, I) must not exceed LO_NOALLOC_SCRATCH_BYTES (64 MiB: the DeepSeek-V3 shape with top_k 8 and
+ * 256 experts fits up to 64 tokens per call); larger shapes are rejected with LO_ERR_INVALID_ARGUMENT.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
+ * current); make that first call outside any stream capture.  The function calls no cudaMalloc / cudaFree
+ * and no allocating library.  All calls on a device share the one array and leave their intermediates
+ * in it: nothing needs clearing between calls, but two calls whose kernels overlap on the GPU (different
+ * streams, or a concurrent call from another host thread) race on it -- serialise them.
+ */
+#define LO_NOALLOC_SCRATCH_BYTES (64u << 20)
+int lo_fused_moe_block_int8_noalloc(const void *x, const int8_t *w1, const int8_t *w2,
+                                    const float *w1_scale, const float *w2_scale,
+                                    const float *topk_weights, const void *topk_ids, int ids_dtype,
+                                    const int32_t *expert_map, int global_num_experts,
+                                    int64_t M, int E_local, int topk, int64_t H, int64_t I,
+                                    void *cache3, const void *shared_output, void *out,
+                                    int apply_router_weight_on_input, float routed_scaling_factor,
+                                    int32_t *status, void *stream);
+
+/*
  * Per-stage timing of lo_fused_moe_block_int8 for benchmarks: while enabled (per host thread), the
  * call records CUDA events between its five kernels (align, group quant, gate_up GEMM, down GEMM,
  * top-k sum); lo_profile_read waits for the last one and returns the five durations in

@@ -2,6 +2,7 @@
 // grouped GEMM entry point.  Everything here only carves the caller's workspace
 // and enqueues kernels on the caller's stream.
 #include "common.h"
+#include <mutex>
 
 namespace lo {
 float round_eps_to_dtype(float eps, int dtype);   // quant.cu
@@ -258,4 +259,68 @@ extern "C" int lo_moe_grouped_gemm_i8_block(const int8_t *A, const float *a_scal
   g.C = static_cast<__nv_bfloat16 *>(C);
   g.topk_weights = topk_weights; g.weight_mode = weight_mode; g.act_eps = 0.f; g.status = nullptr;
   return launch_grouped_gemm(GEMM_SINGLE, g, st);
+}
+
+// ---------------------------------------------------------------------------
+// Fused layer without any caller-supplied or allocated scratch.
+//
+// Some hosts of this library have no way to obtain device memory at the moment they need the
+// layer: a serving thread that must not trigger the implicit device-wide synchronisation of
+// cudaMalloc, a plugin that is handed raw pointers by a runtime which owns the only allocator,
+// a foreign-language binding (cgo / JNI / Rust FFI) that was given no allocator handle.  For
+// them the scratch of the fused layer lives in a fixed array that is part of the library image:
+// every GPU that loads the library reserves LO_NOALLOC_SCRATCH_BYTES for it until the process ends.
+// ---------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_noalloc_scratch[LO_NOALLOC_SCRATCH_BYTES];
+
+namespace lo {
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_noalloc_mu;
+void *g_noalloc_ptr[kMaxDevices] = {};   // device address of g_noalloc_scratch, per device ordinal
+
+// The name g_noalloc_scratch is a host-side handle here, not an address a kernel may use: the
+// device address is looked up once per device, with that device current.
+int noalloc_scratch(void **out) {
+  int dev = -1;
+  LO_CUDA_OK(cudaGetDevice(&dev));
+  LO_REQUIRE(dev >= 0 && dev < kMaxDevices, "no-alloc fused moe: device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_noalloc_mu);
+  if (g_noalloc_ptr[dev] == nullptr) {
+    void *ptr = nullptr;
+    LO_CUDA_OK(cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+    LO_REQUIRE(ptr != nullptr, "no-alloc fused moe: the scratch symbol has no device address");
+    g_noalloc_ptr[dev] = ptr;
+  }
+  *out = g_noalloc_ptr[dev];
+  return LO_OK;
+}
+}  // namespace
+}  // namespace lo
+
+extern "C" int lo_fused_moe_block_int8_noalloc(const void *x, const int8_t *w1, const int8_t *w2,
+                                               const float *w1_scale, const float *w2_scale,
+                                               const float *topk_weights, const void *topk_ids, int ids_dtype,
+                                               const int32_t *expert_map, int global_num_experts, int64_t M,
+                                               int E_local, int topk, int64_t H, int64_t I, void *cache3,
+                                               const void *shared_output, void *out,
+                                               int apply_router_weight_on_input, float routed_scaling_factor,
+                                               int32_t *status, void *stream) {
+  using namespace lo;
+  LO_REQUIRE(M >= 0 && E_local >= 1 && topk >= 1 && H >= 128 && I >= 128, "no-alloc fused moe: bad shape");
+  const size_t need = lo_fused_moe_workspace_bytes(M, E_local, global_num_experts, topk, H, I);
+  if (need > (size_t)LO_NOALLOC_SCRATCH_BYTES)
+    return fail(LO_ERR_INVALID_ARGUMENT,
+                "no-alloc fused moe: this shape needs %zu bytes of scratch, the built-in array holds %zu; "
+                "use fewer tokens per call or lo_fused_moe_block_int8 with a caller-owned workspace",
+                need, (size_t)LO_NOALLOC_SCRATCH_BYTES);
+  void *scratch = nullptr;
+  const int rc = noalloc_scratch(&scratch);
+  if (rc != LO_OK) return rc;
+  // Nothing in the scratch has to start at zero: every region a kernel reads for a result was written
+  // earlier in the same call (sentinel fill, header, chunk table, sorted rows), so the previous call's
+  // contents that remain in it are never interpreted.
+  return lo_fused_moe_block_int8(x, w1, w2, w1_scale, w2_scale, topk_weights, topk_ids, ids_dtype, expert_map,
+                                 global_num_experts, M, E_local, topk, H, I, cache3, shared_output, out,
+                                 apply_router_weight_on_input, routed_scaling_factor, scratch, need, status, stream);
 }
