@@ -195,6 +195,22 @@ int lo_fused_moe_block_int8_noalloc(const void *x, const int8_t *w1, const int8_
                                     int32_t *status, void *stream);
 
 /*
+ * Expert side of expert parallelism: run gate_up -> SiLU*mul -> re-quantise -> down on rows that arrive
+ * already group-quantised from other ranks.  xq [T,H] int8, xs [T,H/128] f32, row_expert i32 [T] (local
+ * expert of the row; rows with an id outside [0,E_local) are skipped and their output row is left
+ * untouched), row_weight f32 [T] or NULL (routed weight, applied as bf16(acc)*bf16(w)), out [T,H] bf16.
+ * workspace: lo_fused_moe_workspace_bytes(T, E_local, E_local, 1, H, I) bytes.
+ * The reference has no such entry point: its EP support stops at the local permutation kernels
+ * (csrc/kernels/deepgemm_moe_permute.cu) and leaves the exchange and the expert-side driver to the
+ * serving framework (test/test_ep_gather_scatter_moe.py:205-296 shows the intended sequence).
+ */
+int lo_expert_rows_block_int8(const int8_t *xq, const float *xs, const int32_t *row_expert,
+                              const float *row_weight, const int8_t *w1, const int8_t *w2,
+                              const float *w1_scale, const float *w2_scale, int64_t T, int E_local,
+                              int64_t H, int64_t I, void *out, void *workspace, size_t workspace_bytes,
+                              int32_t *status, void *stream);
+
+/*
  * Per-stage timing of lo_fused_moe_block_int8 for benchmarks: while enabled (per host thread), the
  * call records CUDA events between its five kernels (align, group quant, gate_up GEMM, down GEMM,
  * top-k sum); lo_profile_read waits for the last one and returns the five durations in

@@ -324,3 +324,54 @@ extern "C" int lo_fused_moe_block_int8_noalloc(const void *x, const int8_t *w1, 
                                  global_num_experts, M, E_local, topk, H, I, cache3, shared_output, out,
                                  apply_router_weight_on_input, routed_scaling_factor, scratch, need, status, stream);
 }
+
+// ---------------------------------------------------------------------------
+// Expert side of expert parallelism: rows arrive already quantised (int8 + group scales), each with
+// the local expert that has to process it and, optionally, its routed weight.
+// ---------------------------------------------------------------------------
+extern "C" int lo_expert_rows_block_int8(const int8_t *xq, const float *xs, const int32_t *row_expert,
+                                         const float *row_weight, const int8_t *w1, const int8_t *w2,
+                                         const float *w1_scale, const float *w2_scale, int64_t T, int E_local,
+                                         int64_t H, int64_t I, void *out, void *workspace, size_t workspace_bytes,
+                                         int32_t *status, void *stream) {
+  using namespace lo;
+  LO_REQUIRE(T >= 0 && E_local >= 1 && E_local <= 1024, "expert rows: bad shape");
+  if (T == 0) return LO_OK;
+  LO_REQUIRE(xq && xs && row_expert && w1 && w2 && w1_scale && w2_scale && out && workspace, "expert rows: null pointer");
+  LO_REQUIRE(H % 128 == 0 && I % 128 == 0, "expert rows: hidden and intermediate sizes must be multiples of 128");
+  LO_REQUIRE(T < (1LL << 30), "expert rows: too many rows");
+  LO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & (ALIGN_BYTES - 1)) == 0, "expert rows: workspace must be 256-byte aligned");
+  FusedLayout L = carve_fused(workspace, T, E_local, 1, H, I);
+  LO_REQUIRE(workspace_bytes >= L.bytes, "expert rows: workspace of %zu bytes, %zu needed", workspace_bytes, L.bytes);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // 1. expert-major stable order of the rows (ids outside [0, E_local) are dropped)
+  int rc = launch_align(row_expert, LO_I32, T, E_local, FUSED_ALIGN_BLOCK, nullptr, 0, L.sorted_ids, L.sorted_cap,
+                        nullptr, 0, L.header, L.chunks, L.header + 1, L.chunk_cap, nullptr, st);
+  if (rc != LO_OK) return rc;
+  // 2. rows and scales into sorted order
+  rc = launch_permute_rows(xq, xs, T, H, L.sorted_ids, L.sorted_cap, L.header, T, 1, L.xq, L.xs, st);
+  if (rc != LO_OK) return rc;
+  GemmArgs g1{};
+  g1.A = L.xq; g1.a_scale = L.xs; g1.rows_a = L.sorted_cap; g1.max_chunk_rows = (int)(T < 128 ? T : 128);
+  g1.B = w1; g1.b_scale = w1_scale; g1.E = E_local;
+  g1.n_rows_per_expert = 2 * I; g1.K = H; g1.n_tiles = (int)(I / 128);
+  g1.sorted_ids = L.sorted_ids; g1.numel_valid = T;
+  g1.chunks = L.chunks; g1.num_chunks = L.header + 1;
+  g1.act_q = L.act_q; g1.act_s = L.act_s;
+  g1.weight_mode = LO_WEIGHT_NONE;
+  g1.act_eps = round_eps_to_dtype(1e-10f, LO_BF16);
+  g1.status = status;
+  rc = launch_grouped_gemm(GEMM_GATE_UP, g1, st);
+  if (rc != LO_OK) return rc;
+  GemmArgs g2{};
+  g2.A = L.act_q; g2.a_scale = L.act_s; g2.rows_a = L.sorted_cap; g2.max_chunk_rows = g1.max_chunk_rows;
+  g2.B = w2; g2.b_scale = w2_scale; g2.E = E_local;
+  g2.n_rows_per_expert = H; g2.K = I; g2.n_tiles = (int)(H / 128);
+  g2.sorted_ids = L.sorted_ids; g2.numel_valid = T;
+  g2.chunks = L.chunks; g2.num_chunks = L.header + 1;
+  g2.C = static_cast<__nv_bfloat16 *>(out);      // top_k = 1: the sorted id is the row itself
+  g2.topk_weights = row_weight;
+  g2.weight_mode = row_weight ? LO_WEIGHT_BF16_PRODUCT : LO_WEIGHT_NONE;
+  g2.status = status;
+  return launch_grouped_gemm(GEMM_SINGLE, g2, st);
+}

@@ -270,3 +270,30 @@ def test_fused_zipf_imbalance(lo):
     y_ref = O.fused_moe_block_int8(x, w1, w2, w1_s, w2_s, w, ids)
     y = _run_fused(lo, x, w1, w2, w1_s, w2_s, w, ids)
     assert_out_close(y, y_ref, "zipf")
+
+
+# ------------------------------ expert parallelism on one device -----------------------
+
+def test_expert_rows_entry_point_and_ep_driver_world1(lo):
+    """The EP driver with a single rank (NCCL, world size 1) must give the bits of the fused layer."""
+    import socket
+    import torch.distributed as dist
+    from lightop_b200.ep import ExpertParallelMoE
+    E, k, M, H, I = 16, 4, 70, 512, 256
+    w1, w2, w1_s, w2_s = synthetic.make_weights(E, H, I, seed=21)
+    x, logits = synthetic.make_activations(M, H, E, seed=22)
+    w, ids = _route(logits, k)
+    base = _run_fused(lo, x, w1, w2, w1_s, w2_s, w, ids)
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1)
+    try:
+        layer = ExpertParallelMoE(w1.to(DEV), w2.to(DEV), w1_s.to(DEV), w2_s.to(DEV), E)
+        y = layer.forward(x.to(DEV), w.to(DEV), ids.to(DEV))
+        torch.cuda.synchronize()
+        lo.check_device_status()
+    finally:
+        dist.destroy_process_group()
+    assert torch.equal(y, base)
+    assert_out_close(y, O.fused_moe_block_int8(x, w1, w2, w1_s, w2_s, w, ids), "ep world 1")
