@@ -14,7 +14,7 @@
 // same weight tiles at about the same time out of L2.  Persistent CTAs take
 // items round-robin.
 //
-// Warp roles in a CTA of 12 warps (3 warpgroups):
+// Warp roles in a CTA of 20 warps:
 //   warp 0      : TMA producer (one elected lane): weight tiles and the chunk's token rows.
 //                 Token rows are read from an expert-sorted copy of the activations, so a
 //                 chunk is a run of consecutive rows and one tiled TMA load fetches it.
@@ -22,15 +22,19 @@
 //   warps 2-3   : scale producers: the token scales of the K block (prefetched four K
 //                 blocks ahead) times the weight-block scale(s) -> per-step table in
 //                 shared memory
-//   warps 4-11  : promotion / epilogue: tcgen05.ld of the int32 partial, exact
-//                 int->float conversion by the 2^23+2^22 offset trick, multiply by the
-//                 scale product, add into fp32 registers with packed f32x2 operations
-//                 (mul and add kept separate: same rounding sequence as the
-//                 reference's torch model), then the fused epilogue.
-// Pipelines: STAGES shared-memory stages (full/empty mbarriers) between the
-// producers and the MMA warp, two tensor-memory partial buffers (tmem_full /
-// tmem_empty) between the MMA warp and the promotion warps, so the MMAs of K
-// block kb+1 overlap the promotion of K block kb.
+//   warps 4-19  : promotion / epilogue.  The fp32 running sums live in tensor memory next to
+//                 the int32 partials: per K block a warp loads 16 columns of the partial and of
+//                 the running sum, converts exactly (2^23+2^22 offset trick), multiplies by the
+//                 scale product, adds (packed f32x2; mul and add kept separate: the rounding
+//                 sequence of the reference's torch model) and stores the sum back.  All loops
+//                 over columns are rolled, so the instruction footprint is one 16-column body
+//                 however many tokens a chunk has, and a thread needs few registers, which is
+//                 what lets 16 such warps (4 per scheduler) hide the tensor-memory latency.
+// Pipelines: STAGES shared-memory stages (full/empty mbarriers) between the producers and
+// the MMA warp; NBUF tensor-memory partial buffers (tmem_full / tmem_empty) between the MMA
+// warp and the promotion warps.  A buffer holds ONE accumulator: for gate_up the gate and the
+// up partial of a K block are separate half-steps, so the MMAs of one overlap the promotion
+// of the other even when only two buffers fit.
 //
 // Every wait is bounded: after about a second a waiter records a timeout in the
 // status word, raises a CTA-wide abort flag, and all roles fall through to the
@@ -48,9 +52,9 @@ namespace {
 constexpr int TILE_N = 128;      // weight rows per accumulator (MMA M)
 constexpr int TILE_K = 128;      // int8 elements (= bytes) per K block
 constexpr int T_MAX = 128;       // tokens per chunk (MMA N upper bound)
-constexpr int NUM_THREADS = 384;
+constexpr int NUM_THREADS = 640;
 constexpr int SCALE_THREADS = 64;
-constexpr int EPI_WARPS = 8;
+constexpr int EPI_WARPS = 16;
 constexpr int W_TILE_BYTES = TILE_N * TILE_K;   // 16 KiB
 constexpr uint32_t TMEM_COLS = 512;
 // 2^23 + 2^22: adding it to an int32 of magnitude < 2^22 and reading the bits as fp32 gives
@@ -66,9 +70,10 @@ template <int MODE, int A_ROWS> struct Cfg {
   static constexpr int NUM_W = MODE == GEMM_GATE_UP ? 2 : 1;   // gate tile + up tile
   static constexpr int STAGE_BYTES = NUM_W * W_TILE_BYTES + A_ROWS * TILE_K;
   static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 10 ? 10 : (200 * 1024) / STAGE_BYTES;
-  // tensor-memory partial buffers: NUM_W accumulators of A_ROWS columns each, as many as fit (at most 8)
-  static constexpr int BUF_COLS = NUM_W * A_ROWS;
-  static constexpr int NBUF = (int)TMEM_COLS / BUF_COLS > 8 ? 8 : (int)TMEM_COLS / BUF_COLS;
+  // tensor memory: columns [0, NUM_W * A_ROWS) hold the fp32 running sums (gate, then up); the rest is
+  // cut into partial buffers of A_ROWS columns, one accumulator each (at most 8 are used)
+  static constexpr int ACC_COLS = NUM_W * A_ROWS;
+  static constexpr int NBUF = ((int)TMEM_COLS - ACC_COLS) / A_ROWS > 8 ? 8 : ((int)TMEM_COLS - ACC_COLS) / A_ROWS;
   // Ring of scale-product tables.  A slot written for K-block step i was last read at step
   // i - SC_SLOTS; the producer of step i has seen the MMAs of step i - STAGES complete, which were
   // issued after the promotion of step i - STAGES - NBUF finished, so STAGES + NBUF slots suffice.
@@ -84,12 +89,13 @@ template <int MODE, int A_ROWS> struct Smem {
   uint8_t a[STAGES][A_ROWS * TILE_K];
   static constexpr int SC_SLOTS = Cfg<MODE, A_ROWS>::SC_SLOTS;
   float sc[SC_SLOTS][NUM_W][A_ROWS];       // token scale x weight-block scale, ring indexed by the K-block counter
-  uint32_t amax[2][2][4][T_MAX / 2];       // gate_up epilogue: |act| maxima per (item parity, half, lane quarter, token)
+  uint32_t amax[2][4][T_MAX];              // gate_up epilogue: |act| maxima per (item parity, lane quarter, token)
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
   uint64_t tmem_full[NBUF];
   uint64_t tmem_empty[NBUF];
-  uint64_t esync[2];                       // rendezvous of the 128 epilogue threads of a token half
+  uint64_t esync[4];                       // rendezvous of the 128 epilogue threads of a column group
+  uint64_t isync;                          // rendezvous of all promotion warps between two items
   uint32_t tmem_base;
   volatile int abort_flag;
 };
@@ -215,6 +221,16 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// Store 16 consecutive tensor-memory columns of this thread's lane.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Packed fp32 pair arithmetic (two IEEE round-to-nearest operations per instruction).
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
@@ -278,7 +294,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   constexpr int STAGES = SM::STAGES;
   constexpr int NUM_W = SM::NUM_W;
   constexpr int NBUF = SM::NBUF;
-  constexpr uint32_t BUF_COLS = Cfg<MODE, A_ROWS>::BUF_COLS;
+  constexpr uint32_t ACC_COLS = Cfg<MODE, A_ROWS>::ACC_COLS;
   extern __shared__ uint8_t smem_raw[];
   SM &sm = *reinterpret_cast<SM *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -296,7 +312,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       mbar_init(&sm.tmem_full[b], 1);
       mbar_init(&sm.tmem_empty[b], EPI_WARPS);
     }
-    for (int b = 0; b < 2; ++b) mbar_init(&sm.esync[b], 128);
+    for (int b = 0; b < 4; ++b) mbar_init(&sm.esync[b], 128);
+    mbar_init(&sm.isync, EPI_WARPS);
     sm.abort_flag = 0;
     fence_barrier_init();
   }
@@ -314,11 +331,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   const int64_t num_items = (int64_t)num_chunks * p.n_tiles;
   const int KB = p.KB;
 
-  // Register re-partitioning.  The CTA owns NUM_THREADS * 168 = 64512 registers (launch bound);
-  // setmaxnreg.inc blocks (unboundedly) until the pool has room, so the producers' decrease must
-  // free at least what the two epilogue warpgroups take: 128 * 72 + 256 * 216 = 64512.
   if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     if (warp == 0) {
       // ============ TMA producer: weight tiles + the chunk's token rows ============
       if (lane == 0) {
@@ -356,25 +369,26 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           if (ch.expert < 0) continue;
           const uint32_t T = (uint32_t)((ch.rows + 15) & ~15);
           const uint32_t idesc = make_idesc(T);
-          for (int kb = 0; kb < KB; ++kb, ++it, ++ab) {
+          for (int kb = 0; kb < KB; ++kb, ++it) {
             const int s = it % STAGES;
             const uint32_t ph = (it / STAGES) & 1u;
-            const uint32_t b = ab % NBUF;
-            const uint32_t aph = (ab / NBUF) & 1u;
-            if (!mbar_wait(sm, &sm.tmem_empty[b], aph ^ 1u, p.status, 2)) { ok = false; break; }
             if (!mbar_wait(sm, &sm.full[s], ph, p.status, 3)) { ok = false; break; }
-            tc_fence_after();
             const uint64_t bdesc = make_smem_desc(smem_u32(sm.a[s]));
 #pragma unroll
-            for (int w = 0; w < NUM_W; ++w) {
+            for (int w = 0; w < NUM_W; ++w, ++ab) {
+              const uint32_t b = ab % NBUF;
+              const uint32_t aph = (ab / NBUF) & 1u;
+              if (!mbar_wait(sm, &sm.tmem_empty[b], aph ^ 1u, p.status, 2)) { ok = false; break; }
+              tc_fence_after();
               const uint64_t adesc = make_smem_desc(smem_u32(sm.w[s][w]));
-              const uint32_t d = tmem_base + b * BUF_COLS + (uint32_t)w * A_ROWS;
+              const uint32_t d = tmem_base + ACC_COLS + b * (uint32_t)A_ROWS;
 #pragma unroll
               for (int k4 = 0; k4 < TILE_K / 32; ++k4)
                 umma_i8(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, k4 > 0 ? 1u : 0u);
+              umma_commit(&sm.tmem_full[b]);
             }
+            if (!ok) break;
             umma_commit(&sm.empty[s]);
-            umma_commit(&sm.tmem_full[b]);
           }
         }
       }
@@ -459,11 +473,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       }
     }
   } else {
-    // ====================== promotion + epilogue (8 warps) =====================
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
-    const int ew = warp - 4;             // 0..7
-    const int q = warp & 3;              // lane quarter of tensor memory this warp may read
-    const int h = ew >> 2;               // which half of the chunk's tokens this warp promotes
+    // ====================== promotion + epilogue (16 warps) ====================
+    const int pw = warp - 4;             // 0..15
+    const int q = warp & 3;              // lane quarter of tensor memory this warp may access
+    const int cg = pw >> 2;              // column group: which share of the chunk's tokens
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const uint64_t neg_magic2 = pack2(-MAGIC_F, -MAGIC_F);
     const uint64_t negzero2 = pack2(p.neg_zero, p.neg_zero);
@@ -476,9 +489,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       if (ch.expert < 0) {
         // block of a non-local expert: its output rows are zero
         if (MODE == GEMM_SINGLE) {
-          for (int j = 0; j < 64; ++j) {
-            const int t = h * 64 + j;
-            if (t >= ch.rows) break;
+          for (int t = cg; t < ch.rows; t += 4) {
             const int32_t sid = p.sorted_ids[ch.row0 + t];
             if (sid >= 0 && sid < p.numel_valid)
               p.C[(int64_t)sid * p.n_rows_per_expert + (int64_t)nt * TILE_N + n_local] = __float2bfloat16_rn(0.f);
@@ -486,178 +497,174 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         }
         continue;
       }
-      // The chunk's T columns are split between the two warp sets in multiples of 16, as evenly
-      // as that allows (T = 80 -> 48 + 32), so that both finish a K block at about the same time.
+      // The chunk's T columns (a multiple of 16) are dealt to the four column groups in pieces of 16,
+      // as evenly as that allows; a group owns at most two pieces (32 tokens).
       const int T = (ch.rows + 15) & ~15;
-      const int cols0 = ((T >> 4) + 1) / 2 * 16;
-      const int col_begin = h == 0 ? 0 : cols0;
-      const int my_cols = h == 0 ? cols0 : T - cols0;     // <= 64, may be 0
+      const int n_pieces = T >> 4;
+      const int my_p = n_pieces / 4 + (cg < (n_pieces & 3) ? 1 : 0);
+      const int col_begin = (cg * (n_pieces / 4) + min(cg, n_pieces & 3)) * 16;
 
-      // Row ids and routed weights of this warp's tokens, two per lane (token col_begin + u*32 + lane),
-      // fetched now so that the latency is hidden behind the K loop; broadcast by shuffle later.
-      int32_t sid_r[2] = {-1, -1};
-      float wgt_r[2] = {0.f, 0.f};
+      // Row id and routed weight of token col_begin + lane, fetched now so that the latency is
+      // hidden behind the K loop; broadcast by shuffle in the epilogue.
+      int32_t sid_r = -1;
+      float wgt_r = 0.f;
       if (MODE == GEMM_SINGLE || p.weight_mode != LO_WEIGHT_NONE) {
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int j = u * 32 + lane;
-          const int t = col_begin + j;
-          if (j < my_cols && t < ch.rows) {
-            int32_t sid = p.sorted_ids[ch.row0 + t];
-            if (sid < 0 || sid >= p.numel_valid) sid = -1;
-            sid_r[u] = sid;
-            if (sid >= 0 && p.weight_mode != LO_WEIGHT_NONE) wgt_r[u] = p.topk_weights[sid];
-          }
+        const int t = col_begin + lane;
+        if (lane < my_p * 16 && t < ch.rows) {
+          int32_t sid = p.sorted_ids[ch.row0 + t];
+          if (sid < 0 || sid >= p.numel_valid) sid = -1;
+          sid_r = sid;
+          if (sid >= 0 && p.weight_mode != LO_WEIGHT_NONE) wgt_r = p.topk_weights[sid];
         }
       }
 
-      uint64_t acc2[NUM_W][32];                // fp32 running sums, two tokens per 64-bit register
-#pragma unroll
-      for (int w = 0; w < NUM_W; ++w)
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc2[w][j] = 0ull;
-
-      for (int kb = 0; kb < KB; ++kb, ++it, ++ab) {
+      for (int kb = 0; kb < KB && ok; ++kb, ++it) {
         const int slot = it % SC_SLOTS;
-        const uint32_t b = ab % NBUF;
-        const uint32_t aph = (ab / NBUF) & 1u;
-        // The scale products of this step were written to shared memory before the stage's full
-        // barrier completed, which the MMA thread observed before it issued the MMAs whose
-        // completion this wait observes.  Warp-uniform outcome: the loads below are warp-collective.
-        if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.tmem_full[b], aph, p.status, 5))) { ok = false; break; }
-        tc_fence_after();
-        // NUM_W * 4 pieces of 16 columns, software-pipelined: the load of piece i+1 is in flight
-        // while piece i is promoted.
-        constexpr int PIECES = NUM_W * 4;
-        const uint32_t t_base = tmem_base + lane_off + b * BUF_COLS + (uint32_t)col_begin;
-        uint32_t raw[2][16];
-        if (my_cols > 0) tmem_ld16(t_base, raw[0]);
 #pragma unroll
-        for (int pc = 0; pc < PIECES; ++pc) {
-          const int c = pc / NUM_W;          // 16-column piece of this warp's columns
-          const int w = pc % NUM_W;          // gate / up
-          if (c * 16 < my_cols) {
-            tmem_ld_wait();
-            if (pc + 1 < PIECES) {
-              const int cn = (pc + 1) / NUM_W, wn = (pc + 1) % NUM_W;
-              if (cn * 16 < my_cols) tmem_ld16(t_base + (uint32_t)wn * A_ROWS + (uint32_t)(cn * 16), raw[(pc + 1) & 1]);
+        for (int w = 0; w < NUM_W; ++w, ++ab) {
+          const uint32_t b = ab % NBUF;
+          const uint32_t aph = (ab / NBUF) & 1u;
+          // The scale products of this step were written to shared memory before the stage's full
+          // barrier completed, which the MMA thread observed before it issued the MMAs whose
+          // completion this wait observes.  Warp-uniform outcome: the accesses below are warp-collective.
+          if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.tmem_full[b], aph, p.status, 5))) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t part = tmem_base + lane_off + ACC_COLS + b * (uint32_t)A_ROWS + (uint32_t)col_begin;
+          const uint32_t accp = tmem_base + lane_off + (uint32_t)(w * A_ROWS + col_begin);
+#pragma unroll 1
+          for (int pc = 0; pc < my_p; ++pc) {
+            uint32_t raw[16], accv[16];
+            tmem_ld16(part + pc * 16, raw);
+            if (kb > 0) {
+              tmem_ld16(accp + pc * 16, accv);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) accv[j] = 0u;
             }
-            const ulonglong2 *scv = reinterpret_cast<const ulonglong2 *>(&sm.sc[slot][w][col_begin + c * 16]);
+            tmem_ld_wait();
+            const ulonglong2 *scv = reinterpret_cast<const ulonglong2 *>(&sm.sc[slot][w][col_begin + pc * 16]);
 #pragma unroll
             for (int j4 = 0; j4 < 4; ++j4) {
               const ulonglong2 sc = scv[j4];     // scale products of four tokens
-              const uint32_t *r = &raw[pc & 1][j4 * 4];
+              const uint32_t *r = &raw[j4 * 4];
               // exact int -> float: bits(int + MAGIC_I) read as fp32, minus MAGIC_F
               const uint64_t f01 = add2(pack2(__uint_as_float(r[0] + MAGIC_I), __uint_as_float(r[1] + MAGIC_I)), neg_magic2);
               const uint64_t f23 = add2(pack2(__uint_as_float(r[2] + MAGIC_I), __uint_as_float(r[3] + MAGIC_I)), neg_magic2);
-              uint64_t *a = &acc2[w][c * 8 + j4 * 2];
-              a[0] = add2(a[0], mul2_rounded(f01, sc.x, negzero2));
-              a[1] = add2(a[1], mul2_rounded(f23, sc.y, negzero2));
+              const uint64_t a01 = add2(pack2(__uint_as_float(accv[j4 * 4 + 0]), __uint_as_float(accv[j4 * 4 + 1])),
+                                        mul2_rounded(f01, sc.x, negzero2));
+              const uint64_t a23 = add2(pack2(__uint_as_float(accv[j4 * 4 + 2]), __uint_as_float(accv[j4 * 4 + 3])),
+                                        mul2_rounded(f23, sc.y, negzero2));
+              float o0, o1, o2, o3;
+              unpack2(a01, o0, o1);
+              unpack2(a23, o2, o3);
+              accv[j4 * 4 + 0] = __float_as_uint(o0);
+              accv[j4 * 4 + 1] = __float_as_uint(o1);
+              accv[j4 * 4 + 2] = __float_as_uint(o2);
+              accv[j4 * 4 + 3] = __float_as_uint(o3);
             }
+            tmem_st16(accp + pc * 16, accv);
           }
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sm.tmem_empty[b]);
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.tmem_empty[b]);
       }
       if (!ok) break;
 
       // ------------------------------ epilogue -------------------------------
+      const uint32_t acc0 = tmem_base + lane_off + (uint32_t)col_begin;            // gate (or the only) sums
       if (MODE == GEMM_GATE_UP) {
         const int64_t I = (int64_t)p.n_tiles * TILE_N;
-        // Phase 1 (independent per token, no cross-lane traffic: the compiler can interleave
-        // the chains): act = bf16(bf16(silu(bf16(gate))) * bf16(up))
-        float act[64];
+        const uint32_t acc1 = acc0 + (uint32_t)A_ROWS;                              // up sums
+        uint32_t(*amax_tab)[T_MAX] = sm.amax[item_par];
+        // Pass A, per piece of 16 tokens: act = bf16(bf16(silu(bf16(gate))) * bf16(up)), kept in tensor
+        // memory in place of the gate sums; maximum of |act| over this warp's 32 output columns.
+#pragma unroll 1
+        for (int pc = 0; pc < my_p; ++pc) {
+          uint32_t gv[16], uv[16];
+          tmem_ld16(acc0 + pc * 16, gv);
+          tmem_ld16(acc1 + pc * 16, uv);
+          tmem_ld_wait();
+          uint32_t own = 0u;
 #pragma unroll
-        for (int j2 = 0; j2 < 32; ++j2) {
-          float gv[2], uv[2];
-          unpack2(acc2[0][j2], gv[0], gv[1]);
-          unpack2(acc2[NUM_W - 1][j2], uv[0], uv[1]);
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int j = j2 * 2 + e;
-            float a = 0.f;
-            if (j < my_cols) {
-              float gte = gv[e], up = uv[e];
-              if (p.weight_mode == LO_WEIGHT_FP32) {
-                const float wgt = __shfl_sync(0xffffffffu, wgt_r[j >> 5], j & 31);
-                gte *= wgt;
-                up *= wgt;
-              }
-              gte = bf16_round(gte);
-              up = bf16_round(up);
-              const float sl = bf16_round(__fdiv_rn(gte, 1.0f + expf(-gte)));
-              a = bf16_round(sl * up);
+          for (int j = 0; j < 16; ++j) {
+            float gte = __uint_as_float(gv[j]), up = __uint_as_float(uv[j]);
+            if (p.weight_mode == LO_WEIGHT_FP32) {
+              const float wgt = __shfl_sync(0xffffffffu, wgt_r, pc * 16 + j);
+              gte *= wgt;
+              up *= wgt;
             }
-            act[j] = a;
+            gte = bf16_round(gte);
+            up = bf16_round(up);
+            const float sl = bf16_round(__fdiv_rn(gte, 1.0f + expf(-gte)));
+            const float a = bf16_round(sl * up);
+            gv[j] = __float_as_uint(a);
+            const uint32_t m = __reduce_max_sync(0xffffffffu, __float_as_uint(a) & 0x7fffffffu);
+            if (j == lane) own = m;
           }
+          tmem_st16(acc0 + pc * 16, gv);
+          if (lane < 16) amax_tab[q][col_begin + pc * 16 + lane] = own;
         }
-        // Phase 2: maximum of |act| over this warp's 32 output columns, per token; lane (j mod 32)
-        // keeps the result of token j.
-        uint32_t own[2] = {0u, 0u};
-#pragma unroll
-        for (int j = 0; j < 64; ++j) {
-          if (j < my_cols) {
-            const uint32_t m = __reduce_max_sync(0xffffffffu, __float_as_uint(act[j]) & 0x7fffffffu);
-            if ((j & 31) == lane) own[j >> 5] = m;
-          }
-        }
-        uint32_t(*amax_tab)[T_MAX / 2] = sm.amax[item_par][h];
-#pragma unroll
-        for (int u = 0; u < 2; ++u)
-          if (u * 32 + lane < my_cols) amax_tab[q][u * 32 + lane] = own[u];
-        // Phase 3: the four warps of this half exchange their maxima (the table alternates between
-        // two copies from item to item, so one rendezvous per item is enough).
-        mbar_arrive(&sm.esync[h]);
-        if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.esync[h], eph, p.status, 9))) { ok = false; break; }
+        tmem_st_wait();
+        // the four warps of this column group exchange their maxima (the table alternates between two
+        // copies from item to item, so one rendezvous per item is enough)
+        mbar_arrive(&sm.esync[cg]);
+        if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.esync[cg], eph, p.status, 9))) { ok = false; break; }
         eph ^= 1u;
-        // Phase 4: the owning lane forms the group scale of its tokens: amax / 127
-        float scale_r[2] = {1.f, 1.f};
-#pragma unroll
-        for (int u = 0; u < 2; ++u) {
-          const int j = u * 32 + lane;
-          if (j < my_cols) {
-            const uint32_t m = max(max(amax_tab[0][j], amax_tab[1][j]), max(amax_tab[2][j], amax_tab[3][j]));
-            scale_r[u] = __fdiv_rn(fmaxf(__uint_as_float(m), p.act_eps), 127.0f);
-            const int t = col_begin + j;
-            if (q == 0 && t < ch.rows) p.act_s[((int64_t)ch.row0 + t) * p.n_tiles + nt] = scale_r[u];
+        // Pass B: lane j (< 16) forms the group scale of token j of the piece, amax / 127; every thread then
+        // quantises its column of the 16 tokens: q = trunc(clamp(act / scale)).
+#pragma unroll 1
+        for (int pc = 0; pc < my_p; ++pc) {
+          uint32_t av[16];
+          tmem_ld16(acc0 + pc * 16, av);
+          float scale_r = 1.f;
+          const int t_own = col_begin + pc * 16 + (lane & 15);
+          {
+            const uint32_t m = max(max(amax_tab[0][t_own], amax_tab[1][t_own]), max(amax_tab[2][t_own], amax_tab[3][t_own]));
+            scale_r = __fdiv_rn(fmaxf(__uint_as_float(m), p.act_eps), 127.0f);
+            if (q == 0 && lane < 16 && t_own < ch.rows) p.act_s[((int64_t)ch.row0 + t_own) * p.n_tiles + nt] = scale_r;
           }
-        }
-        // Phase 5: q = trunc(clamp(act / scale)), one byte per (token, column)
+          tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 64; ++j) {
-          const int t = col_begin + j;
-          if (j < my_cols && t < ch.rows) {
-            const float scale = __shfl_sync(0xffffffffu, scale_r[j >> 5], j & 31);
-            float r = __fdiv_rn(act[j], scale);
-            r = fminf(fmaxf(r, -128.0f), 127.0f);
-            p.act_q[((int64_t)ch.row0 + t) * I + (int64_t)nt * TILE_N + n_local] = (int8_t)__float2int_rz(r);
+          for (int j = 0; j < 16; ++j) {
+            const int t = col_begin + pc * 16 + j;
+            const float scale = __shfl_sync(0xffffffffu, scale_r, j);
+            if (t < ch.rows) {
+              float r = __fdiv_rn(__uint_as_float(av[j]), scale);
+              r = fminf(fmaxf(r, -128.0f), 127.0f);
+              p.act_q[((int64_t)ch.row0 + t) * I + (int64_t)nt * TILE_N + n_local] = (int8_t)__float2int_rz(r);
+            }
           }
         }
       } else {
+#pragma unroll 1
+        for (int pc = 0; pc < my_p; ++pc) {
+          uint32_t av[16];
+          tmem_ld16(acc0 + pc * 16, av);
+          tmem_ld_wait();
 #pragma unroll
-        for (int j2 = 0; j2 < 32; ++j2) {
-          float v2[2];
-          unpack2(acc2[0][j2], v2[0], v2[1]);
-#pragma unroll
-          for (int e = 0; e < 2; ++e) {
-            const int j = j2 * 2 + e;
-            if (j < my_cols) {
-              const int32_t sid = __shfl_sync(0xffffffffu, sid_r[j >> 5], j & 31);
-              const float wgt = __shfl_sync(0xffffffffu, wgt_r[j >> 5], j & 31);
-              if (sid >= 0) {
-                float v = v2[e];
-                if (p.weight_mode == LO_WEIGHT_FP32) {
-                  v = v * wgt;
-                } else if (p.weight_mode == LO_WEIGHT_BF16_PRODUCT) {
-                  v = bf16_round(v) * bf16_round(wgt);
-                }
-                p.C[(int64_t)sid * p.n_rows_per_expert + (int64_t)nt * TILE_N + n_local] = __float2bfloat16_rn(v);
+          for (int j = 0; j < 16; ++j) {
+            const int32_t sid = __shfl_sync(0xffffffffu, sid_r, pc * 16 + j);
+            const float wgt = __shfl_sync(0xffffffffu, wgt_r, pc * 16 + j);
+            if (sid >= 0) {
+              float v = __uint_as_float(av[j]);
+              if (p.weight_mode == LO_WEIGHT_FP32) {
+                v = v * wgt;
+              } else if (p.weight_mode == LO_WEIGHT_BF16_PRODUCT) {
+                v = bf16_round(v) * bf16_round(wgt);
               }
+              p.C[(int64_t)sid * p.n_rows_per_expert + (int64_t)nt * TILE_N + n_local] = __float2bfloat16_rn(v);
             }
           }
         }
       }
+      // Column ownership changes from item to item (it depends on the chunk size), so the next item's
+      // first K block may store running sums into columns another warp is still reading in the passes
+      // above: all promotion warps meet before any of them goes on.
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.isync);
+      if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.isync, item_par, p.status, 11))) { ok = false; break; }
       item_par ^= 1u;
     }
   }
