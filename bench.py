@@ -307,6 +307,10 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
+    # NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION; stdout carries the one JSON line only
+    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+        os.environ["NCCL_DEBUG"] = "WARN"
+
     if args.impl == "reference":
         if args.steps > 3:
             args.steps = 3          # each step is seconds of CPU work
@@ -317,6 +321,10 @@ def main():
     line = run_ours(args, rank, world, local_rank)
     if line is not None and rank == 0:
         print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+        if dist.is_initialized():
+            dist.destroy_process_group()
 
 
 if __name__ == "__main__":
