@@ -59,7 +59,9 @@ constexpr int W_TILE_BYTES = TILE_N * TILE_K;   // 16 KiB
 constexpr uint32_t TMEM_COLS = 512;
 // 2^23 + 2^22: adding it to an int32 of magnitude < 2^22 and reading the bits as fp32 gives
 // 12582912 + value exactly, so (that - 12582912.0f) is the exact int->float conversion
-// (|128-long int8 dot| <= 128 * 127 * 127 < 2^21).
+// (|128-long int8 dot| <= 128 * 127 * 127 < 2^21).  The addition costs nothing: every partial
+// buffer holds MAGIC_I whenever it is free (filled at start-up, refilled by the promotion warps
+// right after they read a partial) and all MMAs accumulate, so the tensor core adds it.
 constexpr uint32_t MAGIC_I = 0x4B400000u;
 constexpr float MAGIC_F = 12582912.0f;
 
@@ -113,14 +115,17 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+// One poll.  The suspend-time hint lets the hardware park the thread until the phase completes (or the
+// hint runs out) instead of returning at once: waiting warps then stop competing for issue slots
+// with the warps that have work (without it, polling made up most of the executed instructions).
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(200000u)
       : "memory");
   return ok != 0;
 }
@@ -230,6 +235,14 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
         "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
       : "memory");
 }
+// Store one value to 16 consecutive tensor-memory columns of this thread's lane.
+__device__ __forceinline__ void tmem_st16_fill(uint32_t taddr, uint32_t v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
+      ::"r"(taddr), "r"(v)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Packed fp32 pair arithmetic (two IEEE round-to-nearest operations per instruction).
@@ -326,6 +339,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = sm.tmem_base;
+  if (warp >= 4) {
+    // fill every partial buffer with the conversion offset (see MAGIC_I)
+    const uint32_t base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + ACC_COLS;
+    for (int pc = (warp - 4) >> 2; pc < NBUF * A_ROWS / 16; pc += 4) tmem_st16_fill(base + pc * 16, MAGIC_I);
+    tmem_st_wait();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
 
   const int num_chunks = *p.num_chunks;
   const int64_t num_items = (int64_t)num_chunks * p.n_tiles;
@@ -384,7 +406,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
               const uint32_t d = tmem_base + ACC_COLS + b * (uint32_t)A_ROWS;
 #pragma unroll
               for (int k4 = 0; k4 < TILE_K / 32; ++k4)
-                umma_i8(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, k4 > 0 ? 1u : 0u);
+                umma_i8(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, 1u);
               umma_commit(&sm.tmem_full[b]);
             }
             if (!ok) break;
@@ -542,14 +564,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
               for (int j = 0; j < 16; ++j) accv[j] = 0u;
             }
             tmem_ld_wait();
+            tmem_st16_fill(part + pc * 16, MAGIC_I);   // hand the buffer back ready for the next accumulation
             const ulonglong2 *scv = reinterpret_cast<const ulonglong2 *>(&sm.sc[slot][w][col_begin + pc * 16]);
 #pragma unroll
             for (int j4 = 0; j4 < 4; ++j4) {
               const ulonglong2 sc = scv[j4];     // scale products of four tokens
               const uint32_t *r = &raw[j4 * 4];
-              // exact int -> float: bits(int + MAGIC_I) read as fp32, minus MAGIC_F
-              const uint64_t f01 = add2(pack2(__uint_as_float(r[0] + MAGIC_I), __uint_as_float(r[1] + MAGIC_I)), neg_magic2);
-              const uint64_t f23 = add2(pack2(__uint_as_float(r[2] + MAGIC_I), __uint_as_float(r[3] + MAGIC_I)), neg_magic2);
+              // exact int -> float: the partial already carries MAGIC_I; read as fp32, minus MAGIC_F
+              const uint64_t f01 = add2(pack2(__uint_as_float(r[0]), __uint_as_float(r[1])), neg_magic2);
+              const uint64_t f23 = add2(pack2(__uint_as_float(r[2]), __uint_as_float(r[3])), neg_magic2);
               const uint64_t a01 = add2(pack2(__uint_as_float(accv[j4 * 4 + 0]), __uint_as_float(accv[j4 * 4 + 1])),
                                         mul2_rounded(f01, sc.x, negzero2));
               const uint64_t a23 = add2(pack2(__uint_as_float(accv[j4 * 4 + 2]), __uint_as_float(accv[j4 * 4 + 3])),
