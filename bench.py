@@ -61,7 +61,7 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
             return
@@ -162,20 +162,55 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         out_holder["y"] = lightop_b200.moe.fused_experts_impl_int8(
             x, w1, w2, tw, ti, cache13, use_int8_w8a8=True, block_shape=[128, 128], w1_scale=w1_s, w2_scale=w2_s)
 
-    # end-to-end arm: pinned host buffers in, pinned host buffer out
+    # end-to-end arm: pinned host buffers in, pinned host buffer out.  Every step copies its own x and
+    # logits in and its own y out; steps are independent, so the copies of neighbouring steps overlap
+    # the compute of the current one (two device buffer sets, one stream each for H2D and D2H).
     x_h = x.cpu().pin_memory()
     l_h = logits.cpu().pin_memory()
-    y_h = torch.empty(M, H, dtype=torch.bfloat16).pin_memory()
-    x_d = torch.empty_like(x)
-    l_d = torch.empty_like(logits)
+    y_h = [torch.empty(M, H, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    x_d = [torch.empty_like(x) for _ in range(2)]
+    l_d = [torch.empty_like(logits) for _ in range(2)]
+    tw2 = [torch.empty_like(tw) for _ in range(2)]
+    ti2 = [torch.empty_like(ti) for _ in range(2)]
+    c13 = [cache13, torch.empty_like(cache13)]
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
 
-    def step_e2e():
-        x_d.copy_(x_h, non_blocking=True)
-        l_d.copy_(l_h, non_blocking=True)
-        lightop_b200.moe.topk_softmax(tw, ti, None, l_d, True)
-        y = lightop_b200.moe.fused_experts_impl_int8(
-            x_d, w1, w2, tw, ti, cache13, use_int8_w8a8=True, block_shape=[128, 128], w1_scale=w1_s, w2_scale=w2_s)
-        y_h.copy_(y, non_blocking=True)
+    def run_e2e(steps):
+        """Returns device milliseconds from the first H2D copy to the last D2H copy of `steps` steps."""
+        in_done = [torch.cuda.Event() for _ in range(steps)]
+        comp_done = [torch.cuda.Event() for _ in range(steps)]
+        out_done = [torch.cuda.Event() for _ in range(steps)]
+        keep = []
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        t0.record(stream)
+        s_in.wait_event(t0)
+        for i in range(steps):
+            b = i & 1
+            with torch.cuda.stream(s_in):
+                if i >= 2:
+                    s_in.wait_event(comp_done[i - 2])       # the buffers of step i-2 are free again
+                x_d[b].copy_(x_h, non_blocking=True)
+                l_d[b].copy_(l_h, non_blocking=True)
+                in_done[i].record(s_in)
+            stream.wait_event(in_done[i])
+            if i >= 2:
+                stream.wait_event(out_done[i - 2])          # y of step i-2 has left the device
+            lightop_b200.moe.topk_softmax(tw2[b], ti2[b], None, l_d[b], True)
+            y = lightop_b200.moe.fused_experts_impl_int8(
+                x_d[b], w1, w2, tw2[b], ti2[b], c13[b], use_int8_w8a8=True, block_shape=[128, 128],
+                w1_scale=w1_s, w2_scale=w2_s)
+            keep.append(y)
+            comp_done[i].record(stream)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(comp_done[i])
+                y_h[b].copy_(y, non_blocking=True)
+                out_done[i].record(s_out)
+        stream.wait_event(out_done[steps - 1])
+        t1.record(stream)
+        torch.cuda.synchronize()
+        return t0.elapsed_time(t1)
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -188,9 +223,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     clocks = sampler.stop()
     ms_per_step = total_ms / args.steps
 
-    for _ in range(3):
-        step_e2e()
-    e2e_ms = cuda_time_ms(step_e2e, args.steps, stream) / args.steps
+    run_e2e(3)
+    e2e_ms = run_e2e(args.steps) / args.steps
 
     # per-kernel durations of the fused call (separate pass, events between its kernels)
     lib = _lib.load()
@@ -240,7 +274,8 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "layer_alg_gbs": layer_bytes / (ms_per_step * 1e-3) / 1e9,
         "layer_frac_of_hbm_roofline": layer_bytes / (ms_per_step * 1e-3) / 1e9 / hbm_peak,
         "e2e": {"value": M / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
-                "h2d_bytes_per_step": x_h.numel() * 2 + l_h.numel() * 4, "d2h_bytes_per_step": y_h.numel() * 2},
+                "h2d_bytes_per_step": x_h.numel() * 2 + l_h.numel() * 4, "d2h_bytes_per_step": y_h[0].numel() * 2,
+                "overlap": "copies of neighbouring steps overlap compute (double-buffered, 3 streams)"},
         "gpu_launches": 6 * args.steps,
         "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
     }
@@ -300,7 +335,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override the token count M of the workload")
     ap.add_argument("--experts", type=int, default=0, help="override the expert count E (small profiling cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--cpu-sample-experts", type=int, default=8)
+    ap.add_argument("--cpu-sample-experts", type=int, default=64)
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
