@@ -335,7 +335,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=0, help="override the token count M of the workload")
     ap.add_argument("--experts", type=int, default=0, help="override the expert count E (small profiling cases)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--cpu-sample-experts", type=int, default=64)
+    ap.add_argument("--cpu-sample-experts", type=int, default=256)
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
