@@ -66,7 +66,7 @@ int launch_align(const void *topk_ids, int ids_dtype, int64_t numel, int num_exp
                  const int32_t *expert_map, int map_mode, int32_t *sorted_ids, int64_t sorted_capacity,
                  int32_t *expert_ids, int64_t expert_ids_capacity, int32_t *num_tokens_post_pad,
                  Chunk *chunks, int32_t *num_chunks, int64_t chunk_capacity, int32_t *inv_pos,
-                 cudaStream_t stream);
+                 int chunk_max, cudaStream_t stream);
 
 // Group quantisation of bf16 rows [M, H] written straight into the expert-sorted layout:
 // the int8 row and its scales of token t go to every position inv_pos[t * topk + j] >= 0.  quant.cu

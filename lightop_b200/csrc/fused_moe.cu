@@ -41,7 +41,7 @@ FusedLayout carve_fused(void *ws, int64_t M, int num_experts_for_align, int topk
   Carver c(ws);
   const int64_t numel = M * topk;
   L.sorted_cap = numel + (int64_t)num_experts_for_align * (FUSED_ALIGN_BLOCK - 1);
-  L.chunk_cap = numel / 128 + num_experts_for_align + 1;
+  L.chunk_cap = numel / 32 + num_experts_for_align + 1;   // enough for the smallest chunk size (32 rows)
   L.header = c.take<int32_t>(64);
   L.xq = c.take<int8_t>(L.sorted_cap * H);
   L.xs = c.take<float>(L.sorted_cap * (H / 128));
@@ -142,11 +142,15 @@ extern "C" int lo_fused_moe_block_int8(const void *x, const int8_t *w1, const in
   const int64_t numel = M * topk;
   int rc;
 
+  // Largest chunk of one expert's rows handed to a CTA.  128 (the MMA N limit used here) is best at every
+  // size measured: an M=128, K=32 MMA costs the same ~96 cycles for any N <= 128, so smaller chunks only
+  // multiply the MMA count (64 -> 1.3x, 32 -> 1.9x the layer time at 128 rows per expert).
+  const int chunk_max = 128;
   // 1. expert-major stable order, chunk table, position of every (token, slot)
   prof_mark(0, st);
   rc = launch_align(topk_ids, ids_dtype, numel, align_E, FUSED_ALIGN_BLOCK, expert_map, expert_map ? 1 : 0,
                     L.sorted_ids, L.sorted_cap, nullptr, 0, L.header, L.chunks, L.header + 1, L.chunk_cap, L.inv_pos,
-                    st);
+                    chunk_max, st);
   if (rc != LO_OK) return rc;
 
   // 2. activations -> int8 + per-128 scales, written once per routed slot into sorted order so
@@ -159,7 +163,7 @@ extern "C" int lo_fused_moe_block_int8(const void *x, const int8_t *w1, const in
   prof_mark(2, st);
   GemmArgs g1{};
   g1.A = L.xq; g1.a_scale = L.xs; g1.rows_a = L.sorted_cap;
-  g1.max_chunk_rows = (int)(M < 128 ? M : 128);   // an expert receives at most one row per token
+  g1.max_chunk_rows = (int)(M < chunk_max ? M : chunk_max);   // an expert receives at most one row per token
   g1.B = w1; g1.b_scale = w1_scale; g1.E = E_local;
   g1.n_rows_per_expert = 2 * I; g1.K = H; g1.n_tiles = (int)(I / 128);
   g1.sorted_ids = L.sorted_ids; g1.numel_valid = numel;
@@ -344,15 +348,19 @@ extern "C" int lo_expert_rows_block_int8(const int8_t *xq, const float *xs, cons
   FusedLayout L = carve_fused(workspace, T, E_local, 1, H, I);
   LO_REQUIRE(workspace_bytes >= L.bytes, "expert rows: workspace of %zu bytes, %zu needed", workspace_bytes, L.bytes);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // Largest chunk of one expert's rows handed to a CTA.  128 (the MMA N limit used here) is best at every
+  // size measured: an M=128, K=32 MMA costs the same ~96 cycles for any N <= 128, so smaller chunks only
+  // multiply the MMA count (64 -> 1.3x, 32 -> 1.9x the layer time at 128 rows per expert).
+  const int chunk_max = 128;
   // 1. expert-major stable order of the rows (ids outside [0, E_local) are dropped)
   int rc = launch_align(row_expert, LO_I32, T, E_local, FUSED_ALIGN_BLOCK, nullptr, 0, L.sorted_ids, L.sorted_cap,
-                        nullptr, 0, L.header, L.chunks, L.header + 1, L.chunk_cap, nullptr, st);
+                        nullptr, 0, L.header, L.chunks, L.header + 1, L.chunk_cap, nullptr, chunk_max, st);
   if (rc != LO_OK) return rc;
   // 2. rows and scales into sorted order
   rc = launch_permute_rows(xq, xs, T, H, L.sorted_ids, L.sorted_cap, L.header, T, 1, L.xq, L.xs, st);
   if (rc != LO_OK) return rc;
   GemmArgs g1{};
-  g1.A = L.xq; g1.a_scale = L.xs; g1.rows_a = L.sorted_cap; g1.max_chunk_rows = (int)(T < 128 ? T : 128);
+  g1.A = L.xq; g1.a_scale = L.xs; g1.rows_a = L.sorted_cap; g1.max_chunk_rows = (int)(T < chunk_max ? T : chunk_max);
   g1.B = w1; g1.b_scale = w1_scale; g1.E = E_local;
   g1.n_rows_per_expert = 2 * I; g1.K = H; g1.n_tiles = (int)(I / 128);
   g1.sorted_ids = L.sorted_ids; g1.numel_valid = T;

@@ -146,7 +146,7 @@ __global__ void __launch_bounds__(ALIGN_WARPS * 32) align_kernel(
     const IdT *__restrict__ ids, int64_t numel, int E, int block_size, const int32_t *__restrict__ expert_map,
     int map_mode, int32_t *__restrict__ sorted_ids, int64_t sorted_capacity, int32_t *__restrict__ expert_ids,
     int64_t expert_ids_capacity, int32_t *__restrict__ num_tokens_post_pad, Chunk *__restrict__ chunks,
-    int32_t *__restrict__ num_chunks, int64_t chunk_capacity, int32_t *__restrict__ inv_pos) {
+    int32_t *__restrict__ num_chunks, int64_t chunk_capacity, int32_t *__restrict__ inv_pos, int chunk_max) {
   extern __shared__ int32_t smem[];
   int32_t *hist = smem;                       // [ALIGN_WARPS][E]
   int32_t *seg_off = smem + ALIGN_WARPS * E;  // [E + 1] padded exclusive offsets
@@ -192,7 +192,7 @@ __global__ void __launch_bounds__(ALIGN_WARPS * 32) align_kernel(
   {
     const int c = tid < E ? count[tid] : 0;
     const int padded = (c + block_size - 1) / block_size * block_size;
-    const int nch = (c + 127) / 128;
+    const int nch = (c + chunk_max - 1) / chunk_max;
     int a = padded, b = nch;
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
@@ -247,7 +247,7 @@ __global__ void __launch_bounds__(ALIGN_WARPS * 32) align_kernel(
       // the rows of an expert are cut into equal chunks (rounded up to the MMA N granule of 16):
       // chunks of one expert then take about the same time and read the weight tiles together
       const int c = count[e];
-      const int nch = (c + 127) / 128;
+      const int nch = (c + chunk_max - 1) / chunk_max;
       const int per = nch > 0 ? (((c + nch - 1) / nch) + 15) / 16 * 16 : 0;
       int ci = chunk_off[e];
       for (int r = 0; r < c; r += per, ++ci) {
@@ -309,7 +309,8 @@ int launch_align(const void *topk_ids, int ids_dtype, int64_t numel, int num_exp
                  const int32_t *expert_map, int map_mode, int32_t *sorted_ids, int64_t sorted_capacity,
                  int32_t *expert_ids, int64_t expert_ids_capacity, int32_t *num_tokens_post_pad,
                  Chunk *chunks, int32_t *num_chunks, int64_t chunk_capacity, int32_t *inv_pos,
-                 cudaStream_t stream) {
+                 int chunk_max, cudaStream_t stream) {
+  if (chunk_max != 32 && chunk_max != 64) chunk_max = 128;
   LO_REQUIRE(num_experts >= 1 && num_experts <= 1024, "moe_align: num_experts %d outside [1,1024]", num_experts);
   LO_REQUIRE(block_size >= 1, "moe_align: block_size must be positive");
   LO_REQUIRE(numel >= 0 && numel < (1LL << 30), "moe_align: numel out of range");
@@ -326,7 +327,7 @@ int launch_align(const void *topk_ids, int ids_dtype, int64_t numel, int num_exp
     }
     align_kernel<int32_t><<<1, ALIGN_WARPS * 32, smem, stream>>>(
         static_cast<const int32_t *>(topk_ids), numel, num_experts, block_size, expert_map, map_mode, sorted_ids,
-        sorted_capacity, expert_ids, expert_ids_capacity, num_tokens_post_pad, chunks, num_chunks, chunk_capacity, inv_pos);
+        sorted_capacity, expert_ids, expert_ids_capacity, num_tokens_post_pad, chunks, num_chunks, chunk_capacity, inv_pos, chunk_max);
   } else if (ids_dtype == LO_I64) {
     static thread_local size_t set64 = 0;
     if (smem > 48 * 1024 && smem > set64) {
@@ -336,7 +337,7 @@ int launch_align(const void *topk_ids, int ids_dtype, int64_t numel, int num_exp
     }
     align_kernel<int64_t><<<1, ALIGN_WARPS * 32, smem, stream>>>(
         static_cast<const int64_t *>(topk_ids), numel, num_experts, block_size, expert_map, map_mode, sorted_ids,
-        sorted_capacity, expert_ids, expert_ids_capacity, num_tokens_post_pad, chunks, num_chunks, chunk_capacity, inv_pos);
+        sorted_capacity, expert_ids, expert_ids_capacity, num_tokens_post_pad, chunks, num_chunks, chunk_capacity, inv_pos, chunk_max);
   } else {
     return fail(LO_ERR_UNSUPPORTED, "moe_align: unsupported id dtype code %d", ids_dtype);
   }
@@ -382,5 +383,5 @@ extern "C" int lo_moe_align_block_size(const void *topk_ids, int ids_dtype, int6
                                        int64_t expert_ids_capacity, int32_t *num_tokens_post_pad, void *stream) {
   return lo::launch_align(topk_ids, ids_dtype, numel, num_experts, block_size, expert_map, map_mode, sorted_ids,
                           sorted_capacity, expert_ids, expert_ids_capacity, num_tokens_post_pad, nullptr, nullptr,
-                          0, nullptr, static_cast<cudaStream_t>(stream));
+                          0, nullptr, 128, static_cast<cudaStream_t>(stream));
 }
