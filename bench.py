@@ -352,20 +352,25 @@ def main():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
 
-    # NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION; stdout carries the one JSON line only
-    if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-        os.environ["NCCL_DEBUG"] = "WARN"
+    # stdout carries the one JSON line only: anything a library prints to file descriptor 1 (NCCL's
+    # version banner, for one) goes to stderr; the line itself is written to the saved descriptor.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(line):
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
 
     if args.impl == "reference":
         if args.steps > 3:
             args.steps = 3          # each step is seconds of CPU work
         line = run_reference(args, rank, world)
         if line is not None:
-            print(json.dumps(line), flush=True)
+            emit(line)
         return
     line = run_ours(args, rank, world, local_rank)
     if line is not None and rank == 0:
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         import torch.distributed as dist
         if dist.is_initialized():
