@@ -57,5 +57,19 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+def build_tools(force: bool = False) -> str:
+    """Compile the stand-alone MMA-peak micro-benchmark (not part of the library)."""
+    src = os.path.join(CSRC, "bench_mma_peak.cu")
+    exe = os.path.join(CSRC, "bench_mma_peak")
+    if force or not os.path.exists(exe) or os.path.getmtime(src) > os.path.getmtime(exe):
+        res = subprocess.run([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-o", exe, src],
+                             stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"nvcc failed on bench_mma_peak.cu:\n{res.stdout}")
+    return exe
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--tools" in sys.argv:
+        print(build_tools(force="--force" in sys.argv))
