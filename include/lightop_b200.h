@@ -211,6 +211,20 @@ int lo_expert_rows_block_int8(const int8_t *xq, const float *xs, const int32_t *
                               int32_t *status, void *stream);
 
 /*
+ * Dense block-INT8 linear: C[m, n] = sum_kb (A_q[m, kb] . B_q[n, kb]) * a_s[m, kb] * b_s[n/128, kb], bf16 out.
+ * Replaces: the dense block-INT8 matmul of the reference -- matmul_block_int8 / apply_w8a8_block_int8_linear
+ *           (python/lightop/_lmslim_native/layers/gemm/int8_utils.py:298-429) and gemm_w8a8_asm
+ *           (python/lightop/gemmopt.py:633-639, csrc/asm/asm_gemm_w8a8.cu:136-147).
+ * A [M,K] int8, a_scale [M,K/128] f32 (row-major), B [N,K] int8, b_scale [ceil(N/128), K/128] f32, C [M,N] bf16.
+ * K a multiple of 128; N arbitrary (weight rows past N read as zero and are not stored).
+ * Same kernel as the grouped GEMM with one expert.  workspace: lo_block_int8_linear_workspace_bytes(M).
+ */
+size_t lo_block_int8_linear_workspace_bytes(int64_t M);
+int lo_block_int8_linear(const int8_t *A, const float *a_scale, const int8_t *B, const float *b_scale,
+                         int64_t M, int64_t N, int64_t K, void *C, void *workspace, size_t workspace_bytes,
+                         int32_t *status, void *stream);
+
+/*
  * Per-stage timing of lo_fused_moe_block_int8 for benchmarks: while enabled (per host thread), the
  * call records CUDA events between its five kernels (align, group quant, gate_up GEMM, down GEMM,
  * top-k sum); lo_profile_read waits for the last one and returns the five durations in

@@ -52,6 +52,9 @@ PROTOTYPES = {
     "lo_expert_rows_block_int8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                           c_void_p, c_int64, c_int, c_int64, c_int64, c_void_p, c_void_p, c_size_t,
                                           c_void_p, c_void_p]),
+    "lo_block_int8_linear_workspace_bytes": (c_size_t, [c_int64]),
+    "lo_block_int8_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p,
+                                     c_void_p, c_size_t, c_void_p, c_void_p]),
     "lo_profile_enable": (c_int, [c_int]),
     "lo_profile_read": (c_int, [c_void_p]),
     "lo_ep_scatter": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,

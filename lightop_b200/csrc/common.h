@@ -94,6 +94,7 @@ struct GemmArgs {
   const float *b_scale;     // [E, n_rows_per_expert/128, K/128]
   int E;
   int64_t n_rows_per_expert;   // 2I for gate_up, N for single
+  int64_t n_store;             // 0 = n_rows_per_expert; output row length when N is not a multiple of 128 (E == 1 only)
   int64_t K;
   int n_tiles;              // 128-row output tiles per item: I/128 (gate_up) or N/128
   const int32_t *sorted_ids;

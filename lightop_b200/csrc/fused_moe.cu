@@ -383,3 +383,69 @@ extern "C" int lo_expert_rows_block_int8(const int8_t *xq, const float *xs, cons
   g2.status = status;
   return launch_grouped_gemm(GEMM_SINGLE, g2, st);
 }
+
+// ---------------------------------------------------------------------------
+// Dense block-INT8 linear: the grouped GEMM with a single "expert" that owns every row.
+// ---------------------------------------------------------------------------
+namespace lo {
+namespace {
+__global__ void linear_plan_kernel(int64_t M, int32_t *__restrict__ sorted_ids, Chunk *__restrict__ chunks,
+                                   int32_t *__restrict__ num_chunks) {
+  const int64_t n_chunks = (M + 127) / 128;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < M; i += (int64_t)gridDim.x * blockDim.x)
+    sorted_ids[i] = (int32_t)i;
+  for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < n_chunks; c += (int64_t)gridDim.x * blockDim.x) {
+    Chunk ch;
+    ch.expert = 0;
+    ch.row0 = (int32_t)(c * 128);
+    ch.rows = (int32_t)(M - c * 128 < 128 ? M - c * 128 : 128);
+    ch.pad = 0;
+    chunks[c] = ch;
+  }
+  if (blockIdx.x == 0 && threadIdx.x == 0) *num_chunks = (int32_t)n_chunks;
+}
+struct LinearWs {
+  int32_t *num_chunks;
+  int32_t *sorted_ids;
+  Chunk *chunks;
+  size_t bytes;
+};
+LinearWs carve_linear(void *ws, int64_t M) {
+  LinearWs W;
+  Carver c(ws);
+  W.num_chunks = c.take<int32_t>(64);
+  W.sorted_ids = c.take<int32_t>(M);
+  W.chunks = c.take<Chunk>((M + 127) / 128 + 1);
+  W.bytes = c.off;
+  return W;
+}
+}  // namespace
+}  // namespace lo
+
+extern "C" size_t lo_block_int8_linear_workspace_bytes(int64_t M) { return M <= 0 ? 0 : lo::carve_linear(nullptr, M).bytes; }
+
+extern "C" int lo_block_int8_linear(const int8_t *A, const float *a_scale, const int8_t *B, const float *b_scale,
+                                    int64_t M, int64_t N, int64_t K, void *C, void *workspace, size_t workspace_bytes,
+                                    int32_t *status, void *stream) {
+  using namespace lo;
+  LO_REQUIRE(M >= 0 && N >= 1 && K >= 128 && K % 128 == 0, "block int8 linear: bad shape (K must be a multiple of 128)");
+  if (M == 0) return LO_OK;
+  LO_REQUIRE(A && a_scale && B && b_scale && C && workspace, "block int8 linear: null pointer");
+  LO_REQUIRE(M < (1LL << 30), "block int8 linear: too many rows");
+  LO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & (ALIGN_BYTES - 1)) == 0, "block int8 linear: workspace must be 256-byte aligned");
+  LinearWs W = carve_linear(workspace, M);
+  LO_REQUIRE(workspace_bytes >= W.bytes, "block int8 linear: workspace of %zu bytes, %zu needed", workspace_bytes, W.bytes);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int blocks = (int)(ceil_div(M, 256) > 1024 ? 1024 : ceil_div(M, 256));
+  linear_plan_kernel<<<blocks, 256, 0, st>>>(M, W.sorted_ids, W.chunks, W.num_chunks);
+  LO_LAUNCH_OK("linear_plan_kernel");
+  GemmArgs g{};
+  g.A = A; g.a_scale = a_scale; g.rows_a = M; g.max_chunk_rows = (int)(M < 128 ? M : 128);
+  g.B = B; g.b_scale = b_scale; g.E = 1;
+  g.n_rows_per_expert = N; g.n_store = N; g.K = K; g.n_tiles = (int)ceil_div(N, 128);
+  g.sorted_ids = W.sorted_ids; g.numel_valid = M;
+  g.chunks = W.chunks; g.num_chunks = W.num_chunks;
+  g.C = static_cast<__nv_bfloat16 *>(C);
+  g.weight_mode = LO_WEIGHT_NONE; g.status = status;
+  return launch_grouped_gemm(GEMM_SINGLE, g, st);
+}

@@ -276,6 +276,7 @@ struct KParams {
   const float *a_scale;     // [positions, KB]
   const float *b_scale;
   int64_t n_rows_per_expert;
+  int64_t n_store;          // output columns that exist (< n_tiles*128 only for a dense E = 1 call)
   int KB;
   int n_tiles;
   const int32_t *sorted_ids;
@@ -422,7 +423,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       uint32_t it = 0;
       bool ok = true;
       const bool vec4 = (KB & 3) == 0;
-      const int64_t nblk = p.n_rows_per_expert / TILE_N;
+      const int64_t nblk = (p.n_rows_per_expert + TILE_N - 1) / TILE_N;
       for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
         const Chunk ch = p.chunks[item / p.n_tiles];
         const int nt = (int)(item % p.n_tiles);
@@ -514,7 +515,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           for (int t = cg; t < ch.rows; t += 4) {
             const int32_t sid = p.sorted_ids[ch.row0 + t];
             if (sid >= 0 && sid < p.numel_valid)
-              p.C[(int64_t)sid * p.n_rows_per_expert + (int64_t)nt * TILE_N + n_local] = __float2bfloat16_rn(0.f);
+              p.C[(int64_t)sid * p.n_store + (int64_t)nt * TILE_N + n_local] = __float2bfloat16_rn(0.f);
           }
         }
         continue;
@@ -677,7 +678,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
               } else if (p.weight_mode == LO_WEIGHT_BF16_PRODUCT) {
                 v = bf16_round(v) * bf16_round(wgt);
               }
-              p.C[(int64_t)sid * p.n_rows_per_expert + (int64_t)nt * TILE_N + n_local] = __float2bfloat16_rn(v);
+              if ((int64_t)nt * TILE_N + n_local < p.n_store)
+                p.C[(int64_t)sid * p.n_store + (int64_t)nt * TILE_N + n_local] = __float2bfloat16_rn(v);
             }
           }
         }
@@ -768,7 +770,7 @@ int launch_mode(const GemmArgs &a, cudaStream_t stream) {
   }
   KParams p;
   p.a_scale = a.a_scale; p.b_scale = a.b_scale;
-  p.n_rows_per_expert = a.n_rows_per_expert; p.KB = (int)(a.K / TILE_K); p.n_tiles = a.n_tiles;
+  p.n_rows_per_expert = a.n_rows_per_expert; p.n_store = a.n_store > 0 ? a.n_store : a.n_rows_per_expert; p.KB = (int)(a.K / TILE_K); p.n_tiles = a.n_tiles;
   p.sorted_ids = a.sorted_ids; p.numel_valid = a.numel_valid;
   p.chunks = a.chunks; p.num_chunks = a.num_chunks; p.act_q = a.act_q; p.act_s = a.act_s; p.C = a.C;
   p.topk_weights = a.topk_weights; p.weight_mode = a.weight_mode; p.act_eps = a.act_eps; p.status = a.status; p.neg_zero = -0.0f;
@@ -783,7 +785,8 @@ int launch_mode(const GemmArgs &a, cudaStream_t stream) {
 
 int launch_grouped_gemm(GemmMode mode, const GemmArgs &a, cudaStream_t stream) {
   LO_REQUIRE(a.K % TILE_K == 0 && a.K >= TILE_K, "grouped gemm: K=%lld must be a positive multiple of 128", (long long)a.K);
-  LO_REQUIRE(a.n_rows_per_expert % TILE_N == 0, "grouped gemm: N=%lld must be a multiple of 128", (long long)a.n_rows_per_expert);
+  LO_REQUIRE(a.n_rows_per_expert % TILE_N == 0 || (a.E == 1 && mode == GEMM_SINGLE),
+             "grouped gemm: N=%lld must be a multiple of 128", (long long)a.n_rows_per_expert);
   LO_REQUIRE((int64_t)a.E * a.n_rows_per_expert < (1LL << 31), "grouped gemm: E*N exceeds the tensor-map row range");
   LO_REQUIRE(a.rows_a >= 1 && a.rows_a < (1LL << 31), "grouped gemm: activation row count out of range");
   LO_REQUIRE((reinterpret_cast<uintptr_t>(a.B) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.A) & 15) == 0 &&
@@ -798,7 +801,8 @@ int launch_grouped_gemm(GemmMode mode, const GemmArgs &a, cudaStream_t stream) {
     if (cap <= 64) return launch_mode<GEMM_GATE_UP, 64>(a, stream);
     return launch_mode<GEMM_GATE_UP, 128>(a, stream);
   }
-  LO_REQUIRE(a.n_rows_per_expert == (int64_t)a.n_tiles * TILE_N, "grouped gemm: tile count mismatch");
+  LO_REQUIRE((int64_t)a.n_tiles * TILE_N >= a.n_rows_per_expert && (int64_t)(a.n_tiles - 1) * TILE_N < a.n_rows_per_expert,
+             "grouped gemm: tile count mismatch");
   if (cap <= 32) return launch_mode<GEMM_SINGLE, 32>(a, stream);
   if (cap <= 64) return launch_mode<GEMM_SINGLE, 64>(a, stream);
   return launch_mode<GEMM_SINGLE, 128>(a, stream);

@@ -297,3 +297,26 @@ def test_expert_rows_entry_point_and_ep_driver_world1(lo):
         dist.destroy_process_group()
     assert torch.equal(y, base)
     assert_out_close(y, O.fused_moe_block_int8(x, w1, w2, w1_s, w2_s, w, ids), "ep world 1")
+
+
+# ------------------------------ dense block-INT8 linear -------------------------------
+
+@pytest.mark.parametrize("m,n,k", [(1, 576, 7168), (7, 2048, 512), (48, 256, 1024), (128, 7168, 128), (300, 1536, 1536), (1024, 2304, 1152 + 128)])
+def test_dense_block_int8_linear(lo, m, n, k):
+    # shapes from the reference's dense block GEMM test (test/w8a8/test_w8a8_block.py:205-215); N = 576 and 2304
+    # are not multiples of 128
+    g = torch.Generator().manual_seed(m + n)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    aq, a_s = O.group_quant_int8(x, 128)
+    B = torch.randint(-127, 128, (n, k), generator=g, dtype=torch.int8)
+    b_s = torch.rand((n + 127) // 128, k // 128, generator=g) * 9e-3 + 1e-3
+    ref = O.block_int8_matmul(aq, B, a_s, b_s, (128, 128), torch.bfloat16)
+    out = lo.gemm_ops.matmul_block_int8(aq.to(DEV), B.to(DEV), a_s.to(DEV), b_s.to(DEV), [128, 128], torch.bfloat16)
+    torch.cuda.synchronize()
+    lo.check_device_status()
+    assert torch.equal(out.cpu(), ref)          # same fp32 operation sequence as the oracle
+    # the assembly kernel's convention: activation scales transposed; the reference's own bar is allclose(1e-2, 5e-2)
+    out2 = lo.gemm_ops.gemm_w8a8_asm(aq.to(DEV), B.to(DEV), a_s.t().contiguous().to(DEV), b_s.to(DEV), [128, 128], torch.bfloat16)
+    assert torch.equal(out2, out)
+    y = lo.gemm_ops.apply_w8a8_block_int8_linear(x.to(DEV), B.to(DEV), [128, 128], b_s.to(DEV))
+    assert torch.equal(y.cpu(), ref)
