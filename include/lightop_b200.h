@@ -224,6 +224,67 @@ int lo_block_int8_linear(const int8_t *A, const float *a_scale, const int8_t *B,
                          int64_t M, int64_t N, int64_t K, void *C, void *workspace, size_t workspace_bytes,
                          int32_t *status, void *stream);
 
+/* ---------------------------------------------------------------------------
+ * Per-channel W8A8 mode of the same MoE layer (one scale per token, one per output channel).
+ * ------------------------------------------------------------------------- */
+
+/*
+ * Per-token (whole-row) INT8 quantisation: absmax = max(max|x|, 1e-10); s[m] = absmax / 127;
+ * q = rint(x * (127 / absmax)) (round half to even).  x [M, K] f32 / f16 / bf16, any K >= 1.
+ * Replaces: per_token_quant_int8, python/lightop/_lmslim_native/layers/gemm/int8_utils.py:21-71
+ * (exported as lightop.quant.per_token_quant_int8, python/lightop/quant/int8.py:35).
+ */
+int lo_per_token_quant_int8(const void *x, int x_dtype, int64_t M, int64_t K, int8_t *q, float *s, void *stream);
+
+/*
+ * SiLU(gate) * up and per-token INT8 quantisation of bf16 rows [rows, 2*d] (gate columns first):
+ * act = bf16(bf16(silu(gate)) * up); s[row] = max|act| / 127; q = sat(rint(act * (127 / max))); a row of
+ * zeros gets scale 0.  q int8 [rows, d], s f32 [rows].
+ * Replaces: op.fuse_silu_mul_quant, csrc/kernels/gated_activation/fuse_silu_mul_quant.cu:90-131
+ * (python/lightop/fuse_silu_mul_quant.py:44-62), whose reference model is silu_and_mul followed by
+ * a dynamic per-token int8 quantisation (test/test_fuse_silu_mul_quant.py:11-14).
+ */
+int lo_silu_mul_quant_int8(const void *input, int64_t rows, int64_t d, int8_t *q, float *s, void *stream);
+
+/*
+ * Grouped per-channel INT8 GEMM over expert-sorted row blocks:
+ *   C[id, n] = float(sum_k A_q[id / top_k, k] * B_q[e, n, k]) (* w[id] if LO_WEIGHT_FP32) * a_s[id / top_k] * b_s[e, n]
+ * (LO_WEIGHT_BF16_PRODUCT: bf16 of the scaled sum times bf16(w[id])).  a_scale f32 [rows_a], b_scale f32 [E, N];
+ * the other arguments and the workspace (lo_grouped_gemm_workspace_bytes) are those of
+ * lo_moe_grouped_gemm_i8_block.
+ * Replaces: op.moe_gemm_w8a8 (native per-channel MoE GEMM, csrc/moe_gemm/w8a8/moe_w8a8.cu:2389,
+ * python/lightop/gemmopt.py:437-457) and the per_channel_quant branch of the Triton fused_moe_kernel
+ * (python/lightop/_lmslim_native/layers/fused_moe/int8.py:466-474,509,519-532).
+ */
+int lo_moe_grouped_gemm_i8_channel(const int8_t *A, const float *a_scale, int64_t rows_a,
+                                   const int8_t *B, const float *b_scale, int E, int64_t N, int64_t K,
+                                   void *C, const float *topk_weights, int weight_mode,
+                                   const int32_t *sorted_ids, int64_t sorted_capacity,
+                                   const int32_t *expert_ids, const int32_t *num_tokens_post_pad,
+                                   int64_t numel_valid, int top_k, int block_size,
+                                   void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * One chunk of the fused per-channel W8A8 MoE layer: align -> per-token quant -> gate_up GEMM ->
+ * SiLU*mul + per-token quant -> down GEMM (routed weight in fp32 before the scales, as the reference's
+ * kernel does) -> top-k sum.  w1 int8 [E, 2I, H], w2 int8 [E, H, I], w1_scale f32 [E, 2I], w2_scale f32 [E, H];
+ * every other argument as in lo_fused_moe_block_int8 (x_dtype must be LO_BF16).
+ * Replaces: fused_experts_impl_int8 with per_channel_quant=True and block_shape=None
+ * (python/lightop/_lmslim_native/layers/fused_moe/int8.py:735-905) and fused_experts_impl_int8_marlin
+ * (python/lightop/_lmslim_native/layers/fused_moe/int8_marlin.py:165-386; that variant takes weights
+ * pre-shuffled for the reference's matrix cores, this one the plain [E, N, K] layout).
+ */
+size_t lo_fused_moe_channel_workspace_bytes(int64_t M, int E_local, int global_num_experts, int topk,
+                                            int64_t H, int64_t I);
+int lo_fused_moe_channel_int8(const void *x, int x_dtype, const int8_t *w1, const int8_t *w2,
+                              const float *w1_scale, const float *w2_scale,
+                              const float *topk_weights, const void *topk_ids, int ids_dtype,
+                              const int32_t *expert_map, int global_num_experts,
+                              int64_t M, int E_local, int topk, int64_t H, int64_t I,
+                              void *cache3, const void *shared_output, void *out,
+                              int apply_router_weight_on_input, float routed_scaling_factor,
+                              void *workspace, size_t workspace_bytes, int32_t *status, void *stream);
+
 /*
  * Per-stage timing of lo_fused_moe_block_int8 for benchmarks: while enabled (per host thread), the
  * call records CUDA events between its five kernels (align, group quant, gate_up GEMM, down GEMM,

@@ -42,6 +42,6 @@ def check_device_status(device=None) -> None:
         raise _lib.LightopError(f"a grouped-GEMM wait timed out on the device (waiter code {code})")
 
 
-from . import gemm_ops, moe, quant  # noqa: E402
+from . import activation, gemm_ops, moe, quant  # noqa: E402
 
-__all__ = ["gemm_ops", "moe", "quant", "check_device_status", "device_status_word", "__version__"]
+__all__ = ["activation", "gemm_ops", "moe", "quant", "check_device_status", "device_status_word", "__version__"]

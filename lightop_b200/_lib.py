@@ -55,6 +55,16 @@ PROTOTYPES = {
     "lo_block_int8_linear_workspace_bytes": (c_size_t, [c_int64]),
     "lo_block_int8_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p,
                                      c_void_p, c_size_t, c_void_p, c_void_p]),
+    "lo_per_token_quant_int8": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
+    "lo_silu_mul_quant_int8": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
+    "lo_moe_grouped_gemm_i8_channel": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int64,
+                                               c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_void_p,
+                                               c_void_p, c_int64, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "lo_fused_moe_channel_workspace_bytes": (c_size_t, [c_int64, c_int, c_int, c_int, c_int64, c_int64]),
+    "lo_fused_moe_channel_int8": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_void_p, c_int, c_void_p, c_int, c_int64, c_int, c_int, c_int64, c_int64,
+                                          c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_size_t,
+                                          c_void_p, c_void_p]),
     "lo_profile_enable": (c_int, [c_int]),
     "lo_profile_read": (c_int, [c_void_p]),
     "lo_ep_scatter": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,

@@ -1,0 +1,50 @@
+"""Gated-activation entry points of the per-channel W8A8 path
+(reference: python/lightop/activation.py -> python/lightop/fuse_silu_mul_quant.py:44-62)."""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+
+
+def fuse_silu_mul_quant(input: torch.Tensor, num_local_tokens_tensor: Optional[torch.Tensor] = None, topk: int = 1,
+                        expect_m: int = -1, output: Optional[torch.Tensor] = None,
+                        scales: Optional[torch.Tensor] = None, expert_ids: Optional[torch.Tensor] = None
+                        ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``silu(input[:, :d]) * input[:, d:]`` followed by per-token INT8 quantisation.
+
+    Signature of the reference's wrapper (python/lightop/fuse_silu_mul_quant.py:44-62): returns
+    ``(output int8 [rows, d], scales fp32 [rows, 1])``.  Semantics of its kernel
+    (csrc/kernels/gated_activation/fuse_silu_mul_quant.cu:90-131): the activation is rounded to
+    the element type after SiLU and after the product, ``scale = max|act| / 127`` and
+    ``q = sat(rint(act * (127 / max)))``.  The expert-parallel masking arguments
+    (``num_local_tokens_tensor``, ``expect_m``, ``expert_ids``) are not implemented.
+    """
+    if num_local_tokens_tensor is not None or expert_ids is not None:
+        raise NotImplementedError("the expert-parallel masking arguments are not implemented")
+    _lib.require_cuda(input, output, scales)
+    if input.dim() != 2 or input.dtype != torch.bfloat16:
+        raise RuntimeError("fuse_silu_mul_quant expects a 2-D bfloat16 tensor [rows, 2*d]")
+    if not input.is_contiguous():
+        input = input.contiguous()
+    rows, d2 = input.shape
+    d = d2 // 2
+    if d2 % 16 != 0:
+        raise RuntimeError("the row length must be a multiple of 16")
+    if output is None:
+        output = torch.empty(rows, d, dtype=torch.int8, device=input.device)
+    if scales is None:
+        scales = torch.empty((rows, 1), device=input.device, dtype=torch.float32)
+    if output.dtype != torch.int8 or tuple(output.shape) != (rows, d) or not output.is_contiguous():
+        raise RuntimeError("output must be a contiguous int8 tensor [rows, d]")
+    if scales.dtype != torch.float32 or scales.numel() != rows or not scales.is_contiguous():
+        raise RuntimeError("scales must be a contiguous float32 tensor with one value per row")
+    if rows == 0:
+        return output, scales
+    with torch.cuda.device(input.device):
+        st = _lib.load().lo_silu_mul_quant_int8(_lib.ptr(input), rows, d, _lib.ptr(output), _lib.ptr(scales),
+                                                _lib.current_stream(input.device))
+    _lib.check(st, "fuse_silu_mul_quant")
+    return output, scales

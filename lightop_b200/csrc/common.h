@@ -73,17 +73,31 @@ int launch_align(const void *topk_ids, int ids_dtype, int64_t numel, int num_exp
 int launch_group_quant_scatter(const void *x, int64_t M, int64_t H, int topk, const int32_t *inv_pos, float eps,
                                int8_t *q_sorted, float *s_sorted, cudaStream_t stream);
 
-// Copy int8 rows and their scales into sorted-position order: row(pos) = sorted_ids[pos] / top_k.  reduce.cu
+// Per-token (whole-row) quantisation; with inv_pos the result goes to the token's sorted positions
+// (q_out [positions, K], s_out [positions]), without it to row `token`.  quant.cu
+int launch_token_quant(const void *x, int x_dtype, int64_t M, int64_t K, int topk, const int32_t *inv_pos, int8_t *q,
+                       float *s, cudaStream_t stream);
+
+// act = bf16(bf16(silu(gate)) * up) of bf16 rows [rows, 2*d], then per-token quantisation.  Rows at or
+// beyond *num_rows_dev and rows whose row_ids entry is a padding sentinel are skipped (both optional).  quant.cu
+int launch_silu_mul_token_quant(const void *in, int64_t rows, int64_t d, const int32_t *row_ids, int64_t numel_valid,
+                                const int32_t *num_rows_dev, int8_t *q, float *s, cudaStream_t stream);
+
+// Copy int8 rows and their scales into sorted-position order: row(pos) = sorted_ids[pos] / top_k.
+// scales_per_row = 0 means K / 128 (block scales); 1 is the per-token format.  reduce.cu
 int launch_permute_rows(const int8_t *A, const float *a_scale, int64_t rows_a, int64_t K, const int32_t *sorted_ids,
                         int64_t sorted_capacity, const int32_t *num_tokens_post_pad, int64_t numel_valid, int top_k,
-                        int8_t *A_sorted, float *a_scale_sorted, cudaStream_t stream);
+                        int8_t *A_sorted, float *a_scale_sorted, cudaStream_t stream, int64_t scales_per_row = 0);
 
 // Chunk table from an existing (expert_ids, num_tokens_post_pad) pair, see routing.cu.
 int launch_chunks_from_blocks(const int32_t *expert_ids, const int32_t *num_tokens_post_pad,
                               int block_size, int64_t max_blocks, Chunk *chunks, int32_t *num_chunks,
                               cudaStream_t stream);
 
-enum GemmMode { GEMM_GATE_UP = 0, GEMM_SINGLE = 1 };
+// GEMM_GATE_UP / GEMM_SINGLE: 128x128 block scales (a_scale [rows, K/128], b_scale [E, N/128, K/128]).
+// GEMM_CHANNEL: one scale per token and per output channel (a_scale [rows], b_scale [E, N]); bf16 output
+// like GEMM_SINGLE.  In both bf16-output modes sorted_ids may be null: the id of a row is then its position.
+enum GemmMode { GEMM_GATE_UP = 0, GEMM_SINGLE = 1, GEMM_CHANNEL = 2 };
 
 struct GemmArgs {
   const int8_t *A;          // [rows_a, K] int8, rows in sorted-position order (row = position in sorted_ids)
@@ -109,6 +123,7 @@ struct GemmArgs {
   int weight_mode;
   float act_eps;            // eps of the fused re-quantisation, already rounded to bf16
   int32_t *status;          // device word, set non-zero on a wait that ran out (may be null)
+  int out_by_position;      // bf16 output row = sorted position (ids still select validity and the routed weight)
 };
 
 int launch_grouped_gemm(GemmMode mode, const GemmArgs &args, cudaStream_t stream);

@@ -265,6 +265,41 @@ extern "C" int lo_moe_grouped_gemm_i8_block(const int8_t *A, const float *a_scal
   return launch_grouped_gemm(GEMM_SINGLE, g, st);
 }
 
+// Per-channel form of the grouped GEMM: a_scale [rows_a] (one per token), b_scale [E, N].
+extern "C" int lo_moe_grouped_gemm_i8_channel(const int8_t *A, const float *a_scale, int64_t rows_a, const int8_t *B,
+                                              const float *b_scale, int E, int64_t N, int64_t K, void *C,
+                                              const float *topk_weights, int weight_mode, const int32_t *sorted_ids,
+                                              int64_t sorted_capacity, const int32_t *expert_ids,
+                                              const int32_t *num_tokens_post_pad, int64_t numel_valid, int top_k,
+                                              int block_size, void *workspace, size_t workspace_bytes, void *stream) {
+  using namespace lo;
+  LO_REQUIRE(A && a_scale && B && b_scale && C && sorted_ids && expert_ids && num_tokens_post_pad && workspace,
+             "grouped gemm: null pointer");
+  LO_REQUIRE(block_size >= 1 && (block_size <= 128 || block_size % 128 == 0),
+             "grouped gemm: block_size %d must be <= 128 or a multiple of 128", block_size);
+  LO_REQUIRE(top_k >= 1 && E >= 1 && rows_a >= 0 && sorted_capacity >= 1, "grouped gemm: bad shape");
+  LO_REQUIRE(K % 128 == 0 && N % 128 == 0, "grouped gemm: N and K must be multiples of 128");
+  LO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & (ALIGN_BYTES - 1)) == 0, "grouped gemm: workspace must be 256-byte aligned");
+  GemmWs W = carve_gemm(workspace, sorted_capacity, block_size, K);   // as_sorted is larger than needed here
+  LO_REQUIRE(workspace_bytes >= W.bytes, "grouped gemm: workspace of %zu bytes, %zu needed", workspace_bytes, W.bytes);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t max_blocks = ceil_div(sorted_capacity, block_size);
+  int rc = launch_chunks_from_blocks(expert_ids, num_tokens_post_pad, block_size, max_blocks, W.chunks, W.num_chunks, st);
+  if (rc != LO_OK) return rc;
+  rc = launch_permute_rows(A, a_scale, rows_a, K, sorted_ids, sorted_capacity, num_tokens_post_pad, numel_valid, top_k,
+                           W.a_sorted, W.as_sorted, st, 1);
+  if (rc != LO_OK) return rc;
+  GemmArgs g{};
+  g.A = W.a_sorted; g.a_scale = W.as_sorted; g.rows_a = sorted_capacity;
+  g.max_chunk_rows = block_size < 128 ? block_size : 128; g.B = B; g.b_scale = b_scale; g.E = E;
+  g.n_rows_per_expert = N; g.K = K; g.n_tiles = (int)(N / 128);
+  g.sorted_ids = sorted_ids; g.numel_valid = numel_valid;
+  g.chunks = W.chunks; g.num_chunks = W.num_chunks;
+  g.C = static_cast<__nv_bfloat16 *>(C);
+  g.topk_weights = topk_weights; g.weight_mode = weight_mode; g.status = nullptr;
+  return launch_grouped_gemm(GEMM_CHANNEL, g, st);
+}
+
 // ---------------------------------------------------------------------------
 // Fused layer without any caller-supplied or allocated scratch.
 //
@@ -327,6 +362,136 @@ extern "C" int lo_fused_moe_block_int8_noalloc(const void *x, const int8_t *w1, 
   return lo_fused_moe_block_int8(x, w1, w2, w1_scale, w2_scale, topk_weights, topk_ids, ids_dtype, expert_map,
                                  global_num_experts, M, E_local, topk, H, I, cache3, shared_output, out,
                                  apply_router_weight_on_input, routed_scaling_factor, scratch, need, status, stream);
+}
+
+// ---------------------------------------------------------------------------
+// Per-channel W8A8 mode of the same layer: one scale per token (activations) and one per output
+// channel (weights).  The GEMMs accumulate int32 over the whole K extent on the tensor core and
+// apply both scales once in the epilogue; SiLU*mul and the per-token re-quantisation need the
+// maximum of a whole row, so they run as a kernel of their own between the two GEMMs, as in the
+// reference (python/lightop/_lmslim_native/layers/fused_moe/int8.py:771-905).
+// ---------------------------------------------------------------------------
+namespace lo {
+namespace {
+struct ChannelLayout {
+  int32_t *header;      // [0] num_tokens_post_pad, [1] num_chunks
+  int8_t *xq;           // [sorted_cap, H]
+  float *xs;            // [sorted_cap]
+  int32_t *sorted_ids;
+  int32_t *inv_pos;
+  Chunk *chunks;
+  __nv_bfloat16 *cache1;   // [sorted_cap, 2I] gate_up output by sorted position
+  int8_t *act_q;        // [sorted_cap, I]
+  float *act_s;         // [sorted_cap]
+  int64_t sorted_cap;
+  int64_t chunk_cap;
+  size_t bytes;
+};
+ChannelLayout carve_channel(void *ws, int64_t M, int num_experts_for_align, int topk, int64_t H, int64_t I) {
+  ChannelLayout L;
+  Carver c(ws);
+  const int64_t numel = M * topk;
+  L.sorted_cap = numel + (int64_t)num_experts_for_align * (FUSED_ALIGN_BLOCK - 1);
+  L.chunk_cap = numel / 32 + num_experts_for_align + 1;
+  L.header = c.take<int32_t>(64);
+  L.xq = c.take<int8_t>(L.sorted_cap * H);
+  L.xs = c.take<float>(L.sorted_cap);
+  L.sorted_ids = c.take<int32_t>(L.sorted_cap);
+  L.inv_pos = c.take<int32_t>(numel);
+  L.chunks = c.take<Chunk>(L.chunk_cap);
+  L.cache1 = c.take<__nv_bfloat16>(L.sorted_cap * 2 * I);
+  L.act_q = c.take<int8_t>(L.sorted_cap * I);
+  L.act_s = c.take<float>(L.sorted_cap);
+  L.bytes = c.off;
+  return L;
+}
+}  // namespace
+}  // namespace lo
+
+extern "C" size_t lo_fused_moe_channel_workspace_bytes(int64_t M, int E_local, int global_num_experts, int topk,
+                                                       int64_t H, int64_t I) {
+  const int e = global_num_experts > E_local ? global_num_experts : E_local;
+  return lo::carve_channel(nullptr, M, e, topk, H, I).bytes;
+}
+
+extern "C" int lo_fused_moe_channel_int8(const void *x, int x_dtype, const int8_t *w1, const int8_t *w2,
+                                         const float *w1_scale, const float *w2_scale, const float *topk_weights,
+                                         const void *topk_ids, int ids_dtype, const int32_t *expert_map,
+                                         int global_num_experts, int64_t M, int E_local, int topk, int64_t H, int64_t I,
+                                         void *cache3, const void *shared_output, void *out,
+                                         int apply_router_weight_on_input, float routed_scaling_factor, void *workspace,
+                                         size_t workspace_bytes, int32_t *status, void *stream) {
+  using namespace lo;
+  LO_REQUIRE(M >= 0 && E_local >= 1 && topk >= 1, "channel moe: bad shape");
+  if (M == 0) return LO_OK;
+  LO_REQUIRE(x && w1 && w2 && w1_scale && w2_scale && topk_weights && topk_ids && cache3 && out && workspace,
+             "channel moe: null pointer");
+  LO_REQUIRE(x_dtype == LO_BF16, "channel moe: activations must be bfloat16");
+  LO_REQUIRE(H % 128 == 0 && I % 128 == 0, "channel moe: hidden (%lld) and intermediate (%lld) sizes must be multiples of 128",
+             (long long)H, (long long)I);
+  LO_REQUIRE(ids_dtype == LO_I32 || ids_dtype == LO_I64, "channel moe: topk_ids must be int32 or int64");
+  LO_REQUIRE(!apply_router_weight_on_input || topk == 1, "channel moe: apply_router_weight_on_input requires topk == 1");
+  LO_REQUIRE(M * topk < (1LL << 30), "channel moe: too many (token, slot) pairs; split the call into chunks");
+  if (global_num_experts <= 0) global_num_experts = E_local;
+  LO_REQUIRE(expert_map != nullptr || global_num_experts == E_local, "channel moe: global_num_experts != E needs an expert_map");
+  const int align_E = expert_map ? global_num_experts : E_local;
+  LO_REQUIRE(align_E <= 1024, "channel moe: more than 1024 experts");
+  LO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & (ALIGN_BYTES - 1)) == 0, "channel moe: workspace must be 256-byte aligned");
+  ChannelLayout L = carve_channel(workspace, M, align_E, topk, H, I);
+  LO_REQUIRE(workspace_bytes >= L.bytes, "channel moe: workspace of %zu bytes, %zu needed", workspace_bytes, L.bytes);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t numel = M * topk;
+  const int chunk_max = 128;
+  // 1. expert-major stable order, chunk table, position of every (token, slot)
+  prof_mark(0, st);
+  int rc = launch_align(topk_ids, ids_dtype, numel, align_E, FUSED_ALIGN_BLOCK, expert_map, expert_map ? 1 : 0,
+                        L.sorted_ids, L.sorted_cap, nullptr, 0, L.header, L.chunks, L.header + 1, L.chunk_cap,
+                        L.inv_pos, chunk_max, st);
+  if (rc != LO_OK) return rc;
+  // 2. per-token quantisation, written once per routed slot into sorted order
+  prof_mark(1, st);
+  rc = launch_token_quant(x, x_dtype, M, H, topk, L.inv_pos, L.xq, L.xs, st);
+  if (rc != LO_OK) return rc;
+  // 3. gate_up GEMM -> bf16 [position, 2I]
+  prof_mark(2, st);
+  GemmArgs g1{};
+  g1.A = L.xq; g1.a_scale = L.xs; g1.rows_a = L.sorted_cap;
+  g1.max_chunk_rows = (int)(M < chunk_max ? M : chunk_max);
+  g1.B = w1; g1.b_scale = w1_scale; g1.E = E_local;
+  g1.n_rows_per_expert = 2 * I; g1.K = H; g1.n_tiles = (int)(2 * I / 128);
+  g1.sorted_ids = L.sorted_ids; g1.numel_valid = numel; g1.out_by_position = 1;
+  g1.chunks = L.chunks; g1.num_chunks = L.header + 1;
+  g1.C = L.cache1;
+  g1.topk_weights = topk_weights;
+  g1.weight_mode = apply_router_weight_on_input ? LO_WEIGHT_FP32 : LO_WEIGHT_NONE;
+  g1.status = status;
+  rc = launch_grouped_gemm(GEMM_CHANNEL, g1, st);
+  if (rc != LO_OK) return rc;
+  // SiLU*mul + per-token re-quantisation of the rows that exist (padding positions are skipped)
+  rc = launch_silu_mul_token_quant(L.cache1, L.sorted_cap, I, L.sorted_ids, numel, L.header, L.act_q, L.act_s, st);
+  if (rc != LO_OK) return rc;
+  // 4. down GEMM, routed weight in the epilogue -> cache3[token, slot, :]
+  prof_mark(3, st);
+  GemmArgs g2{};
+  g2.A = L.act_q; g2.a_scale = L.act_s; g2.rows_a = L.sorted_cap; g2.max_chunk_rows = g1.max_chunk_rows;
+  g2.B = w2; g2.b_scale = w2_scale; g2.E = E_local;
+  g2.n_rows_per_expert = H; g2.K = I; g2.n_tiles = (int)(H / 128);
+  g2.sorted_ids = L.sorted_ids; g2.numel_valid = numel;
+  g2.chunks = L.chunks; g2.num_chunks = L.header + 1;
+  g2.C = static_cast<__nv_bfloat16 *>(cache3);
+  g2.topk_weights = topk_weights;
+  g2.weight_mode = apply_router_weight_on_input ? LO_WEIGHT_NONE : LO_WEIGHT_FP32;
+  g2.status = status;
+  rc = launch_grouped_gemm(GEMM_CHANNEL, g2, st);
+  if (rc != LO_OK) return rc;
+  // 5. top-k reduction
+  prof_mark(4, st);
+  rc = launch_moe_sum_masked(static_cast<const __nv_bfloat16 *>(cache3), static_cast<__nv_bfloat16 *>(out),
+                             static_cast<const __nv_bfloat16 *>(shared_output), M, topk, H, routed_scaling_factor,
+                             topk_ids, ids_dtype, expert_map, st);
+  prof_mark(5, st);
+  if (g_prof.enabled && g_prof.created) g_prof.recorded = true;
+  return rc;
 }
 
 // ---------------------------------------------------------------------------

@@ -36,6 +36,12 @@
 // up partial of a K block are separate half-steps, so the MMAs of one overlap the promotion
 // of the other even when only two buffers fit.
 //
+// Per-channel mode (one scale per token and one per output channel instead of 128x128 blocks) uses
+// the same pipeline without the promotion: a tensor-memory buffer is the int32 accumulator of a whole
+// item, summed over every K block by the tensor core, and the promotion warps only run an epilogue
+// (int32 -> fp32, times token scale, times channel scale) while the MMAs of the next items fill the
+// other buffers.  The scale-producer warps idle in that mode.
+//
 // Every wait is bounded: after about a second a waiter records a timeout in the
 // status word, raises a CTA-wide abort flag, and all roles fall through to the
 // common exit where tensor memory is released.
@@ -74,12 +80,13 @@ template <int MODE, int A_ROWS> struct Cfg {
   static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 10 ? 10 : (200 * 1024) / STAGE_BYTES;
   // tensor memory: columns [0, NUM_W * A_ROWS) hold the fp32 running sums (gate, then up); the rest is
   // cut into partial buffers of A_ROWS columns, one accumulator each (at most 8 are used)
-  static constexpr int ACC_COLS = NUM_W * A_ROWS;
+  // (per-channel mode keeps no running sums: a buffer is the int32 accumulator of a whole item)
+  static constexpr int ACC_COLS = MODE == GEMM_CHANNEL ? 0 : NUM_W * A_ROWS;
   static constexpr int NBUF = ((int)TMEM_COLS - ACC_COLS) / A_ROWS > 8 ? 8 : ((int)TMEM_COLS - ACC_COLS) / A_ROWS;
   // Ring of scale-product tables.  A slot written for K-block step i was last read at step
   // i - SC_SLOTS; the producer of step i has seen the MMAs of step i - STAGES complete, which were
   // issued after the promotion of step i - STAGES - NBUF finished, so STAGES + NBUF slots suffice.
-  static constexpr int SC_SLOTS = STAGES + NBUF;
+  static constexpr int SC_SLOTS = MODE == GEMM_CHANNEL ? 1 : STAGES + NBUF;
 };
 
 template <int MODE, int A_ROWS> struct Smem {
@@ -291,6 +298,7 @@ struct KParams {
   float act_eps;
   int32_t *status;
   float neg_zero;           // -0.0f, see mul2_rounded
+  int out_by_position;      // bf16 output row = sorted position instead of the sorted id
 };
 
 // Four tensor maps of the sorted activation matrix, box heights 16 / 32 / 64 / 128 rows.
@@ -319,7 +327,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   // ------------------------------ set-up -----------------------------------
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(&sm.full[s], 1 + SCALE_THREADS / 32);   // TMA thread (arrive.expect_tx) + one arrive per scale warp
+      // TMA thread (arrive.expect_tx) + one arrive per scale warp (per-channel mode has no scale tables)
+      mbar_init(&sm.full[s], MODE == GEMM_CHANNEL ? 1 : 1 + SCALE_THREADS / 32);
       mbar_init(&sm.empty[s], 1);                        // tcgen05.commit of the MMA thread
     }
     for (int b = 0; b < NBUF; ++b) {
@@ -340,7 +349,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = sm.tmem_base;
-  if (warp >= 4) {
+  if (warp >= 4 && MODE != GEMM_CHANNEL) {
     // fill every partial buffer with the conversion offset (see MAGIC_I)
     const uint32_t base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + ACC_COLS;
     for (int pc = (warp - 4) >> 2; pc < NBUF * A_ROWS / 16; pc += 4) tmem_st16_fill(base + pc * 16, MAGIC_I);
@@ -392,30 +401,53 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           if (ch.expert < 0) continue;
           const uint32_t T = (uint32_t)((ch.rows + 15) & ~15);
           const uint32_t idesc = make_idesc(T);
-          for (int kb = 0; kb < KB; ++kb, ++it) {
-            const int s = it % STAGES;
-            const uint32_t ph = (it / STAGES) & 1u;
-            if (!mbar_wait(sm, &sm.full[s], ph, p.status, 3)) { ok = false; break; }
-            const uint64_t bdesc = make_smem_desc(smem_u32(sm.a[s]));
-#pragma unroll
-            for (int w = 0; w < NUM_W; ++w, ++ab) {
-              const uint32_t b = ab % NBUF;
-              const uint32_t aph = (ab / NBUF) & 1u;
-              if (!mbar_wait(sm, &sm.tmem_empty[b], aph ^ 1u, p.status, 2)) { ok = false; break; }
+          if constexpr (MODE == GEMM_CHANNEL) {
+            // one int32 accumulator per item, summed over every K block; the scales come in the epilogue
+            const uint32_t b = ab % NBUF;
+            const uint32_t aph = (ab / NBUF) & 1u;
+            ++ab;
+            if (!mbar_wait(sm, &sm.tmem_empty[b], aph ^ 1u, p.status, 2)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t d = tmem_base + b * (uint32_t)A_ROWS;
+            for (int kb = 0; kb < KB; ++kb, ++it) {
+              const int s = it % STAGES;
+              const uint32_t ph = (it / STAGES) & 1u;
+              if (!mbar_wait(sm, &sm.full[s], ph, p.status, 3)) { ok = false; break; }
               tc_fence_after();
-              const uint64_t adesc = make_smem_desc(smem_u32(sm.w[s][w]));
-              const uint32_t d = tmem_base + ACC_COLS + b * (uint32_t)A_ROWS;
+              const uint64_t bdesc = make_smem_desc(smem_u32(sm.a[s]));
+              const uint64_t adesc = make_smem_desc(smem_u32(sm.w[s][0]));
 #pragma unroll
               for (int k4 = 0; k4 < TILE_K / 32; ++k4)
-                umma_i8(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, 1u);
-              umma_commit(&sm.tmem_full[b]);
+                umma_i8(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, (kb | k4) != 0 ? 1u : 0u);
+              umma_commit(&sm.empty[s]);
             }
-            if (!ok) break;
-            umma_commit(&sm.empty[s]);
+            if (ok) umma_commit(&sm.tmem_full[b]);
+          } else {
+            for (int kb = 0; kb < KB; ++kb, ++it) {
+              const int s = it % STAGES;
+              const uint32_t ph = (it / STAGES) & 1u;
+              if (!mbar_wait(sm, &sm.full[s], ph, p.status, 3)) { ok = false; break; }
+              const uint64_t bdesc = make_smem_desc(smem_u32(sm.a[s]));
+#pragma unroll
+              for (int w = 0; w < NUM_W; ++w, ++ab) {
+                const uint32_t b = ab % NBUF;
+                const uint32_t aph = (ab / NBUF) & 1u;
+                if (!mbar_wait(sm, &sm.tmem_empty[b], aph ^ 1u, p.status, 2)) { ok = false; break; }
+                tc_fence_after();
+                const uint64_t adesc = make_smem_desc(smem_u32(sm.w[s][w]));
+                const uint32_t d = tmem_base + ACC_COLS + b * (uint32_t)A_ROWS;
+#pragma unroll
+                for (int k4 = 0; k4 < TILE_K / 32; ++k4)
+                  umma_i8(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, 1u);
+                umma_commit(&sm.tmem_full[b]);
+              }
+              if (!ok) break;
+              umma_commit(&sm.empty[s]);
+            }
           }
         }
       }
-    } else {
+    } else if (MODE != GEMM_CHANNEL) {
       // ========================= scale producers (2 warps) ====================
       // Thread g owns tokens g and g + 64 of the chunk.  Token scales and weight-block scales are
       // read four K blocks at a time and one group ahead, so the loop never waits on memory.
@@ -511,11 +543,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       const int n_local = q * 32 + lane;
       if (ch.expert < 0) {
         // block of a non-local expert: its output rows are zero
-        if (MODE == GEMM_SINGLE) {
+        if (MODE != GEMM_GATE_UP) {
           for (int t = cg; t < ch.rows; t += 4) {
-            const int32_t sid = p.sorted_ids[ch.row0 + t];
+            const int32_t sid = p.sorted_ids ? p.sorted_ids[ch.row0 + t] : ch.row0 + t;
             if (sid >= 0 && sid < p.numel_valid)
-              p.C[(int64_t)sid * p.n_store + (int64_t)nt * TILE_N + n_local] = __float2bfloat16_rn(0.f);
+              p.C[(int64_t)(p.out_by_position ? ch.row0 + t : sid) * p.n_store + (int64_t)nt * TILE_N + n_local] =
+                  __float2bfloat16_rn(0.f);
           }
         }
         continue;
@@ -531,17 +564,68 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       // hidden behind the K loop; broadcast by shuffle in the epilogue.
       int32_t sid_r = -1;
       float wgt_r = 0.f;
-      if (MODE == GEMM_SINGLE || p.weight_mode != LO_WEIGHT_NONE) {
+      if (MODE != GEMM_GATE_UP || p.weight_mode != LO_WEIGHT_NONE) {
         const int t = col_begin + lane;
         if (lane < my_p * 16 && t < ch.rows) {
-          int32_t sid = p.sorted_ids[ch.row0 + t];
+          // without a sorted-id table the id of a row is its position
+          int32_t sid = p.sorted_ids ? p.sorted_ids[ch.row0 + t] : ch.row0 + t;
           if (sid < 0 || sid >= p.numel_valid) sid = -1;
-          sid_r = sid;
           if (sid >= 0 && p.weight_mode != LO_WEIGHT_NONE) wgt_r = p.topk_weights[sid];
+          if (sid >= 0 && p.out_by_position) sid = ch.row0 + t;
+          sid_r = sid;
         }
       }
 
-      for (int kb = 0; kb < KB && ok; ++kb, ++it) {
+      if constexpr (MODE == GEMM_CHANNEL) {
+        // ---------------- per-channel mode: one pass over the finished int32 accumulator ----------------
+        // token scale of column col_begin + lane (broadcast by shuffle) and the scale of this thread's channel
+        float as_r = 0.f;
+        {
+          const int t = col_begin + lane;
+          if (lane < my_p * 16 && t < ch.rows) as_r = __ldg(p.a_scale + ch.row0 + t);
+        }
+        const int64_t n_glob = (int64_t)nt * TILE_N + n_local;
+        const bool n_ok = n_glob < p.n_store;
+        const float bs = n_glob < p.n_rows_per_expert ? __ldg(p.b_scale + (int64_t)ch.expert * p.n_rows_per_expert + n_glob) : 0.f;
+        const uint32_t b = ab % NBUF;
+        const uint32_t aph = (ab / NBUF) & 1u;
+        ++ab;
+        if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.tmem_full[b], aph, p.status, 5))) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t part = tmem_base + lane_off + b * (uint32_t)A_ROWS + (uint32_t)col_begin;
+#pragma unroll 1
+        for (int pc = 0; pc < my_p; ++pc) {
+          uint32_t raw[16];
+          tmem_ld16(part + pc * 16, raw);
+          tmem_ld_wait();
+          if (pc == my_p - 1) {
+            // every value this warp needs is in registers: hand the buffer back before the stores
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.tmem_empty[b]);
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int32_t sid = __shfl_sync(0xffffffffu, sid_r, pc * 16 + j);
+            const float wgt = __shfl_sync(0xffffffffu, wgt_r, pc * 16 + j);
+            const float as = __shfl_sync(0xffffffffu, as_r, pc * 16 + j);
+            if (sid >= 0 && n_ok) {
+              float v = __int2float_rn((int32_t)raw[j]);
+              if (p.weight_mode == LO_WEIGHT_FP32) v = __fmul_rn(v, wgt);
+              v = __fmul_rn(__fmul_rn(v, as), bs);
+              if (p.weight_mode == LO_WEIGHT_BF16_PRODUCT) v = bf16_round(v) * bf16_round(wgt);
+              p.C[(int64_t)sid * p.n_store + n_glob] = __float2bfloat16_rn(v);
+            }
+          }
+        }
+        if (my_p == 0) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sm.tmem_empty[b]);
+        }
+      }
+
+      const int kb_end = MODE == GEMM_CHANNEL ? 0 : KB;   // the block-scaled modes promote once per K block
+      for (int kb = 0; kb < kb_end && ok; ++kb, ++it) {
         const int slot = it % SC_SLOTS;
 #pragma unroll
         for (int w = 0; w < NUM_W; ++w, ++ab) {
@@ -661,7 +745,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
             }
           }
         }
-      } else {
+      } else if (MODE == GEMM_SINGLE) {
 #pragma unroll 1
         for (int pc = 0; pc < my_p; ++pc) {
           uint32_t av[16];
@@ -687,10 +771,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       // Column ownership changes from item to item (it depends on the chunk size), so the next item's
       // first K block may store running sums into columns another warp is still reading in the passes
       // above: all promotion warps meet before any of them goes on.
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sm.isync);
-      if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.isync, item_par, p.status, 11))) { ok = false; break; }
-      item_par ^= 1u;
+      // (Per-channel mode needs none: an item's buffer is private to it until all 16 warps released it.)
+      if (MODE != GEMM_CHANNEL) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.isync);
+        if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.isync, item_par, p.status, 11))) { ok = false; break; }
+        item_par ^= 1u;
+      }
     }
   }
 
@@ -774,6 +861,7 @@ int launch_mode(const GemmArgs &a, cudaStream_t stream) {
   p.sorted_ids = a.sorted_ids; p.numel_valid = a.numel_valid;
   p.chunks = a.chunks; p.num_chunks = a.num_chunks; p.act_q = a.act_q; p.act_s = a.act_s; p.C = a.C;
   p.topk_weights = a.topk_weights; p.weight_mode = a.weight_mode; p.act_eps = a.act_eps; p.status = a.status; p.neg_zero = -0.0f;
+  p.out_by_position = a.out_by_position;
   const int grid = sm_count();
   if (grid <= 0) return fail(LO_ERR_CUDA, "no CUDA device");
   grouped_gemm_kernel<MODE, A_ROWS><<<grid, NUM_THREADS, smem_bytes, stream>>>(wmap, amaps, p);
@@ -785,7 +873,7 @@ int launch_mode(const GemmArgs &a, cudaStream_t stream) {
 
 int launch_grouped_gemm(GemmMode mode, const GemmArgs &a, cudaStream_t stream) {
   LO_REQUIRE(a.K % TILE_K == 0 && a.K >= TILE_K, "grouped gemm: K=%lld must be a positive multiple of 128", (long long)a.K);
-  LO_REQUIRE(a.n_rows_per_expert % TILE_N == 0 || (a.E == 1 && mode == GEMM_SINGLE),
+  LO_REQUIRE(a.n_rows_per_expert % TILE_N == 0 || (a.E == 1 && mode != GEMM_GATE_UP),
              "grouped gemm: N=%lld must be a multiple of 128", (long long)a.n_rows_per_expert);
   LO_REQUIRE((int64_t)a.E * a.n_rows_per_expert < (1LL << 31), "grouped gemm: E*N exceeds the tensor-map row range");
   LO_REQUIRE(a.rows_a >= 1 && a.rows_a < (1LL << 31), "grouped gemm: activation row count out of range");
@@ -803,6 +891,11 @@ int launch_grouped_gemm(GemmMode mode, const GemmArgs &a, cudaStream_t stream) {
   }
   LO_REQUIRE((int64_t)a.n_tiles * TILE_N >= a.n_rows_per_expert && (int64_t)(a.n_tiles - 1) * TILE_N < a.n_rows_per_expert,
              "grouped gemm: tile count mismatch");
+  if (mode == GEMM_CHANNEL) {
+    if (cap <= 32) return launch_mode<GEMM_CHANNEL, 32>(a, stream);
+    if (cap <= 64) return launch_mode<GEMM_CHANNEL, 64>(a, stream);
+    return launch_mode<GEMM_CHANNEL, 128>(a, stream);
+  }
   if (cap <= 32) return launch_mode<GEMM_SINGLE, 32>(a, stream);
   if (cap <= 64) return launch_mode<GEMM_SINGLE, 64>(a, stream);
   return launch_mode<GEMM_SINGLE, 128>(a, stream);

@@ -119,6 +119,140 @@ __global__ void __launch_bounds__(256) group_quant_scatter_kernel(const __nv_bfl
   }
 }
 
+// ---------------------------------------------------------------------------
+// Per-token (whole-row) INT8 quantisation, the activation format of the per-channel W8A8 mode.
+//
+// Arithmetic of the reference's kernel (python/lightop/_lmslim_native/layers/gemm/int8_utils.py:21-44):
+//   absmax = max(max |x|, 1e-10)       (fp32)
+//   scale  = absmax / 127              (IEEE fp32 division)
+//   q      = rint(x * (127 / absmax))  (one fp32 division per row, fp32 product, round half to even)
+// One CTA per row: pass 1 takes the maximum, pass 2 re-reads the row (it is still in L1/L2) and
+// stores 8 int8 per thread and step.  With inv_pos the int8 row and its scale are written to every
+// sorted position of the token instead of to row `token` (same layout trick as the group kernel).
+// ---------------------------------------------------------------------------
+constexpr int TOKEN_QUANT_THREADS = 256;
+
+__device__ __forceinline__ float block_max_256(float v, float *red) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float r = red[lane & 7];
+#pragma unroll
+  for (int off = 4; off > 0; off >>= 1) r = fmaxf(r, __shfl_xor_sync(0xffffffffu, r, off));
+  __syncthreads();   // red may be reused by the caller
+  return r;
+}
+
+__device__ __forceinline__ uint2 quant8_rn(const float (&v)[8], float inv) {
+  uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float r = __fmul_rn(v[i], inv);
+    r = fminf(fmaxf(r, -128.0f), 127.0f);
+    packed[i >> 2] |= (uint32_t)(__float2int_rn(r) & 0xff) << (8 * (i & 3));
+  }
+  return make_uint2(packed[0], packed[1]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(TOKEN_QUANT_THREADS) token_quant_kernel(const T *__restrict__ x, int64_t K, int topk,
+                                                                          const int32_t *__restrict__ inv_pos,
+                                                                          int8_t *__restrict__ q, float *__restrict__ s) {
+  __shared__ float red[8];
+  const int64_t row = blockIdx.x;
+  const T *xr = x + row * K;
+  // rows of a length that is not a multiple of 8 are not 16-byte aligned: they take the scalar loops only
+  const int64_t vecs = (K & 7) == 0 ? K / 8 : 0;
+  float amax = 0.f;
+  for (int64_t i = threadIdx.x; i < vecs; i += TOKEN_QUANT_THREADS) {
+    float v[8];
+    Load8<T>::load(xr + i * 8, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+  }
+  for (int64_t i = vecs * 8 + threadIdx.x; i < K; i += TOKEN_QUANT_THREADS) amax = fmaxf(amax, fabsf((float)xr[i]));
+  amax = fmaxf(block_max_256(amax, red), 1e-10f);
+  const float scale = __fdiv_rn(amax, 127.0f);
+  const float inv = __fdiv_rn(127.0f, amax);
+  if (inv_pos == nullptr) {
+    for (int64_t i = threadIdx.x; i < vecs; i += TOKEN_QUANT_THREADS) {
+      float v[8];
+      Load8<T>::load(xr + i * 8, v);
+      *reinterpret_cast<uint2 *>(q + row * K + i * 8) = quant8_rn(v, inv);
+    }
+    for (int64_t i = vecs * 8 + threadIdx.x; i < K; i += TOKEN_QUANT_THREADS) {
+      const float r = fminf(fmaxf(__fmul_rn((float)xr[i], inv), -128.0f), 127.0f);
+      q[row * K + i] = (int8_t)__float2int_rn(r);
+    }
+    if (threadIdx.x == 0) s[row] = scale;
+    return;
+  }
+  for (int64_t i = threadIdx.x; i < vecs; i += TOKEN_QUANT_THREADS) {
+    float v[8];
+    Load8<T>::load(xr + i * 8, v);
+    const uint2 pk = quant8_rn(v, inv);
+    for (int j = 0; j < topk; ++j) {
+      const int32_t pos = inv_pos[row * topk + j];
+      if (pos >= 0) *reinterpret_cast<uint2 *>(q + (int64_t)pos * K + i * 8) = pk;
+    }
+  }
+  if (threadIdx.x < topk) {
+    const int32_t pos = inv_pos[row * topk + threadIdx.x];
+    if (pos >= 0) s[pos] = scale;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// SiLU(gate) * up followed by per-token INT8 quantisation, one CTA per row of a bf16 [rows, 2*d]
+// matrix (gate columns first).  Semantics of the reference's fused kernel
+// (csrc/kernels/gated_activation/fuse_silu_mul_quant.cu:90-131) with exact fp32 expf / division in
+// the SiLU: act = bf16(bf16(silu(gate)) * up); scale = max|act| / 127; q = rint(act * (127 / max)),
+// saturated; a row of zeros gets scale 0 and q 0.  Rows whose entry in row_ids is a padding
+// sentinel (< 0 or >= numel_valid) are skipped.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(TOKEN_QUANT_THREADS) silu_mul_token_quant_kernel(
+    const __nv_bfloat16 *__restrict__ in, int64_t d, const int32_t *__restrict__ row_ids, int64_t numel_valid,
+    const int32_t *__restrict__ num_rows_dev, int8_t *__restrict__ q, float *__restrict__ s) {
+  __shared__ float red[8];
+  const int64_t row = blockIdx.x;
+  if (num_rows_dev && row >= *num_rows_dev) return;
+  if (row_ids) {
+    const int32_t id = row_ids[row];
+    if (id < 0 || id >= numel_valid) return;
+  }
+  const __nv_bfloat16 *g = in + row * 2 * d;
+  const __nv_bfloat16 *u = g + d;
+  const int64_t vecs = d / 8;
+  float amax = 0.f;
+  for (int64_t i = threadIdx.x; i < vecs; i += TOKEN_QUANT_THREADS) {
+    float gv[8], uv[8];
+    Load8<__nv_bfloat16>::load(g + i * 8, gv);
+    Load8<__nv_bfloat16>::load(u + i * 8, uv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sl = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(gv[j], 1.0f + expf(-gv[j]))));
+      const float a = __bfloat162float(__float2bfloat16_rn(sl * uv[j]));
+      amax = fmaxf(amax, fabsf(a));
+    }
+  }
+  amax = block_max_256(amax, red);
+  const float inv = amax == 0.f ? 0.f : __fdiv_rn(127.0f, amax);
+  for (int64_t i = threadIdx.x; i < vecs; i += TOKEN_QUANT_THREADS) {
+    float gv[8], uv[8], av[8];
+    Load8<__nv_bfloat16>::load(g + i * 8, gv);
+    Load8<__nv_bfloat16>::load(u + i * 8, uv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float sl = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(gv[j], 1.0f + expf(-gv[j]))));
+      av[j] = __bfloat162float(__float2bfloat16_rn(sl * uv[j]));
+    }
+    *reinterpret_cast<uint2 *>(q + row * d + i * 8) = quant8_rn(av, inv);
+  }
+  if (threadIdx.x == 0) s[row] = __fdiv_rn(amax, 127.0f);
+}
+
 template <typename T>
 int launch_typed(const void *x, int64_t num_groups, int group_size, float eps_t, int8_t *q, float *s,
                  cudaStream_t stream) {
@@ -162,7 +296,63 @@ int launch_group_quant_scatter(const void *x, int64_t M, int64_t H, int topk, co
   return LO_OK;
 }
 
+int launch_token_quant(const void *x, int x_dtype, int64_t M, int64_t K, int topk, const int32_t *inv_pos, int8_t *q,
+                       float *s, cudaStream_t stream) {
+  if (M == 0) return LO_OK;
+  LO_REQUIRE(K >= 1, "per-token quant: empty rows");
+  LO_REQUIRE(inv_pos == nullptr || K % 8 == 0, "per-token quant: the sorted layout needs a row length that is a multiple of 8");
+  LO_REQUIRE(M <= 0x7fffffffLL, "per-token quant: too many rows");
+  LO_REQUIRE(inv_pos == nullptr || (topk >= 1 && topk <= TOKEN_QUANT_THREADS), "per-token quant: bad top-k");
+  const unsigned blocks = (unsigned)M;
+  switch (x_dtype) {
+    case LO_BF16:
+      token_quant_kernel<__nv_bfloat16><<<blocks, TOKEN_QUANT_THREADS, 0, stream>>>(static_cast<const __nv_bfloat16 *>(x), K, topk, inv_pos, q, s);
+      break;
+    case LO_F16:
+      token_quant_kernel<__half><<<blocks, TOKEN_QUANT_THREADS, 0, stream>>>(static_cast<const __half *>(x), K, topk, inv_pos, q, s);
+      break;
+    case LO_F32:
+      token_quant_kernel<float><<<blocks, TOKEN_QUANT_THREADS, 0, stream>>>(static_cast<const float *>(x), K, topk, inv_pos, q, s);
+      break;
+    default: return fail(LO_ERR_UNSUPPORTED, "per-token quant: unsupported input dtype code %d", x_dtype);
+  }
+  LO_LAUNCH_OK("token_quant_kernel");
+  return LO_OK;
+}
+
+int launch_silu_mul_token_quant(const void *in, int64_t rows, int64_t d, const int32_t *row_ids, int64_t numel_valid,
+                                const int32_t *num_rows_dev, int8_t *q, float *s, cudaStream_t stream) {
+  if (rows == 0) return LO_OK;
+  LO_REQUIRE(d >= 8 && d % 8 == 0, "silu-mul quant: width %lld must be a multiple of 8", (long long)d);
+  LO_REQUIRE(rows <= 0x7fffffffLL, "silu-mul quant: too many rows");
+  silu_mul_token_quant_kernel<<<(unsigned)rows, TOKEN_QUANT_THREADS, 0, stream>>>(
+      static_cast<const __nv_bfloat16 *>(in), d, row_ids, numel_valid, num_rows_dev, q, s);
+  LO_LAUNCH_OK("silu_mul_token_quant_kernel");
+  return LO_OK;
+}
+
 }  // namespace lo
+
+extern "C" int lo_per_token_quant_int8(const void *x, int x_dtype, int64_t M, int64_t K, int8_t *q, float *s,
+                                       void *stream) {
+  using namespace lo;
+  LO_REQUIRE(M >= 0, "per-token quant: negative row count");
+  if (M == 0) return LO_OK;
+  LO_REQUIRE(x && q && s, "per-token quant: null pointer");
+  LO_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(q) & 7) == 0,
+             "per-token quant: x must be 16-byte and q 8-byte aligned");
+  return launch_token_quant(x, x_dtype, M, K, 0, nullptr, q, s, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int lo_silu_mul_quant_int8(const void *input, int64_t rows, int64_t d, int8_t *q, float *s, void *stream) {
+  using namespace lo;
+  LO_REQUIRE(rows >= 0, "silu-mul quant: negative row count");
+  if (rows == 0) return LO_OK;
+  LO_REQUIRE(input && q && s, "silu-mul quant: null pointer");
+  LO_REQUIRE((reinterpret_cast<uintptr_t>(input) & 15) == 0 && (reinterpret_cast<uintptr_t>(q) & 7) == 0,
+             "silu-mul quant: input must be 16-byte and q 8-byte aligned");
+  return launch_silu_mul_token_quant(input, rows, d, nullptr, 0, nullptr, q, s, static_cast<cudaStream_t>(stream));
+}
 
 extern "C" int lo_group_quant_int8(const void *x, int x_dtype, int64_t num_groups, int group_size,
                                    float eps, int8_t *q, float *s, void *stream) {

@@ -234,7 +234,8 @@ __global__ void __launch_bounds__(256) ep_gather_kernel(const __nv_bfloat16 *__r
 __global__ void __launch_bounds__(128) permute_rows_kernel(const int8_t *__restrict__ A, const float *__restrict__ a_scale,
                                                            int64_t rows_a, int64_t K, const int32_t *__restrict__ sorted_ids,
                                                            const int32_t *__restrict__ num_tokens_post_pad,
-                                                           int64_t numel_valid, int top_k, int8_t *__restrict__ A_sorted,
+                                                           int64_t numel_valid, int top_k, int64_t kb,
+                                                           int8_t *__restrict__ A_sorted,
                                                            float *__restrict__ a_scale_sorted) {
   const int64_t pos = blockIdx.x;
   if (pos >= *num_tokens_post_pad) return;
@@ -245,7 +246,6 @@ __global__ void __launch_bounds__(128) permute_rows_kernel(const int8_t *__restr
   const uint4 *src = reinterpret_cast<const uint4 *>(A + row * K);
   uint4 *dst = reinterpret_cast<uint4 *>(A_sorted + pos * K);
   for (int64_t c = threadIdx.x; c < K / 16; c += blockDim.x) dst[c] = src[c];
-  const int64_t kb = K / 128;
   for (int64_t c = threadIdx.x; c < kb; c += blockDim.x) a_scale_sorted[pos * kb + c] = a_scale[row * kb + c];
 }
 
@@ -253,11 +253,13 @@ __global__ void __launch_bounds__(128) permute_rows_kernel(const int8_t *__restr
 
 int launch_permute_rows(const int8_t *A, const float *a_scale, int64_t rows_a, int64_t K, const int32_t *sorted_ids,
                         int64_t sorted_capacity, const int32_t *num_tokens_post_pad, int64_t numel_valid, int top_k,
-                        int8_t *A_sorted, float *a_scale_sorted, cudaStream_t stream) {
+                        int8_t *A_sorted, float *a_scale_sorted, cudaStream_t stream, int64_t scales_per_row) {
   if (sorted_capacity <= 0) return LO_OK;
   LO_REQUIRE(sorted_capacity <= 0x7fffffffLL, "permute rows: too many positions");
   permute_rows_kernel<<<(unsigned)sorted_capacity, 128, 0, stream>>>(A, a_scale, rows_a, K, sorted_ids, num_tokens_post_pad,
-                                                                     numel_valid, top_k, A_sorted, a_scale_sorted);
+                                                                     numel_valid, top_k,
+                                                                     scales_per_row > 0 ? scales_per_row : K / 128, A_sorted,
+                                                                     a_scale_sorted);
   LO_LAUNCH_OK("permute_rows_kernel");
   return LO_OK;
 }

@@ -1,7 +1,7 @@
 """Mixture-of-experts APIs of the block-INT8 path (reference: python/lightop/moe/__init__.py:81-133)."""
 from .expert_parallel import ep_build_m_indices, ep_gather, ep_scatter
 from .gemm import moe_gemm_w8a8
-from .native import fused_experts_impl_int8
+from .native import fused_experts_impl_int8, fused_experts_impl_int8_marlin
 from .routing import moe_align_block_size, moe_align_block_size_out, moe_sum, topk_softmax
 
 __all__ = [
@@ -9,6 +9,7 @@ __all__ = [
     "ep_gather",
     "ep_scatter",
     "fused_experts_impl_int8",
+    "fused_experts_impl_int8_marlin",
     "moe_align_block_size",
     "moe_align_block_size_out",
     "moe_gemm_w8a8",

@@ -33,3 +33,27 @@ def per_token_group_quant_int8(x: torch.Tensor, group_size: int, eps: float = 1e
                                              _lib.current_stream(x.device))
     _lib.check(st, "per_token_group_quant_int8")
     return x_q, x_s
+
+
+def per_token_quant_int8(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Whole-row symmetric INT8 quantisation along the last dimension.
+
+    Same signature and return values as the reference
+    (python/lightop/_lmslim_native/layers/gemm/int8_utils.py:47-71): ``x_q`` int8 shaped like
+    ``x`` and fp32 scales ``x.shape[:-1] + (1,)``; ``scale = max(max|x|, 1e-10) / 127`` and
+    ``q = rint(x * (127 / absmax))`` (:38-41).
+    """
+    _lib.require_cuda(x)
+    if not x.is_contiguous():
+        x = x.contiguous()
+    K = x.shape[-1]
+    M = x.numel() // K if K else 0
+    x_q = torch.empty_like(x, dtype=torch.int8)
+    scales = torch.empty(x.shape[:-1] + (1,), device=x.device, dtype=torch.float32)
+    if M == 0:
+        return x_q, scales
+    with torch.cuda.device(x.device):
+        st = _lib.load().lo_per_token_quant_int8(_lib.ptr(x), _lib.dtype_code(x.dtype), M, K, _lib.ptr(x_q),
+                                                 _lib.ptr(scales), _lib.current_stream(x.device))
+    _lib.check(st, "per_token_quant_int8")
+    return x_q, scales

@@ -36,6 +36,15 @@ def make_weights(E: int, H: int, I: int, seed: int = 0, device="cpu"):
     return w1, w2, w1_s, w2_s
 
 
+def make_channel_scales(E: int, H: int, I: int, seed: int = 0, device="cpu"):
+    """Per-output-channel weight scales of the per-channel W8A8 mode: w1_s [E,2I], w2_s [E,H] fp32."""
+    dev = torch.device(device)
+    g = torch.Generator(device=dev).manual_seed(seed + 7919)
+    w1_s = torch.rand(E, 2 * I, generator=g, device=dev) * (1e-3 - 1e-4) + 1e-4
+    w2_s = torch.rand(E, H, generator=g, device=dev) * (1e-3 - 1e-4) + 1e-4
+    return w1_s, w2_s
+
+
 def make_activations(M: int, H: int, E: int, seed: int = 1, device="cpu", zipf: Optional[float] = None):
     """x [M,H] bf16 ~ N(0,1) and router logits [M,E] fp32 ~ N(0,1) (+ Zipf bias)."""
     dev = torch.device(device)

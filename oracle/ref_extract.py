@@ -101,3 +101,25 @@ def reference_composed_moe():
           "native_w8a8_per_token_matmul": native_w8a8_per_token_matmul}
     exec(compile(ast.Module(body=body, type_ignores=[]), "benchmark_moe_int8.py", "exec"), ns)
     return ns["torch_w8a8_per_column_moe"]
+
+
+def reference_channel_functions(per_token_quant):
+    """(per-token matmul, composed per-channel MoE) from test/moe_w8a8/benchmark_moe_int8.py:142-201.
+
+    ``torch_w8a8_per_column_moe`` calls ``per_token_quant_int8``, which in the reference is a
+    Triton kernel and cannot run on a CPU; the caller passes the restatement to bind under that
+    name.  Everything else (the matmul, the expert loop, SiLU*mul, the weighted sum) is the
+    reference's own code.
+    """
+    import torch
+    import torch.nn.functional as F
+    mm = extract_functions("test/moe_w8a8/benchmark_moe_int8.py", ["native_w8a8_per_token_matmul"])[
+        "native_w8a8_per_token_matmul"]
+    root = reference_root()
+    with open(os.path.join(root, "test/moe_w8a8/benchmark_moe_int8.py"), "r", encoding="utf-8") as fh:
+        tree = ast.parse(fh.read())
+    body = [n for n in tree.body if isinstance(n, ast.FunctionDef) and n.name == "torch_w8a8_per_column_moe"]
+    ns = {"torch": torch, "F": F, "math": math, "per_token_quant_int8": per_token_quant,
+          "native_w8a8_per_token_matmul": mm}
+    exec(compile(ast.Module(body=body, type_ignores=[]), "benchmark_moe_int8.py", "exec"), ns)
+    return mm, ns["torch_w8a8_per_column_moe"]

@@ -1,7 +1,8 @@
 """Generate the golden fixtures of tests/golden/ from the reference's own torch functions.
 
 Run where a reference checkout is available (``$LIGHTOP_REF`` or ``/root/reference``):
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py            (all fixtures)
+    python tests/golden/make_golden.py channel    (only channel_cases.pt)
 The outputs are produced by the reference code itself (loaded by oracle/ref_extract.py),
 not by the restatement in oracle/moe_block_int8.py; the tests then hold both the oracle
 and the CUDA kernels to these files.  Inputs are not stored: they are regenerated from
@@ -73,5 +74,32 @@ def main() -> None:
     print("wrote", os.listdir(HERE))
 
 
+def main_channel() -> None:
+    """Fixtures of the per-channel W8A8 mode (tests/golden/channel_cases.pt)."""
+    from oracle import moe_channel_int8 as och
+    mm, moe = ref_extract.reference_channel_functions(och.per_token_quant_int8)
+    cfg = synthetic.CONFIGS["c0_tiny"]
+    w1, w2, _, _ = synthetic.make_weights(cfg["E"], cfg["H"], cfg["I"], seed=0)
+    w1_s, w2_s = synthetic.make_channel_scales(cfg["E"], cfg["H"], cfg["I"], seed=0)
+    x, logits = synthetic.make_activations(cfg["M"], cfg["H"], cfg["E"], seed=1)
+    w, ids = torch.topk(torch.softmax(logits.float(), dim=-1), cfg["topk"])
+    w = w / w.sum(dim=-1, keepdim=True)
+    # the reference's matmul alone, on the rows of one expert (inputs from the restated quantiser)
+    xq, xs = och.per_token_quant_int8(x)
+    e0 = int(ids.reshape(-1)[0])
+    rows = torch.nonzero(ids.reshape(-1) == e0).reshape(-1) // cfg["topk"]
+    h0 = mm(xq[rows], w1[e0], xs[rows], w1_s[e0], output_dtype=torch.bfloat16)
+    # the reference's composed per-channel layer
+    y = moe(x, w1, w2, w1_s, w2_s, w, ids, cfg["topk"])
+    torch.save(dict(topk_weights=w, topk_ids=ids.to(torch.int32), gemm1_expert=e0, gemm1_rows=rows,
+                    gemm1_out=h0, y=y),
+               os.path.join(HERE, "channel_cases.pt"))
+    print("wrote channel_cases.pt")
+
+
 if __name__ == "__main__":
-    main()
+    if len(sys.argv) > 1 and sys.argv[1] == "channel":
+        main_channel()
+    else:
+        main()
+        main_channel()

@@ -76,8 +76,14 @@ def test_fused_experts_contract_checks():
         moe.fused_experts_impl_int8(x, w1, w2, tw, ti, None)
     with pytest.raises(AssertionError, match="Hidden size"):
         moe.fused_experts_impl_int8(x[:, :128], w1, w2, tw, ti, None, use_int8_w8a8=True, block_shape=[128, 128])
-    with pytest.raises(NotImplementedError):       # per-channel mode is not this path
-        moe.fused_experts_impl_int8(x, w1, w2, tw, ti, None, use_int8_w8a8=True, per_channel_quant=True)
+    with pytest.raises(NotImplementedError):       # per-channel flag together with a block shape
+        moe.fused_experts_impl_int8(x, w1, w2, tw, ti, None, use_int8_w8a8=True, per_channel_quant=True,
+                                    block_shape=[128, 128])
+    with pytest.raises(AssertionError, match="block or channel-wise"):      # the reference's own rule
+        moe.fused_experts_impl_int8(x, w1, w2, tw, ti, None, use_int8_w8a8=True)
+    with pytest.raises(RuntimeError):              # CPU tensors never reach a kernel
+        moe.fused_experts_impl_int8(x, w1, w2, tw, ti, None, use_int8_w8a8=True, per_channel_quant=True,
+                                    w1_scale=torch.zeros(2, 512, 1), w2_scale=torch.zeros(2, 256, 1))
     with pytest.raises(ValueError, match="activation"):
         moe.fused_experts_impl_int8(x, w1, w2, tw, ti, None, use_int8_w8a8=True, block_shape=[128, 128],
                                     activation="gelu", w1_scale=tw, w2_scale=tw)
@@ -86,6 +92,9 @@ def test_fused_experts_contract_checks():
 def test_api_names_present():
     import lightop_b200
     for name in ["topk_softmax", "moe_align_block_size", "moe_align_block_size_out", "moe_sum", "moe_gemm_w8a8",
-                 "fused_experts_impl_int8", "ep_scatter", "ep_gather", "ep_build_m_indices"]:
+                 "fused_experts_impl_int8", "fused_experts_impl_int8_marlin", "ep_scatter", "ep_gather",
+                 "ep_build_m_indices"]:
         assert hasattr(lightop_b200.moe, name)
     assert hasattr(lightop_b200.quant, "per_token_group_quant_int8")
+    assert hasattr(lightop_b200.quant, "per_token_quant_int8")
+    assert hasattr(lightop_b200.activation, "fuse_silu_mul_quant")
