@@ -441,7 +441,11 @@ extern "C" int lo_fused_moe_channel_int8(const void *x, int x_dtype, const int8_
   LO_REQUIRE(workspace_bytes >= L.bytes, "channel moe: workspace of %zu bytes, %zu needed", workspace_bytes, L.bytes);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t numel = M * topk;
-  const int chunk_max = 128;
+  // Largest chunk of one expert's rows handed to a CTA.  A chunk of up to 256 rows is one MMA N extent, so an
+  // expert with 129..256 rows streams its weights once instead of once per 128-row chunk (the second pass
+  // was found to miss L2 often), and an N = 256 MMA costs about 1.3x an N = 128 one.  The 256-row kernel
+  // stages fewer K blocks ahead, so it is used only when experts are expected to receive that many rows.
+  const int chunk_max = numel / align_E >= 64 ? 256 : 128;
   // 1. expert-major stable order, chunk table, position of every (token, slot)
   prof_mark(0, st);
   int rc = launch_align(topk_ids, ids_dtype, numel, align_E, FUSED_ALIGN_BLOCK, expert_map, expert_map ? 1 : 0,

@@ -98,7 +98,8 @@ template <int MODE, int A_ROWS> struct Smem {
   uint8_t a[STAGES][A_ROWS * TILE_K];
   static constexpr int SC_SLOTS = Cfg<MODE, A_ROWS>::SC_SLOTS;
   float sc[SC_SLOTS][NUM_W][A_ROWS];       // token scale x weight-block scale, ring indexed by the K-block counter
-  uint32_t amax[2][4][T_MAX];              // gate_up epilogue: |act| maxima per (item parity, lane quarter, token)
+  // gate_up epilogue: |act| maxima per (item parity, lane quarter, token); a stub in the other modes
+  uint32_t amax[MODE == GEMM_GATE_UP ? 2 : 1][4][MODE == GEMM_GATE_UP ? T_MAX : 1];
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
   uint64_t tmem_full[NBUF];
@@ -301,7 +302,8 @@ struct KParams {
   int out_by_position;      // bf16 output row = sorted position instead of the sorted id
 };
 
-// Four tensor maps of the sorted activation matrix, box heights 16 / 32 / 64 / 128 rows.
+// Four tensor maps of the sorted activation matrix, box heights 16 / 32 / 64 / 128 rows.  A chunk of
+// more than 128 rows (per-channel mode only) is fetched as a 128-row box plus a second box for the rest.
 struct AMaps {
   CUtensorMap m[4];
 };
@@ -376,8 +378,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           const int nt = (int)(item % p.n_tiles);
           if (ch.expert < 0) continue;
           const int T = (ch.rows + 15) & ~15;
-          const int mi = a_map_index(T);
-          const uint32_t a_bytes = (16u << mi) * TILE_K;
+          const int T0 = T > 128 ? 128 : T;                  // first box; the rest (if any) goes into a second one
+          const int mi = a_map_index(T0);
+          const int mi2 = T > 128 ? a_map_index(T - 128) : -1;
+          const uint32_t a_bytes = (16u << mi) * TILE_K + (mi2 >= 0 ? (16u << mi2) * TILE_K : 0u);
           const int32_t row_g = (int32_t)(ch.expert * p.n_rows_per_expert + (int64_t)nt * TILE_N);
           for (int kb = 0; kb < KB; ++kb, ++it) {
             const int s = it % STAGES;
@@ -388,6 +392,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
             if (NUM_W == 2)
               tma_load_2d(sm.w[s][NUM_W - 1], &w_map, kb * TILE_K, row_g + p.n_tiles * TILE_N, &sm.full[s], pol_w);
             tma_load_2d(sm.a[s], &a_maps.m[mi], kb * TILE_K, ch.row0, &sm.full[s], pol_a);
+            if constexpr (A_ROWS > 128) {
+              if (mi2 >= 0)
+                tma_load_2d(sm.a[s] + 128 * TILE_K, &a_maps.m[mi2], kb * TILE_K, ch.row0 + 128, &sm.full[s], pol_a);
+            }
           }
         }
       }
@@ -560,29 +568,37 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       const int my_p = n_pieces / 4 + (cg < (n_pieces & 3) ? 1 : 0);
       const int col_begin = (cg * (n_pieces / 4) + min(cg, n_pieces & 3)) * 16;
 
-      // Row id and routed weight of token col_begin + lane, fetched now so that the latency is
-      // hidden behind the K loop; broadcast by shuffle in the epilogue.
-      int32_t sid_r = -1;
-      float wgt_r = 0.f;
-      if (MODE != GEMM_GATE_UP || p.weight_mode != LO_WEIGHT_NONE) {
-        const int t = col_begin + lane;
-        if (lane < my_p * 16 && t < ch.rows) {
-          // without a sorted-id table the id of a row is its position
-          int32_t sid = p.sorted_ids ? p.sorted_ids[ch.row0 + t] : ch.row0 + t;
-          if (sid < 0 || sid >= p.numel_valid) sid = -1;
-          if (sid >= 0 && p.weight_mode != LO_WEIGHT_NONE) wgt_r = p.topk_weights[sid];
-          if (sid >= 0 && p.out_by_position) sid = ch.row0 + t;
-          sid_r = sid;
+      // Row id and routed weight of token col_begin + 32 * u + lane, fetched now so that the latency is
+      // hidden behind the K loop; broadcast by shuffle in the epilogue.  (A column group owns at most
+      // 32 tokens of a chunk of up to 128, 64 of a chunk of up to 256.)
+      constexpr int NPF = A_ROWS > 128 ? 2 : 1;
+      int32_t sid_r[NPF];
+      float wgt_r[NPF];
+#pragma unroll
+      for (int u = 0; u < NPF; ++u) {
+        sid_r[u] = -1;
+        wgt_r[u] = 0.f;
+        if (MODE != GEMM_GATE_UP || p.weight_mode != LO_WEIGHT_NONE) {
+          const int t = col_begin + u * 32 + lane;
+          if (u * 32 + lane < my_p * 16 && t < ch.rows) {
+            // without a sorted-id table the id of a row is its position
+            int32_t sid = p.sorted_ids ? p.sorted_ids[ch.row0 + t] : ch.row0 + t;
+            if (sid < 0 || sid >= p.numel_valid) sid = -1;
+            if (sid >= 0 && p.weight_mode != LO_WEIGHT_NONE) wgt_r[u] = p.topk_weights[sid];
+            if (sid >= 0 && p.out_by_position) sid = ch.row0 + t;
+            sid_r[u] = sid;
+          }
         }
       }
 
       if constexpr (MODE == GEMM_CHANNEL) {
         // ---------------- per-channel mode: one pass over the finished int32 accumulator ----------------
         // token scale of column col_begin + lane (broadcast by shuffle) and the scale of this thread's channel
-        float as_r = 0.f;
-        {
-          const int t = col_begin + lane;
-          if (lane < my_p * 16 && t < ch.rows) as_r = __ldg(p.a_scale + ch.row0 + t);
+        float as_r[NPF];
+#pragma unroll
+        for (int u = 0; u < NPF; ++u) {
+          const int t = col_begin + u * 32 + lane;
+          as_r[u] = (u * 32 + lane < my_p * 16 && t < ch.rows) ? __ldg(p.a_scale + ch.row0 + t) : 0.f;
         }
         const int64_t n_glob = (int64_t)nt * TILE_N + n_local;
         const bool n_ok = n_glob < p.n_store;
@@ -604,11 +620,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.tmem_empty[b]);
           }
+          // piece pc holds tokens 16 * pc .. 16 * pc + 15 of this group: register set pc / 2, lanes 16 * (pc & 1) ..
+          const int u = NPF > 1 ? (pc >> 1) : 0;
+          const int32_t sid_u = NPF > 1 && u ? sid_r[NPF - 1] : sid_r[0];
+          const float wgt_u = NPF > 1 && u ? wgt_r[NPF - 1] : wgt_r[0];
+          const float as_u = NPF > 1 && u ? as_r[NPF - 1] : as_r[0];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const int32_t sid = __shfl_sync(0xffffffffu, sid_r, pc * 16 + j);
-            const float wgt = __shfl_sync(0xffffffffu, wgt_r, pc * 16 + j);
-            const float as = __shfl_sync(0xffffffffu, as_r, pc * 16 + j);
+            const int src = (pc & 1) * 16 + j;
+            const int32_t sid = __shfl_sync(0xffffffffu, sid_u, src);
+            const float wgt = __shfl_sync(0xffffffffu, wgt_u, src);
+            const float as = __shfl_sync(0xffffffffu, as_u, src);
             if (sid >= 0 && n_ok) {
               float v = __int2float_rn((int32_t)raw[j]);
               if (p.weight_mode == LO_WEIGHT_FP32) v = __fmul_rn(v, wgt);
@@ -682,7 +704,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
 
       // ------------------------------ epilogue -------------------------------
       const uint32_t acc0 = tmem_base + lane_off + (uint32_t)col_begin;            // gate (or the only) sums
-      if (MODE == GEMM_GATE_UP) {
+      if constexpr (MODE == GEMM_GATE_UP) {
         const int64_t I = (int64_t)p.n_tiles * TILE_N;
         const uint32_t acc1 = acc0 + (uint32_t)A_ROWS;                              // up sums
         uint32_t(*amax_tab)[T_MAX] = sm.amax[item_par];
@@ -699,7 +721,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           for (int j = 0; j < 16; ++j) {
             float gte = __uint_as_float(gv[j]), up = __uint_as_float(uv[j]);
             if (p.weight_mode == LO_WEIGHT_FP32) {
-              const float wgt = __shfl_sync(0xffffffffu, wgt_r, pc * 16 + j);
+              const float wgt = __shfl_sync(0xffffffffu, wgt_r[0], pc * 16 + j);
               gte *= wgt;
               up *= wgt;
             }
@@ -753,8 +775,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const int32_t sid = __shfl_sync(0xffffffffu, sid_r, pc * 16 + j);
-            const float wgt = __shfl_sync(0xffffffffu, wgt_r, pc * 16 + j);
+            const int32_t sid = __shfl_sync(0xffffffffu, sid_r[0], pc * 16 + j);
+            const float wgt = __shfl_sync(0xffffffffu, wgt_r[0], pc * 16 + j);
             if (sid >= 0) {
               float v = __uint_as_float(av[j]);
               if (p.weight_mode == LO_WEIGHT_FP32) {
@@ -892,10 +914,13 @@ int launch_grouped_gemm(GemmMode mode, const GemmArgs &a, cudaStream_t stream) {
   LO_REQUIRE((int64_t)a.n_tiles * TILE_N >= a.n_rows_per_expert && (int64_t)(a.n_tiles - 1) * TILE_N < a.n_rows_per_expert,
              "grouped gemm: tile count mismatch");
   if (mode == GEMM_CHANNEL) {
+    LO_REQUIRE(cap <= 256, "grouped gemm: per-channel chunks hold at most 256 rows");
     if (cap <= 32) return launch_mode<GEMM_CHANNEL, 32>(a, stream);
     if (cap <= 64) return launch_mode<GEMM_CHANNEL, 64>(a, stream);
-    return launch_mode<GEMM_CHANNEL, 128>(a, stream);
+    if (cap <= 128) return launch_mode<GEMM_CHANNEL, 128>(a, stream);
+    return launch_mode<GEMM_CHANNEL, 256>(a, stream);
   }
+  LO_REQUIRE(cap <= T_MAX, "grouped gemm: block-scaled chunks hold at most 128 rows");
   if (cap <= 32) return launch_mode<GEMM_SINGLE, 32>(a, stream);
   if (cap <= 64) return launch_mode<GEMM_SINGLE, 64>(a, stream);
   return launch_mode<GEMM_SINGLE, 128>(a, stream);

@@ -140,7 +140,9 @@ def test_fused_channel_c0_against_golden(lo, golden_dir):
 
 
 @pytest.mark.parametrize("E,k,M,H,I", [(8, 2, 1, 256, 128), (8, 2, 33, 512, 256), (16, 4, 200, 1024, 384),
-                                       (4, 1, 300, 256, 128), (32, 8, 64, 7168, 256), (8, 8, 16, 256, 2048)])
+                                       (4, 1, 300, 256, 128), (32, 8, 64, 7168, 256), (8, 8, 16, 256, 2048),
+                                       # experts with 129..256 rows (one chunk, two activation boxes) and more (split)
+                                       (4, 2, 320, 512, 256), (2, 1, 700, 256, 128), (8, 2, 1000, 384, 128)])
 def test_fused_channel_shapes(lo, E, k, M, H, I):
     w1, w2, _, _ = synthetic.make_weights(E, H, I, seed=2)
     w1_s, w2_s = synthetic.make_channel_scales(E, H, I, seed=2)
