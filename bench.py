@@ -152,6 +152,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         cfg["E"] = args.experts
     E, k, M, H, I = cfg["E"], cfg["topk"], cfg["M"], cfg["H"], cfg["I"]
     w1, w2, w1_s, w2_s = synthetic.make_weights(E, H, I, seed=0, device=dev)
+    channel = args.quant == "channel"
+    if channel:
+        # per-channel W8A8 mode of the same layer: same int8 weights, one scale per output channel
+        w1_s, w2_s = synthetic.make_channel_scales(E, H, I, seed=0, device=dev)
+        quant_kw = dict(use_int8_w8a8=True, per_channel_quant=True, block_shape=None)
+    else:
+        quant_kw = dict(use_int8_w8a8=True, block_shape=[128, 128])
     x, logits = synthetic.make_activations(M, H, E, seed=1, device=dev, zipf=cfg.get("zipf"))
     tw = torch.empty(M, k, dtype=torch.float32, device=dev)
     ti = torch.empty(M, k, dtype=torch.int32, device=dev)
@@ -162,7 +169,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     def step():
         lightop_b200.moe.topk_softmax(tw, ti, None, logits, True)
         out_holder["y"] = lightop_b200.moe.fused_experts_impl_int8(
-            x, w1, w2, tw, ti, cache13, use_int8_w8a8=True, block_shape=[128, 128], w1_scale=w1_s, w2_scale=w2_s)
+            x, w1, w2, tw, ti, cache13, w1_scale=w1_s, w2_scale=w2_s, **quant_kw)
 
     # end-to-end arm: pinned host buffers in, pinned host buffer out.  Every step copies its own x and
     # logits in and its own y out; steps are independent, so the copies of neighbouring steps overlap
@@ -201,8 +208,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                 stream.wait_event(out_done[i - 2])          # y of step i-2 has left the device
             lightop_b200.moe.topk_softmax(tw2[b], ti2[b], None, l_d[b], True)
             y = lightop_b200.moe.fused_experts_impl_int8(
-                x_d[b], w1, w2, tw2[b], ti2[b], c13[b], use_int8_w8a8=True, block_shape=[128, 128],
-                w1_scale=w1_s, w2_scale=w2_s)
+                x_d[b], w1, w2, tw2[b], ti2[b], c13[b], w1_scale=w1_s, w2_scale=w2_s, **quant_kw)
             keep.append(y)
             comp_done[i].record(stream)
             with torch.cuda.stream(s_out):
@@ -248,6 +254,11 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     # the experts hit (2I x H each), the int8 activations + scales read once, the int8 act + scales written once.
     g1_bytes = (experts_hit * (2.0 * I * H + 4.0 * (2 * I // 128) * (H // 128)) + M * (H + 4.0 * H / 128)
                 + rows_routed * (I + 4.0 * I / 128))
+    if channel:
+        # per-channel: int8 weights + one scale per channel, int8 activations + one scale per row read,
+        # bf16 gate_up rows written, read again by the SiLU*mul+quant kernel (same stage), int8 act written
+        g1_bytes = (experts_hit * (2.0 * I * H + 4.0 * 2 * I) + M * (H + 4.0)
+                    + rows_routed * (2.0 * 2 * I * 2 + I + 4.0))
     g1_s = stage[2] * 1e-3
     # DRAM traffic of the dominant kernel from the committed ncu captures (profiles/), scaled by the experts hit:
     # 128 rows per expert -> 1.238 GB read + 5.9 MB written per 32 experts; decode-size chunks -> no re-reads.
@@ -257,7 +268,14 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     else:
         traffic = experts_hit / 32.0 * (0.945257e9 + 5.829e6)
         traffic_src = "profiles/grouped_gemm_decode_e32_m64.md (ncu dram bytes of the E=32, M=64 case) x experts_hit/32"
-    roofline = {"bound": "hbm", "kernel": "grouped_gemm_kernel<gate_up>", "achieved": g1_bytes / g1_s / 1e9,
+    if channel:
+        # gate_up launch of the committed capture: 973.8 MB read + 10.6 MB written per 32 experts at 128 rows each
+        # (bf16 output rows scale with the routed rows, not with the experts)
+        traffic = experts_hit / 32.0 * 973.80864e6 + rows_routed / 4096.0 * 10.649856e6
+        traffic_src = ("profiles/grouped_gemm_channel_prefill_e32_m512.md (ncu dram bytes of the E=32, M=512 case): reads x "
+                       "experts_hit/32, writes x routed rows/4096; GEMM launch only")
+    roofline = {"bound": "hbm", "kernel": "grouped_gemm_kernel<channel> + silu_mul_token_quant_kernel" if channel
+                else "grouped_gemm_kernel<gate_up>", "achieved": g1_bytes / g1_s / 1e9,
                 "peak": hbm_peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": g1_bytes / g1_s / 1e9 / hbm_peak,
                 "traffic": traffic, "traffic_source": traffic_src, "ms_per_launch": stage[2],
                 "stage_ms": {"align": stage[0], "group_quant_scatter": stage[1], "gemm_gate_up": stage[2],
@@ -266,7 +284,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     flops = synthetic.alg_flops(M, k, H, I)
 
     cpu = None
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and not channel:
         threads = os.cpu_count() or 1
         n_sample = args.cpu_sample_experts
         v, dt, rows = cpu_baseline(cfg, w1, w2, w1_s, w2_s, x, logits, n_sample, threads)
@@ -277,8 +295,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     line = {
         "metric": METRIC, "value": M / (ms_per_step * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "int8 x int8 -> int32, fp32 block scaling, bf16 in/out", "data": "synthetic",
-        "config": {"workload": name, "E": E, "top_k": k, "M": M, "hidden": H, "intermediate": I,
+        "vs_baseline": None, "dtype": "int8 x int8 -> int32, fp32 %s scaling, bf16 in/out" % ("per-channel" if channel else "block"),
+        "data": "synthetic",
+        "config": {"workload": name + ("+per_channel_quant" if channel else ""), "E": E, "top_k": k, "M": M,
+                   "hidden": H, "intermediate": I,
                    "experts_hit": experts_hit, "l2": "weights (11.3 GB) exceed L2; no flush needed"},
         "tflops": flops / (ms_per_step * 1e-3) / 1e12,
         "layer_alg_gbs": layer_bytes / (ms_per_step * 1e-3) / 1e9,
@@ -286,7 +306,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "e2e": {"value": M / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": x_h.numel() * 2 + l_h.numel() * 4, "d2h_bytes_per_step": y_h[0].numel() * 2,
                 "overlap": "copies of neighbouring steps overlap compute (double-buffered, 3 streams)"},
-        "gpu_launches": 6 * args.steps,
+        "gpu_launches": (7 if channel else 6) * args.steps,
         "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
     }
     return line
@@ -344,6 +364,9 @@ def main():
     ap.add_argument("--workload", default=None)
     ap.add_argument("--tokens", type=int, default=0, help="override the token count M of the workload")
     ap.add_argument("--experts", type=int, default=0, help="override the expert count E (small profiling cases)")
+    ap.add_argument("--quant", default="block", choices=["block", "channel"],
+                    help="block = the 128x128 block-INT8 path (the headline metric); channel = the per-channel W8A8 mode "
+                         "of the same layer (1 GPU, no CPU baseline)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-sample-experts", type=int, default=256)
     args = ap.parse_args()
