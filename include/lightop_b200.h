@@ -225,6 +225,37 @@ int lo_block_int8_linear(const int8_t *A, const float *a_scale, const int8_t *B,
                          int32_t *status, void *stream);
 
 /* ---------------------------------------------------------------------------
+ * Routers upstream of the expert layer other than plain softmax top-k.
+ * ------------------------------------------------------------------------- */
+
+/*
+ * Grouped, bias-corrected sigmoid gate (DeepSeek-V3 style).  Per token: p = sigmoid(x) in fp32, selection
+ * score s = p + bias; the score of an expert group (E / num_expert_group consecutive experts) is the sum of its
+ * two largest s; the topk_group best groups stay; among their experts the (topk - n_share_experts_fusion)
+ * largest s are taken in descending order (ties: lower id); weight = p / sum(p of the taken) times
+ * routed_scaling_factor when apply_routed_scaling_factor_on_output (and the factor is > 0).  The fused shared
+ * experts fill the remaining slots with ids E, E+1, ... and weight (1 / routed_scaling_factor) times the same
+ * output factor.  x [M,E] f32/f16/bf16, bias [E] f32/f16/bf16, topk_weights [M,topk] f32, topk_ids [M,topk]
+ * LO_I32 or LO_I64.  E <= 1024, num_expert_group <= 32, topk <= 32; any configuration that satisfies the
+ * reference's argument rules is accepted (its kernels cover a fixed table of layouts only).
+ * Replaces: op.moe_fused_gate, csrc/kernels/moe_gate/moe_fused_gate.cu:1331-1420 (python/lightop/moe_fused_gate.py:10-31).
+ */
+int lo_moe_fused_gate(const void *x, int x_dtype, const void *bias, int bias_dtype, int64_t M, int E,
+                      int num_expert_group, int topk_group, int topk, int n_share_experts_fusion,
+                      float routed_scaling_factor, int apply_routed_scaling_factor_on_output,
+                      float *topk_weights, void *topk_ids, int ids_dtype, void *stream);
+
+/*
+ * In-place post-processing of top-k ids: ids of tokens at or beyond *num_token_non_padded become -1, the others
+ * go through the logical -> physical expert map (ids outside [0, map_size) become -1).  Either pointer may be
+ * NULL to skip that step.  topk_ids [M,topk] LO_I32 / LO_I64; the map and the count are LO_I32 / LO_I64 device data.
+ * Replaces: op.topk_ids_postprocess, csrc/kernels/topk/topk_ids_postprocess.cu:30-66.
+ */
+int lo_topk_ids_postprocess(void *topk_ids, int ids_dtype, int64_t M, int64_t topk,
+                            const void *logical_to_physical_map, int map_dtype, int64_t map_size,
+                            const void *num_token_non_padded, int num_token_dtype, void *stream);
+
+/* ---------------------------------------------------------------------------
  * Per-channel W8A8 mode of the same MoE layer (one scale per token, one per output channel).
  * ------------------------------------------------------------------------- */
 

@@ -55,6 +55,10 @@ PROTOTYPES = {
     "lo_block_int8_linear_workspace_bytes": (c_size_t, [c_int64]),
     "lo_block_int8_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p,
                                      c_void_p, c_size_t, c_void_p, c_void_p]),
+    "lo_moe_fused_gate": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_int, c_float,
+                                  c_int, c_void_p, c_void_p, c_int, c_void_p]),
+    "lo_topk_ids_postprocess": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_int64, c_void_p, c_int,
+                                        c_void_p]),
     "lo_per_token_quant_int8": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "lo_silu_mul_quant_int8": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),
     "lo_moe_grouped_gemm_i8_channel": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_int64,

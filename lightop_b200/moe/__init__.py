@@ -2,7 +2,8 @@
 from .expert_parallel import ep_build_m_indices, ep_gather, ep_scatter
 from .gemm import moe_gemm_w8a8
 from .native import fused_experts_impl_int8, fused_experts_impl_int8_marlin
-from .routing import moe_align_block_size, moe_align_block_size_out, moe_sum, topk_softmax
+from .routing import (moe_align_block_size, moe_align_block_size_out, moe_fused_gate, moe_sum, topk_ids_postprocess,
+                      topk_softmax)
 
 __all__ = [
     "ep_build_m_indices",
@@ -12,7 +13,9 @@ __all__ = [
     "fused_experts_impl_int8_marlin",
     "moe_align_block_size",
     "moe_align_block_size_out",
+    "moe_fused_gate",
     "moe_gemm_w8a8",
     "moe_sum",
+    "topk_ids_postprocess",
     "topk_softmax",
 ]

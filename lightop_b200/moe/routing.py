@@ -139,3 +139,65 @@ def moe_sum(input: torch.Tensor, output: torch.Tensor, bias: Optional[torch.Tens
                                     M, topk, H, float(factor), _lib.ptr(expert_mask), _lib.ptr(num_local_tokens),
                                     _lib.current_stream(input.device))
     _lib.check(st, "moe_sum")
+
+
+def moe_fused_gate(x: torch.Tensor, bias: torch.Tensor, num_expert_group: int, topk_group: int, topk: int,
+                   n_share_experts_fusion: int, routed_scaling_factor: float,
+                   apply_routed_scaling_factor_on_output: bool = True,
+                   output_indices_int64: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Grouped, bias-corrected sigmoid gate; returns ``(weights fp32 [M,topk], ids [M,topk])``.
+
+    Signature of the reference (python/lightop/moe_fused_gate.py:10-31).  Selection and weights
+    follow its kernel and test model (csrc/kernels/moe_gate/moe_fused_gate.cu:130-315,
+    test/ci_tests/test_fused_moe_gate.py:9-117): scores ``sigmoid(x) + bias`` choose groups (sum of
+    the two best scores per group) and then experts, in descending order with the lower id winning
+    ties; weights are the unbiased ``sigmoid(x)`` of the chosen experts divided by their sum, times
+    ``routed_scaling_factor`` when applied on the output; fused shared experts take ids
+    ``num_experts + j``.  Any layout that satisfies the reference's argument rules is accepted.
+    """
+    _lib.require_cuda(x, bias)
+    if x.dim() != 2:
+        raise RuntimeError(f"moe_fused_gate: input must have shape [tokens, experts], got {tuple(x.shape)}")
+    if bias.dim() != 1 or bias.numel() != x.shape[1]:
+        raise RuntimeError(f"moe_fused_gate: bias must have shape [experts], got {tuple(bias.shape)}")
+    if not (x.is_contiguous() and bias.is_contiguous()):
+        raise RuntimeError("moe_fused_gate: input and bias must be contiguous")
+    M, E = x.shape
+    weights = torch.empty(M, topk, dtype=torch.float32, device=x.device)
+    ids = torch.empty(M, topk, dtype=torch.int64 if output_indices_int64 else torch.int32, device=x.device)
+    with torch.cuda.device(x.device):
+        st = _lib.load().lo_moe_fused_gate(_lib.ptr(x), _lib.dtype_code(x.dtype), _lib.ptr(bias),
+                                           _lib.dtype_code(bias.dtype), M, E, int(num_expert_group), int(topk_group),
+                                           int(topk), int(n_share_experts_fusion), float(routed_scaling_factor),
+                                           int(bool(apply_routed_scaling_factor_on_output)), _lib.ptr(weights),
+                                           _lib.ptr(ids), _lib.dtype_code(ids.dtype), _lib.current_stream(x.device))
+    _lib.check(st, "moe_fused_gate")
+    return weights, ids
+
+
+def topk_ids_postprocess(topk_ids: torch.Tensor, logical_to_physical_map: Optional[torch.Tensor] = None,
+                         num_token_non_padded: Optional[torch.Tensor] = None) -> None:
+    """In place: padded tokens' ids become -1, the others are mapped logical -> physical
+    (reference: csrc/kernels/topk/topk_ids_postprocess.cu:30-66, known answer in
+    test/test_native_categorized_moe_api.py:147-169)."""
+    if topk_ids.numel() == 0:
+        return
+    _lib.require_cuda(topk_ids, logical_to_physical_map, num_token_non_padded)
+    if topk_ids.dim() != 2:
+        raise RuntimeError("topk_ids_postprocess expects 2D topk_ids")
+    if not topk_ids.is_contiguous():
+        raise RuntimeError("topk_ids_postprocess expects contiguous topk_ids")
+    for t, name in ((topk_ids, "topk_ids"), (logical_to_physical_map, "logical_to_physical_map"),
+                    (num_token_non_padded, "num_token_non_padded")):
+        if t is not None and t.dtype not in (torch.int32, torch.int64):
+            raise RuntimeError(f"{name} expects int32 or int64 tensor")
+    m = logical_to_physical_map
+    n = num_token_non_padded
+    with torch.cuda.device(topk_ids.device):
+        st = _lib.load().lo_topk_ids_postprocess(
+            _lib.ptr(topk_ids), _lib.dtype_code(topk_ids.dtype), topk_ids.shape[0], topk_ids.shape[1],
+            _lib.ptr(m.contiguous()) if m is not None else 0, _lib.dtype_code(m.dtype) if m is not None else 0,
+            m.numel() if m is not None else 0,
+            _lib.ptr(n) if n is not None else 0, _lib.dtype_code(n.dtype) if n is not None else 0,
+            _lib.current_stream(topk_ids.device))
+    _lib.check(st, "topk_ids_postprocess")

@@ -123,3 +123,13 @@ def reference_channel_functions(per_token_quant):
           "native_w8a8_per_token_matmul": mm}
     exec(compile(ast.Module(body=body, type_ignores=[]), "benchmark_moe_int8.py", "exec"), ns)
     return mm, ns["torch_w8a8_per_column_moe"]
+
+
+def reference_gate_model():
+    """``requested_baseline_moe_gate`` (with ``biased_grouped_topk_impl``) from
+    test/ci_tests/test_fused_moe_gate.py:9-117: the reference's torch model of ``moe_fused_gate``."""
+    fns = extract_functions("test/ci_tests/test_fused_moe_gate.py",
+                            ["biased_grouped_topk_impl", "requested_baseline_moe_gate"])
+    # the second function calls the first by name: give both the same globals
+    fns["requested_baseline_moe_gate"].__globals__["biased_grouped_topk_impl"] = fns["biased_grouped_topk_impl"]
+    return fns["requested_baseline_moe_gate"]

@@ -3,6 +3,7 @@
 Run where a reference checkout is available (``$LIGHTOP_REF`` or ``/root/reference``):
     python tests/golden/make_golden.py            (all fixtures)
     python tests/golden/make_golden.py channel    (only channel_cases.pt)
+    python tests/golden/make_golden.py gate       (only gate_cases.pt)
 The outputs are produced by the reference code itself (loaded by oracle/ref_extract.py),
 not by the restatement in oracle/moe_block_int8.py; the tests then hold both the oracle
 and the CUDA kernels to these files.  Inputs are not stored: they are regenerated from
@@ -97,9 +98,41 @@ def main_channel() -> None:
     print("wrote channel_cases.pt")
 
 
+GATE_CASES = [  # (tokens, experts, groups, topk_group, topk, shared, routed_scaling_factor, seed)
+    (64, 256, 8, 4, 8, 0, 2.5, 21),       # DeepSeek-V3 layout
+    (33, 256, 8, 4, 9, 1, 2.5, 22),       # with one fused shared expert
+    (16, 128, 4, 2, 6, 0, 1.0, 23),
+    (20, 384, 1, 1, 8, 0, 2.827, 24),     # single group
+    (7, 128, 1, 1, 8, 1, 16.0, 25),
+]
+
+
+def gate_inputs(case):
+    M, E, _, _, _, _, _, seed = case
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(M, E, generator=g), torch.randn(E, generator=g)
+
+
+def main_gate() -> None:
+    """Fixtures of the grouped sigmoid gate (tests/golden/gate_cases.pt): outputs of the reference's torch model,
+    canonicalised by expert id as its own test does (test/ci_tests/test_fused_moe_gate.py:160-167)."""
+    model = ref_extract.reference_gate_model()
+    out = []
+    for case in GATE_CASES:
+        x, b = gate_inputs(case)
+        w, i = model(x, b, *case[2:7])
+        order = torch.argsort(i, dim=-1)
+        out.append(dict(case=case, ids=torch.gather(i, 1, order), weights=torch.gather(w, 1, order)))
+    torch.save(out, os.path.join(HERE, "gate_cases.pt"))
+    print("wrote gate_cases.pt")
+
+
 if __name__ == "__main__":
     if len(sys.argv) > 1 and sys.argv[1] == "channel":
         main_channel()
+    elif len(sys.argv) > 1 and sys.argv[1] == "gate":
+        main_gate()
     else:
         main()
         main_channel()
+        main_gate()
