@@ -317,6 +317,39 @@ int lo_fused_moe_channel_int8(const void *x, int x_dtype, const int8_t *w1, cons
                               void *workspace, size_t workspace_bytes, int32_t *status, void *stream);
 
 /*
+ * fuse_silu_mul_quant on the masked expert-parallel layout: input bf16 [groups, group_rows, 2*d]; only the first
+ * tokens_per_group[g] (i32, device) rows of group g are processed, the others are left untouched.
+ * q int8 [groups, group_rows, d], s f32 [groups, group_rows].
+ * Replaces: op.fuse_silu_mul_quant_ep, csrc/kernels/gated_activation/fuse_silu_mul_quant_ep.cu
+ * (python/lightop/fuse_silu_mul_quant.py:235-252).
+ */
+int lo_silu_mul_quant_int8_masked(const void *input, int64_t groups, int64_t group_rows, int64_t d,
+                                  const int32_t *tokens_per_group, int8_t *q, float *s, void *stream);
+
+/*
+ * Per-channel grouped INT8 GEMMs on rows that are already grouped by expert (the layouts expert-parallel
+ * dispatchers produce): C[m, n] = float(sum_k A_q[m, k] * B_q[e(m), n, k]) * a_s[m] * b_s[e(m), n], bf16 out.
+ *   contiguous: A [M, K], m_indices i32 [M] = expert of each row, -1 for padding rows (their output rows are
+ *               left untouched).  Layout contract: an expert's rows are consecutive, padding rows come at the end
+ *               of its range, and every 128-row block holds rows of one expert (ranges padded to a multiple of
+ *               128); a block that breaks the contract is skipped and code 20 is written to *status.
+ *   masked:     A [E, max_m, K], masked_m i32 [E] = rows that exist per expert; C [E, max_m, N].
+ * a_scale f32 [rows], B int8 [E, N, K] (plain layout), b_scale f32 [E, N].  N and K multiples of 128.
+ * workspace: lo_m_grouped_gemm_workspace_bytes(total rows, E) bytes, 256-byte aligned.
+ * Replaces: op.m_grouped_w8a8_gemm_nt_contig_asm (python/lightop/gemmopt.py:744-751) and
+ * op.m_grouped_marlin_w8a8_gemm_nt_masked_asm (python/lightop/gemmopt.py:604-617), which take weights
+ * pre-shuffled for the reference's matrix cores; reference models test/w8a8/test_w8a8_deepgemm_contig.py:106-147
+ * and test/deepgemm/w8a8_moe_groupgemm_mask_marlin_correctness.py:40-57.
+ */
+size_t lo_m_grouped_gemm_workspace_bytes(int64_t total_rows, int num_groups);
+int lo_m_grouped_w8a8_gemm_nt_contig(const int8_t *A, const float *a_scale, const int8_t *B, const float *b_scale,
+                                     void *C, const int32_t *m_indices, int64_t M, int E, int64_t N, int64_t K,
+                                     void *workspace, size_t workspace_bytes, int32_t *status, void *stream);
+int lo_m_grouped_w8a8_gemm_nt_masked(const int8_t *A, const float *a_scale, const int8_t *B, const float *b_scale,
+                                     void *C, const int32_t *masked_m, int E, int64_t max_m, int64_t N, int64_t K,
+                                     void *workspace, size_t workspace_bytes, int32_t *status, void *stream);
+
+/*
  * Per-stage timing of lo_fused_moe_block_int8 for benchmarks: while enabled (per host thread), the
  * call records CUDA events between its five kernels (align, group quant, gate_up GEMM, down GEMM,
  * top-k sum); lo_profile_read waits for the last one and returns the five durations in

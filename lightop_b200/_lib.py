@@ -69,6 +69,12 @@ PROTOTYPES = {
                                           c_void_p, c_int, c_void_p, c_int, c_int64, c_int, c_int, c_int64, c_int64,
                                           c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_size_t,
                                           c_void_p, c_void_p]),
+    "lo_silu_mul_quant_int8_masked": (c_int, [c_void_p, c_int64, c_int64, c_int64, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "lo_m_grouped_gemm_workspace_bytes": (c_size_t, [c_int64, c_int]),
+    "lo_m_grouped_w8a8_gemm_nt_contig": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                                 c_int, c_int64, c_int64, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "lo_m_grouped_w8a8_gemm_nt_masked": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                                 c_int64, c_int64, c_int64, c_void_p, c_size_t, c_void_p, c_void_p]),
     "lo_profile_enable": (c_int, [c_int]),
     "lo_profile_read": (c_int, [c_void_p]),
     "lo_ep_scatter": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,

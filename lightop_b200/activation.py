@@ -48,3 +48,42 @@ def fuse_silu_mul_quant(input: torch.Tensor, num_local_tokens_tensor: Optional[t
                                                 _lib.current_stream(input.device))
     _lib.check(st, "fuse_silu_mul_quant")
     return output, scales
+
+
+def fuse_silu_mul_quant_ep(input: torch.Tensor, tokens_per_expert: Optional[torch.Tensor] = None,
+                           num_local_tokens_tensor: Optional[torch.Tensor] = None, topk: int = 1,
+                           expect_m: int = -1) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``fuse_silu_mul_quant`` on the masked layout ``[E, T, 2*d]``: only the first
+    ``tokens_per_expert[e]`` rows of expert ``e`` are processed (all rows without it).
+
+    Signature of the reference (python/lightop/fuse_silu_mul_quant.py:235-252): returns
+    ``(int8 [E, T, d], fp32 [E, T, 1])``; rows that are not processed hold unspecified values.
+    ``num_local_tokens_tensor`` / ``expect_m`` (launch-shaping hints there) are not implemented / ignored.
+    """
+    if input.dim() != 3:
+        raise ValueError(f"Input tensor must be 3-dimensional [E, T, H], but got shape {input.shape}")
+    if num_local_tokens_tensor is not None:
+        raise NotImplementedError("num_local_tokens_tensor is not implemented")
+    _lib.require_cuda(input, tokens_per_expert)
+    if input.dtype != torch.bfloat16:
+        raise RuntimeError("fuse_silu_mul_quant_ep expects bfloat16 input")
+    if not input.is_contiguous():
+        input = input.contiguous()
+    E, T, H = input.shape
+    d = H // 2
+    if H % 16 != 0:
+        raise RuntimeError("the row length must be a multiple of 16")
+    output = torch.empty(E, T, d, dtype=torch.int8, device=input.device)
+    scales = torch.empty((E, T, 1), device=input.device, dtype=torch.float32)
+    if E * T == 0:
+        return output, scales
+    counts = None
+    if tokens_per_expert is not None:
+        if tokens_per_expert.numel() != E:
+            raise RuntimeError("tokens_per_expert must hold one count per expert")
+        counts = tokens_per_expert.to(torch.int32).contiguous()
+    with torch.cuda.device(input.device):
+        st = _lib.load().lo_silu_mul_quant_int8_masked(_lib.ptr(input), E, T, d, _lib.ptr(counts), _lib.ptr(output),
+                                                       _lib.ptr(scales), _lib.current_stream(input.device))
+    _lib.check(st, "fuse_silu_mul_quant_ep")
+    return output, scales

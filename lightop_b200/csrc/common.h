@@ -80,8 +80,10 @@ int launch_token_quant(const void *x, int x_dtype, int64_t M, int64_t K, int top
 
 // act = bf16(bf16(silu(gate)) * up) of bf16 rows [rows, 2*d], then per-token quantisation.  Rows at or
 // beyond *num_rows_dev and rows whose row_ids entry is a padding sentinel are skipped (both optional).  quant.cu
+// With group_counts the rows form [groups, group_rows] and only the first group_counts[g] rows of group g exist.
 int launch_silu_mul_token_quant(const void *in, int64_t rows, int64_t d, const int32_t *row_ids, int64_t numel_valid,
-                                const int32_t *num_rows_dev, int8_t *q, float *s, cudaStream_t stream);
+                                const int32_t *num_rows_dev, int8_t *q, float *s, cudaStream_t stream,
+                                int64_t group_rows = 0, const int32_t *group_counts = nullptr);
 
 // Copy int8 rows and their scales into sorted-position order: row(pos) = sorted_ids[pos] / top_k.
 // scales_per_row = 0 means K / 128 (block scales); 1 is the per-token format.  reduce.cu

@@ -214,10 +214,13 @@ __global__ void __launch_bounds__(TOKEN_QUANT_THREADS) token_quant_kernel(const 
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(TOKEN_QUANT_THREADS) silu_mul_token_quant_kernel(
     const __nv_bfloat16 *__restrict__ in, int64_t d, const int32_t *__restrict__ row_ids, int64_t numel_valid,
-    const int32_t *__restrict__ num_rows_dev, int8_t *__restrict__ q, float *__restrict__ s) {
+    const int32_t *__restrict__ num_rows_dev, int64_t group_rows, const int32_t *__restrict__ group_counts,
+    int8_t *__restrict__ q, float *__restrict__ s) {
   __shared__ float red[8];
   const int64_t row = blockIdx.x;
   if (num_rows_dev && row >= *num_rows_dev) return;
+  // masked layout [groups, group_rows, 2d]: only the first group_counts[g] rows of a group exist
+  if (group_counts && row % group_rows >= group_counts[row / group_rows]) return;
   if (row_ids) {
     const int32_t id = row_ids[row];
     if (id < 0 || id >= numel_valid) return;
@@ -321,12 +324,14 @@ int launch_token_quant(const void *x, int x_dtype, int64_t M, int64_t K, int top
 }
 
 int launch_silu_mul_token_quant(const void *in, int64_t rows, int64_t d, const int32_t *row_ids, int64_t numel_valid,
-                                const int32_t *num_rows_dev, int8_t *q, float *s, cudaStream_t stream) {
+                                const int32_t *num_rows_dev, int8_t *q, float *s, cudaStream_t stream,
+                                int64_t group_rows, const int32_t *group_counts) {
   if (rows == 0) return LO_OK;
   LO_REQUIRE(d >= 8 && d % 8 == 0, "silu-mul quant: width %lld must be a multiple of 8", (long long)d);
   LO_REQUIRE(rows <= 0x7fffffffLL, "silu-mul quant: too many rows");
   silu_mul_token_quant_kernel<<<(unsigned)rows, TOKEN_QUANT_THREADS, 0, stream>>>(
-      static_cast<const __nv_bfloat16 *>(in), d, row_ids, numel_valid, num_rows_dev, q, s);
+      static_cast<const __nv_bfloat16 *>(in), d, row_ids, numel_valid, num_rows_dev, group_rows > 0 ? group_rows : 1,
+      group_counts, q, s);
   LO_LAUNCH_OK("silu_mul_token_quant_kernel");
   return LO_OK;
 }
@@ -352,6 +357,18 @@ extern "C" int lo_silu_mul_quant_int8(const void *input, int64_t rows, int64_t d
   LO_REQUIRE((reinterpret_cast<uintptr_t>(input) & 15) == 0 && (reinterpret_cast<uintptr_t>(q) & 7) == 0,
              "silu-mul quant: input must be 16-byte and q 8-byte aligned");
   return launch_silu_mul_token_quant(input, rows, d, nullptr, 0, nullptr, q, s, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int lo_silu_mul_quant_int8_masked(const void *input, int64_t groups, int64_t group_rows, int64_t d,
+                                             const int32_t *tokens_per_group, int8_t *q, float *s, void *stream) {
+  using namespace lo;
+  LO_REQUIRE(groups >= 0 && group_rows >= 0, "silu-mul quant: negative shape");
+  if (groups * group_rows == 0) return LO_OK;
+  LO_REQUIRE(input && q && s, "silu-mul quant: null pointer");
+  LO_REQUIRE((reinterpret_cast<uintptr_t>(input) & 15) == 0 && (reinterpret_cast<uintptr_t>(q) & 7) == 0,
+             "silu-mul quant: input must be 16-byte and q 8-byte aligned");
+  return launch_silu_mul_token_quant(input, groups * group_rows, d, nullptr, 0, nullptr, q, s,
+                                     static_cast<cudaStream_t>(stream), group_rows, tokens_per_group);
 }
 
 extern "C" int lo_group_quant_int8(const void *x, int x_dtype, int64_t num_groups, int group_size,

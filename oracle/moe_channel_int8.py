@@ -10,6 +10,10 @@ Parity status: PARTLY PINNED.
   * ``fused_moe_channel_int8`` is checked against the reference's composed torch model
     ``torch_w8a8_per_column_moe`` (test/moe_w8a8/benchmark_moe_int8.py:163-201) within the
     bf16 tolerance of the layer (the two differ in where bf16 roundings fall, see below).
+  * ``grouped_matmul_contig`` / ``grouped_matmul_masked`` are checked bit-for-bit against the reference's
+    ``torch_gemm`` (test/w8a8/test_w8a8_deepgemm_contig.py:106-147) and
+    ``native_w8a8_perChannel_batch_matmul``
+    (test/deepgemm/w8a8_moe_groupgemm_mask_marlin_correctness.py:40-57) where a reference checkout exists.
   * ``per_token_quant_int8`` and ``silu_mul_quant_int8`` restate GPU-only code of the
     reference (a Triton kernel and a HIP kernel) that cannot run where the fixtures are
     made: PARITY UNPINNED for these two; they follow the formulas of the cited lines.
@@ -123,3 +127,37 @@ def fused_moe_channel_int8(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
     if return_intermediates:
         return y, dict(x_q=x_q, x_s=x_s, cache3=cache3.reshape(M, k, H), experts=inter_all)
     return y
+
+
+def grouped_matmul_contig(A: torch.Tensor, As: torch.Tensor, B: torch.Tensor, Bs: torch.Tensor,
+                          m_indices: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Contiguous grouped layout: ``out[m] = (A[m] . B[e]) * As[m] * Bs[e]`` with ``e = m_indices[m]``;
+    rows with index -1 (or outside the expert range) keep the value they have in ``out``.
+
+    Restates ``torch_gemm`` with alpha 1 and beta 0 (test/w8a8/test_w8a8_deepgemm_contig.py:106-147):
+    fp32 dot product (exact here: summed in fp64 and rounded once), times the row scale, times the
+    channel scale, cast to the output type.
+    """
+    res = out.clone()
+    E = B.shape[0]
+    for e in range(E):
+        rows = torch.nonzero(m_indices == e).reshape(-1)
+        if rows.numel():
+            res[rows] = per_token_matmul(A[rows], B[e], As[rows], Bs[e], out.dtype)
+    return res
+
+
+def grouped_matmul_masked(A: torch.Tensor, As: torch.Tensor, B: torch.Tensor, Bs: torch.Tensor,
+                          masked_m: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """Masked grouped layout: ``out[e, :masked_m[e]] = (A[e] @ B[e]^T) * As[e] * Bs[e]``; other rows keep their value.
+
+    Restates ``native_w8a8_perChannel_batch_matmul``
+    (test/deepgemm/w8a8_moe_groupgemm_mask_marlin_correctness.py:40-57), which computes every row, limited
+    to the rows the kernel is asked for (:139-147).
+    """
+    res = out.clone()
+    for e in range(B.shape[0]):
+        m = int(masked_m[e])
+        if m > 0:
+            res[e, :m] = per_token_matmul(A[e, :m], B[e], As[e, :m].reshape(-1, 1), Bs[e].reshape(-1), out.dtype)
+    return res

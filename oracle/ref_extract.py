@@ -133,3 +133,11 @@ def reference_gate_model():
     # the second function calls the first by name: give both the same globals
     fns["requested_baseline_moe_gate"].__globals__["biased_grouped_topk_impl"] = fns["biased_grouped_topk_impl"]
     return fns["requested_baseline_moe_gate"]
+
+
+def reference_grouped_layout_models():
+    """(``torch_gemm`` of the contiguous layout, ``native_w8a8_perChannel_batch_matmul`` of the masked one)."""
+    contig = extract_functions("test/w8a8/test_w8a8_deepgemm_contig.py", ["torch_gemm"])["torch_gemm"]
+    masked = extract_functions("test/deepgemm/w8a8_moe_groupgemm_mask_marlin_correctness.py",
+                               ["native_w8a8_perChannel_batch_matmul"])["native_w8a8_perChannel_batch_matmul"]
+    return contig, masked

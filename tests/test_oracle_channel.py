@@ -101,3 +101,30 @@ def test_against_reference_functions(c0):
     assert torch.equal(OC.per_token_matmul(A, B, As, Bs, torch.bfloat16), mm(A, B, As, Bs, output_dtype=torch.bfloat16))
     y_ref = moe(x, w1, w2, w1_s, w2_s, gold["topk_weights"], gold["topk_ids"], gold["topk_ids"].shape[1])
     assert torch.equal(y_ref, gold["y"])
+
+
+@pytest.mark.skipif(ref_extract.reference_root() is None, reason="no reference checkout")
+def test_grouped_layouts_against_reference_models(capsys):
+    contig, masked = ref_extract.reference_grouped_layout_models()
+    g = torch.Generator().manual_seed(17)
+    # contiguous: 3 experts, ranges padded to 8 rows here (the model has no alignment rule), tiny N and K
+    M, N, K, E = 24, 6, 64, 3
+    A = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int8)
+    B = torch.randint(-127, 128, (E, N, K), generator=g, dtype=torch.int8)
+    As = torch.rand(M, generator=g) * 0.05
+    Bs = torch.rand(E, N, generator=g) * 1e-3
+    m_indices = torch.tensor([0] * 5 + [-1] * 3 + [1] * 8 + [2] * 2 + [-1] * 6, dtype=torch.int32)
+    base = torch.full((M, N), 7.0, dtype=torch.bfloat16)
+    ref = contig(A, B, base, As, Bs, 1.0, 0.0, m_index_h=m_indices)
+    assert torch.equal(OC.grouped_matmul_contig(A, As, B, Bs, m_indices, base), ref)
+    # masked
+    Em, T = 2, 5
+    A3 = torch.randint(-127, 128, (Em, T, K), generator=g, dtype=torch.int8)
+    B3 = torch.randint(-127, 128, (Em, N, K), generator=g, dtype=torch.int8)
+    As3 = torch.rand(Em, T, 1, generator=g) * 0.05
+    Bs3 = torch.rand(Em, N, 1, generator=g) * 1e-3
+    full = masked(A3, B3, As3, Bs3, torch.bfloat16)
+    capsys.readouterr()      # the reference function prints shapes
+    mm = torch.tensor([5, 3], dtype=torch.int32)
+    got = OC.grouped_matmul_masked(A3, As3, B3, Bs3, mm, torch.zeros(Em, T, N, dtype=torch.bfloat16))
+    assert torch.equal(got[0], full[0]) and torch.equal(got[1, :3], full[1, :3]) and bool((got[1, 3:] == 0).all())
