@@ -56,6 +56,7 @@ class ClockSampler:
         self.reasons = set()
         self.max_mhz = None
         self._stop = threading.Event()
+        self._first = threading.Event()
         self.thread = None
         self.error = None
 
@@ -81,14 +82,16 @@ class ClockSampler:
                 for name, bit in self.REASONS.items():
                     if mask & bit:
                         self.reasons.add(name)
+                self._first.set()
                 time.sleep(self.period)
         except Exception as e:  # NVML missing or refused: report it, do not fail the benchmark
             self.error = repr(e)
+            self._first.set()
 
     def start(self):
         self.thread = threading.Thread(target=self._run, daemon=True)
         self.thread.start()
-        time.sleep(0.02)      # let the first sample land before the timed region starts
+        self._first.wait(timeout=5.0)      # NVML start-up can take a while: the first sample lands before the timed region
 
     def stop(self):
         self._stop.set()

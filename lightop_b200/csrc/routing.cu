@@ -156,12 +156,15 @@ __global__ void __launch_bounds__(ALIGN_WARPS * 32) align_kernel(
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
+  // warps that get a segment: with few ids (decode) only the first ones, so that the histogram rows to
+  // clear and to scan shrink with the input
+  const int nw = (int)(numel >= (int64_t)ALIGN_WARPS * 32 ? ALIGN_WARPS : (numel + 31) / 32 > 0 ? (numel + 31) / 32 : 1);
   for (int64_t i = tid; i < sorted_capacity; i += blockDim.x) sorted_ids[i] = (int32_t)numel;
-  for (int i = tid; i < ALIGN_WARPS * E; i += blockDim.x) hist[i] = 0;
+  for (int i = tid; i < nw * E; i += blockDim.x) hist[i] = 0;
   __syncthreads();
 
   // segment of this warp, a multiple of 32 ids long
-  int64_t seg_len = (numel + ALIGN_WARPS - 1) / ALIGN_WARPS;
+  int64_t seg_len = (numel + nw - 1) / nw;
   seg_len = (seg_len + 31) / 32 * 32;
   const int64_t seg_begin = (int64_t)warp * seg_len;
   const int64_t seg_end = seg_begin + seg_len < numel ? seg_begin + seg_len : numel;
@@ -178,7 +181,7 @@ __global__ void __launch_bounds__(ALIGN_WARPS * 32) align_kernel(
   // per expert: exclusive prefix over the warps, total count
   for (int e = tid; e < E; e += blockDim.x) {
     int run = 0;
-    for (int w = 0; w < ALIGN_WARPS; ++w) {
+    for (int w = 0; w < nw; ++w) {
       const int c = hist[w * E + e];
       hist[w * E + e] = run;
       run += c;
