@@ -65,9 +65,10 @@ constexpr int W_TILE_BYTES = TILE_N * TILE_K;   // 16 KiB
 constexpr uint32_t TMEM_COLS = 512;
 // 2^23 + 2^22: adding it to an int32 of magnitude < 2^22 and reading the bits as fp32 gives
 // 12582912 + value exactly, so (that - 12582912.0f) is the exact int->float conversion
-// (|128-long int8 dot| <= 128 * 127 * 127 < 2^21).  The addition costs nothing: every partial
-// buffer holds MAGIC_I whenever it is free (filled at start-up, refilled by the promotion warps
-// right after they read a partial) and all MMAs accumulate, so the tensor core adds it.
+// (|128-long int8 dot| <= 128 * 127 * 127 < 2^21).  The integer addition runs on the integer pipe,
+// which the promotion loop leaves idle; the conversion instruction proper is an order of magnitude
+// slower.  (Letting the tensor core add the offset, by keeping free partial buffers filled with it,
+// was measured slower: the refill is one more tensor-memory store per piece.)
 constexpr uint32_t MAGIC_I = 0x4B400000u;
 constexpr float MAGIC_F = 12582912.0f;
 
@@ -323,7 +324,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   SM &sm = *reinterpret_cast<SM *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
   const int tid = threadIdx.x;
-  const int warp = tid >> 5;
+  // broadcast from lane 0 so that the compiler knows the warp index (and everything derived from it:
+  // roles, tensor-memory addresses, barrier addresses) is uniform across the warp
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);
   const int lane = tid & 31;
 
   // ------------------------------ set-up -----------------------------------
@@ -351,15 +354,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = sm.tmem_base;
-  if (warp >= 4 && MODE != GEMM_CHANNEL) {
-    // fill every partial buffer with the conversion offset (see MAGIC_I)
-    const uint32_t base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + ACC_COLS;
-    for (int pc = (warp - 4) >> 2; pc < NBUF * A_ROWS / 16; pc += 4) tmem_st16_fill(base + pc * 16, MAGIC_I);
-    tmem_st_wait();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
 
   const int num_chunks = *p.num_chunks;
   const int64_t num_items = (int64_t)num_chunks * p.n_tiles;
@@ -446,7 +440,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
                 const uint32_t d = tmem_base + ACC_COLS + b * (uint32_t)A_ROWS;
 #pragma unroll
                 for (int k4 = 0; k4 < TILE_K / 32; ++k4)
-                  umma_i8(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, 1u);
+                  umma_i8(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, k4 != 0 ? 1u : 0u);
                 umma_commit(&sm.tmem_full[b]);
               }
               if (!ok) break;
@@ -646,6 +640,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         }
       }
 
+      if (MODE != GEMM_CHANNEL) {
+        // the running sums of this item start at zero (all warps have left the previous item's epilogue:
+        // see the rendezvous at the end of the item loop), so the K loop below needs no first-block case
+        for (int pc = 0; pc < my_p * NUM_W; ++pc) {
+          const int w = pc / my_p, pq = pc % my_p;
+          tmem_st16_fill(tmem_base + lane_off + (uint32_t)(w * A_ROWS + col_begin + pq * 16), 0u);
+        }
+        tmem_st_wait();
+      }
       const int kb_end = MODE == GEMM_CHANNEL ? 0 : KB;   // the block-scaled modes promote once per K block
       for (int kb = 0; kb < kb_end && ok; ++kb, ++it) {
         const int slot = it % SC_SLOTS;
@@ -664,22 +667,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           for (int pc = 0; pc < my_p; ++pc) {
             uint32_t raw[16], accv[16];
             tmem_ld16(part + pc * 16, raw);
-            if (kb > 0) {
-              tmem_ld16(accp + pc * 16, accv);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 16; ++j) accv[j] = 0u;
-            }
+            tmem_ld16(accp + pc * 16, accv);
             tmem_ld_wait();
-            tmem_st16_fill(part + pc * 16, MAGIC_I);   // hand the buffer back ready for the next accumulation
             const ulonglong2 *scv = reinterpret_cast<const ulonglong2 *>(&sm.sc[slot][w][col_begin + pc * 16]);
 #pragma unroll
             for (int j4 = 0; j4 < 4; ++j4) {
               const ulonglong2 sc = scv[j4];     // scale products of four tokens
               const uint32_t *r = &raw[j4 * 4];
-              // exact int -> float: the partial already carries MAGIC_I; read as fp32, minus MAGIC_F
-              const uint64_t f01 = add2(pack2(__uint_as_float(r[0]), __uint_as_float(r[1])), neg_magic2);
-              const uint64_t f23 = add2(pack2(__uint_as_float(r[2]), __uint_as_float(r[3])), neg_magic2);
+              // exact int -> float: add MAGIC_I as an integer, read as fp32, subtract MAGIC_F
+              const uint64_t f01 = add2(pack2(__uint_as_float(r[0] + MAGIC_I), __uint_as_float(r[1] + MAGIC_I)), neg_magic2);
+              const uint64_t f23 = add2(pack2(__uint_as_float(r[2] + MAGIC_I), __uint_as_float(r[3] + MAGIC_I)), neg_magic2);
               const uint64_t a01 = add2(pack2(__uint_as_float(accv[j4 * 4 + 0]), __uint_as_float(accv[j4 * 4 + 1])),
                                         mul2_rounded(f01, sc.x, negzero2));
               const uint64_t a23 = add2(pack2(__uint_as_float(accv[j4 * 4 + 2]), __uint_as_float(accv[j4 * 4 + 3])),
