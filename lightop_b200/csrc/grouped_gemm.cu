@@ -861,10 +861,13 @@ template <int MODE, int A_ROWS>
 int launch_mode(const GemmArgs &a, cudaStream_t stream) {
   using SM = Smem<MODE, A_ROWS>;
   const size_t smem_bytes = sizeof(SM) + 1024;
-  static thread_local bool configured = false;
-  if (!configured) {
+  // the attribute belongs to the (kernel, device) pair: set it once per device this thread launches on
+  static thread_local uint64_t configured_devices = 0;
+  int dev = 0;
+  LO_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !((configured_devices >> dev) & 1u)) {
     LO_CUDA_OK(cudaFuncSetAttribute(grouped_gemm_kernel<MODE, A_ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_bytes));
-    configured = true;
+    if (dev >= 0 && dev < 64) configured_devices |= (uint64_t)1 << dev;
   }
   CUtensorMap wmap;
   int rc = make_tile_map(&wmap, a.B, (int64_t)a.E * a.n_rows_per_expert, a.K, TILE_N);
