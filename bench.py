@@ -264,12 +264,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                     + rows_routed * (2.0 * 2 * I * 2 + I + 4.0))
     g1_s = stage[2] * 1e-3
     # DRAM traffic of the dominant kernel from the committed ncu captures (profiles/), scaled by the experts hit:
-    # 128 rows per expert -> 1.238 GB read + 5.9 MB written per 32 experts; decode-size chunks -> no re-reads.
+    # 128 rows per expert -> 1.208 GB read + 4.3 MB written per 32 experts; decode-size chunks -> no re-reads.
     if rows_routed / max(experts_hit, 1) > 64:
-        traffic = experts_hit / 32.0 * (1.237975e9 + 5.887e6)
+        traffic = experts_hit / 32.0 * (1.208155e9 + 4.270e6)
         traffic_src = "profiles/grouped_gemm_prefill_e32_m512.md (ncu dram bytes of the E=32, M=512 case) x experts_hit/32"
     else:
-        traffic = experts_hit / 32.0 * (0.945257e9 + 5.829e6)
+        traffic = experts_hit / 32.0 * (0.945233e9 + 4.008e6)
         traffic_src = "profiles/grouped_gemm_decode_e32_m64.md (ncu dram bytes of the E=32, M=64 case) x experts_hit/32"
     if channel:
         # gate_up launch of the committed capture: 973.8 MB read + 10.6 MB written per 32 experts at 128 rows each
