@@ -58,7 +58,7 @@ struct Chunk {
   int32_t expert;
   int32_t row0;   // first position in sorted_ids
   int32_t rows;   // positions covered (<= 128); validity of each is the sentinel test
-  int32_t pad;
+  int32_t pad;    // 1 = the next chunk reads the same weight tiles (keep them in L2), else 0
 };
 
 // Align + (optionally) chunk table, see routing.cu.

@@ -173,6 +173,11 @@ __device__ __forceinline__ uint64_t policy_evict_first() {
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
   return p;
 }
+__device__ __forceinline__ uint64_t policy_evict_normal() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
 __device__ __forceinline__ uint64_t policy_evict_last() {
   uint64_t p;
   asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
@@ -363,7 +368,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
     if (warp == 0) {
       // ============ TMA producer: weight tiles + the chunk's token rows ============
       if (lane == 0) {
-        const uint64_t pol_w = policy_evict_first();
+        const uint64_t pol_stream = policy_evict_first();
+        const uint64_t pol_keep = policy_evict_normal();
         const uint64_t pol_a = policy_evict_last();
         uint32_t it = 0;
         bool ok = true;
@@ -377,6 +383,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           const int mi2 = T > 128 ? a_map_index(T - 128) : -1;
           const uint32_t a_bytes = (16u << mi) * TILE_K + (mi2 >= 0 ? (16u << mi2) * TILE_K : 0u);
           const int32_t row_g = (int32_t)(ch.expert * p.n_rows_per_expert + (int64_t)nt * TILE_N);
+          // weight tiles are streamed (evict-first) unless another chunk of the same expert is about to read
+          // them again: those stay in L2 under the normal policy
+          const uint64_t pol_w = ch.pad ? pol_keep : pol_stream;
           for (int kb = 0; kb < KB; ++kb, ++it) {
             const int s = it % STAGES;
             const uint32_t ph = (it / STAGES) & 1u;

@@ -259,7 +259,7 @@ __global__ void __launch_bounds__(ALIGN_WARPS * 32) align_kernel(
           ch.expert = e;
           ch.row0 = seg_off[e] + r;
           ch.rows = c - r < per ? c - r : per;
-          ch.pad = 0;
+          ch.pad = r + per < c ? 1 : 0;      // another chunk of this expert follows: its weight tiles are read again soon
           chunks[ci] = ch;
         }
       }
