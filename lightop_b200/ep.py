@@ -12,6 +12,8 @@ One process per GPU.  Rank r owns experts [r*E/R, (r+1)*E/R).  A step on every r
   5. combine all-to-all-v: bf16 rows back to their source rank, in the order they were sent;
   6. top-k sum per token in slot order with fp32 accumulation (ep_gather with unit weights), so the
      result has the same bits as the single-GPU layer.
+A step with enough tokens is cut into two micro-batches: the dispatch of one and the combine of the other
+travel over NVLink while the experts compute (asynchronous collectives on the communication stream).
 
 The reference contains only the local halves of 2 and 6 (csrc/kernels/deepgemm_moe_permute.cu;
 sequence in test/test_ep_gather_scatter_moe.py:205-296) and simulates EP on one device with an
@@ -94,8 +96,13 @@ class ExpertParallelMoE:
     def __init__(self, w1_local: torch.Tensor, w2_local: torch.Tensor, w1_scale: torch.Tensor,
                  w2_scale: torch.Tensor, num_experts_global: int, group=None,
                  quant_fn: Optional[Callable] = None, pack_fn: Optional[Callable] = None,
-                 expert_fn: Optional[Callable] = None, combine_fn: Optional[Callable] = None):
+                 expert_fn: Optional[Callable] = None, combine_fn: Optional[Callable] = None,
+                 micro_batches: int = 2, micro_batch_min_tokens: int = 512):
         self.group = group
+        # a step of at least micro_batches * micro_batch_min_tokens tokens is cut into micro-batches whose
+        # exchanges overlap the expert compute of their neighbours (see forward)
+        self.micro_batches = max(1, int(micro_batches))
+        self.micro_batch_min_tokens = int(micro_batch_min_tokens)
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.E_local = w1_local.shape[0]
@@ -116,41 +123,75 @@ class ExpertParallelMoE:
                                group=self.group)
         return recv
 
+    def _all_to_all_async(self, send: torch.Tensor, send_counts: List[int], recv_counts: List[int]):
+        recv = torch.empty((sum(recv_counts),) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
+        work = dist.all_to_all_single(recv, send, output_split_sizes=recv_counts, input_split_sizes=send_counts,
+                                      group=self.group, async_op=True)
+        return recv, work
+
     def forward(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
+        """Collective over the group.  The tokens are cut into micro-batches (when there are enough of them);
+        the dispatch of micro-batch i + 1 and the combine of micro-batch i - 1 travel while the experts work on
+        micro-batch i.  Tokens are independent of one another, so the result has the same bits either way."""
         T, k = topk_ids.shape
         dev = x.device
-        ids = topk_ids.to(torch.int64)
-        # 1. quantise once
-        xq, xs = self.quant_fn(x)
-        # 2. rows per destination rank, exchanged so that every rank knows what it receives
-        dest = self.rank_of_expert.to(torch.int64)[ids]                       # [T, k]
-        send_counts_t = torch.bincount(dest.reshape(-1), minlength=self.world)
+        nmb = self.micro_batches if T >= self.micro_batches * self.micro_batch_min_tokens else 1
+        bounds = [T * i // nmb for i in range(nmb + 1)]
+        ids_all = topk_ids.to(torch.int64)
+        # 1. rows per destination rank and micro-batch, exchanged in ONE small collective (and one host read) so
+        #    that every rank knows what it receives
+        dest_all = self.rank_of_expert.to(torch.int64)[ids_all]                          # [T, k]
+        send_counts_t = torch.stack([torch.bincount(dest_all[bounds[i]:bounds[i + 1]].reshape(-1), minlength=self.world)
+                                     for i in range(nmb)], dim=1).contiguous()             # [world, nmb]
         recv_counts_t = torch.empty_like(send_counts_t)
         dist.all_to_all_single(recv_counts_t, send_counts_t, group=self.group)
-        send_counts = [int(v) for v in send_counts_t.tolist()]
-        recv_counts = [int(v) for v in recv_counts_t.tolist()]
-        if sum(send_counts) != T * k:
-            raise RuntimeError("dispatch bookkeeping lost rows")
-        self.last_counts = (send_counts, recv_counts)
-        rows = T * k
-        pq, ps, inv = self.pack_fn(xq, xs, topk_ids, self.rank_of_expert, self.world, rows)
-        # per packed row: local expert id on the destination rank and the routed weight
-        flat_inv = inv.reshape(-1).to(torch.int64)
-        meta_e = torch.empty(rows, dtype=torch.int32, device=dev)
-        meta_w = torch.empty(rows, dtype=torch.float32, device=dev)
-        meta_e[flat_inv] = (ids % self.E_local).reshape(-1).to(torch.int32)
-        meta_w[flat_inv] = topk_weights.reshape(-1).to(torch.float32)
-        # 3. dispatch
-        rq = self._all_to_all(pq, send_counts, recv_counts)
-        rs = self._all_to_all(ps, send_counts, recv_counts)
-        re = self._all_to_all(meta_e, send_counts, recv_counts)
-        rw = self._all_to_all(meta_w, send_counts, recv_counts)
-        # 4. expert side
-        out_rows = self.expert_fn(rq, rs, re, rw)
-        # 5. combine: rows travel back in the order they came
-        back = self._all_to_all(out_rows, recv_counts, send_counts)
+        send_all = send_counts_t.tolist()
+        recv_all = recv_counts_t.tolist()
+        # 2. per micro-batch: quantise once, pack one row per routed (token, slot) by destination rank
+        mbs = []
+        for i in range(nmb):
+            lo_t, hi_t = bounds[i], bounds[i + 1]
+            ids = ids_all[lo_t:hi_t]
+            tk_ids = topk_ids[lo_t:hi_t]
+            send_counts = [int(send_all[r][i]) for r in range(self.world)]
+            recv_counts = [int(recv_all[r][i]) for r in range(self.world)]
+            rows = (hi_t - lo_t) * k
+            if sum(send_counts) != rows:
+                raise RuntimeError("dispatch bookkeeping lost rows")
+            xq, xs = self.quant_fn(x[lo_t:hi_t])
+            pq, ps, inv = self.pack_fn(xq, xs, tk_ids, self.rank_of_expert, self.world, rows)
+            # per packed row: local expert id on the destination rank and the routed weight
+            flat_inv = inv.reshape(-1).to(torch.int64)
+            meta_e = torch.empty(rows, dtype=torch.int32, device=dev)
+            meta_w = torch.empty(rows, dtype=torch.float32, device=dev)
+            meta_e[flat_inv] = (ids % self.E_local).reshape(-1).to(torch.int32)
+            meta_w[flat_inv] = topk_weights[lo_t:hi_t].reshape(-1).to(torch.float32)
+            mbs.append(dict(send=send_counts, recv=recv_counts, payload=(pq, ps, meta_e, meta_w), ids=tk_ids, inv=inv))
+        self.last_counts = ([sum(m["send"][r] for m in mbs) for r in range(self.world)],
+                            [sum(m["recv"][r] for m in mbs) for r in range(self.world)])
+
+        def dispatch(m):
+            m["in_flight"] = [self._all_to_all_async(t, m["send"], m["recv"]) for t in m["payload"]]
+
+        # 3.-5. software pipeline: dispatch(i + 1) and combine(i - 1) are in flight during expert(i)
+        dispatch(mbs[0])
+        for i, m in enumerate(mbs):
+            received = []
+            for recv, work in m["in_flight"]:
+                work.wait()
+                received.append(recv)
+            if i + 1 < nmb:
+                dispatch(mbs[i + 1])
+            out_rows = self.expert_fn(*received)
+            m["out_rows"] = out_rows                     # kept alive until the combine has completed
+            m["back"] = self._all_to_all_async(out_rows, m["recv"], m["send"])
         # 6. top-k sum in slot order
-        return self.combine_fn(back, topk_ids, inv)
+        outs = []
+        for m in mbs:
+            back, work = m["back"]
+            work.wait()
+            outs.append(self.combine_fn(back, m["ids"], m["inv"]))
+        return outs[0] if nmb == 1 else torch.cat(outs, dim=0)
 
 
 # --------------------------------------------------------------------------- benchmark leg (N > 1)

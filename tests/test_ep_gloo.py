@@ -76,10 +76,12 @@ def _worker(rank, world, port, q, mode):
             except ValueError as e:
                 q.put((rank, "ValueError"))
             return
+        # "pipelined": three micro-batches of 7..9 tokens, so the asynchronous dispatch / combine schedule runs
+        mb_kw = dict(micro_batches=3, micro_batch_min_tokens=7) if mode == "pipelined" else {}
         layer = ExpertParallelMoE(w1[sl], w2[sl], w1_s[sl], w2_s[sl], E,
-                                  quant_fn=lambda t: O.group_quant_int8(t, 128), pack_fn=_pack_torch,
+                                  quant_fn=lambda t: O.group_quant_int8(t.contiguous(), 128), pack_fn=_pack_torch,
                                   expert_fn=_make_expert_fn(w1[sl], w2[sl], w1_s[sl], w2_s[sl]),
-                                  combine_fn=_combine_torch)
+                                  combine_fn=_combine_torch, **mb_kw)
         y = layer.forward(x, w, ids)
         y_ref = O.fused_moe_block_int8(x, w1, w2, w1_s, w2_s, w, ids)
         send, recv = layer.last_counts
@@ -107,6 +109,13 @@ def test_ep_two_ranks_match_single_process_oracle():
     assert [r[1] for r in res] == [True, True], res
     assert all(r[2] for r in res)
     # what rank 0 sends to rank 1 is what rank 1 receives from rank 0
+    assert res[0][3][1] == res[1][4][0] and res[1][3][0] == res[0][4][1]
+
+
+def test_ep_micro_batched_schedule_gives_the_same_bits():
+    res = _run("pipelined")
+    assert [r[1] for r in res] == [True, True], res
+    assert all(r[2] for r in res)
     assert res[0][3][1] == res[1][4][0] and res[1][3][0] == res[0][4][1]
 
 
