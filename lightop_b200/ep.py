@@ -271,6 +271,7 @@ def bench_step_setup(args, rank: int, world: int, dev: torch.device):
         "dtype": "int8 x int8 -> int32, fp32 block scaling, bf16 in/out", "data": "synthetic",
         "config": {"workload": name, "E": E, "top_k": k, "M_per_rank": M, "hidden": H, "intermediate": I,
                    "parallelism": f"ep{world}", "experts_per_rank": E_local,
+                   "micro_batches": layer.micro_batches if M >= layer.micro_batches * layer.micro_batch_min_tokens else 1,
                    "rows_received_rank0": rows_recv, "rows_sent_to_peers_rank0": remote_rows,
                    "dispatch_bytes_per_row": H + 4 * (H // 128) + 8, "combine_bytes_per_row": 2 * H,
                    "l2": "per-rank weights (>=1.4 GB) exceed L2; no flush needed"},
@@ -278,7 +279,9 @@ def bench_step_setup(args, rank: int, world: int, dev: torch.device):
         "e2e": {"value": total_tokens / (e2e_ms * 1e-3), "unit": B.UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": (x_h.numel() * 2 + l_h.numel() * 4) * world,
                 "d2h_bytes_per_step": y_h.numel() * 2 * world},
-        "gpu_launches": 11 * args.steps,
+        # own kernels per step: the router, then per micro-batch quantise, pack (2), align, permute, two GEMMs, gather ...
+        "gpu_launches": (1 + 10 * (layer.micro_batches if M >= layer.micro_batches * layer.micro_batch_min_tokens else 1))
+        * args.steps,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "grouped_gemm_kernel<gate_up>", "achieved": None, "peak": hbm_peak,
                      "peak_kind": peak_kind, "unit": "GB/s", "frac": None, "traffic": None,
