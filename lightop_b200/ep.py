@@ -12,8 +12,8 @@ One process per GPU.  Rank r owns experts [r*E/R, (r+1)*E/R).  A step on every r
   5. combine all-to-all-v: bf16 rows back to their source rank, in the order they were sent;
   6. top-k sum per token in slot order with fp32 accumulation (ep_gather with unit weights), so the
      result has the same bits as the single-GPU layer.
-A step with enough tokens is cut into two micro-batches: the dispatch of one and the combine of the other
-travel over NVLink while the experts compute (asynchronous collectives on the communication stream).
+Optionally (micro_batches > 1) a step is cut into micro-batches: the dispatch of one and the combine of
+another travel over NVLink while the experts compute (asynchronous collectives on the communication stream).
 
 The reference contains only the local halves of 2 and 6 (csrc/kernels/deepgemm_moe_permute.cu;
 sequence in test/test_ep_gather_scatter_moe.py:205-296) and simulates EP on one device with an
@@ -97,10 +97,13 @@ class ExpertParallelMoE:
                  w2_scale: torch.Tensor, num_experts_global: int, group=None,
                  quant_fn: Optional[Callable] = None, pack_fn: Optional[Callable] = None,
                  expert_fn: Optional[Callable] = None, combine_fn: Optional[Callable] = None,
-                 micro_batches: int = 2, micro_batch_min_tokens: int = 512):
+                 micro_batches: int = 1, micro_batch_min_tokens: int = 512):
         self.group = group
-        # a step of at least micro_batches * micro_batch_min_tokens tokens is cut into micro-batches whose
-        # exchanges overlap the expert compute of their neighbours (see forward)
+        # With micro_batches > 1 a step of at least micro_batches * micro_batch_min_tokens tokens is cut into
+        # micro-batches whose exchanges overlap the expert compute of their neighbours (see forward).  Off by
+        # default: on 2 and on 8 B200s the pipelined step measured 2-8 % slower than the plain one -- the
+        # exchange is a small part of the step, every micro-batch streams the rank's expert weights again,
+        # and the collectives' kernels compete for SMs with the persistent GEMM.
         self.micro_batches = max(1, int(micro_batches))
         self.micro_batch_min_tokens = int(micro_batch_min_tokens)
         self.world = dist.get_world_size(group)
@@ -130,9 +133,10 @@ class ExpertParallelMoE:
         return recv, work
 
     def forward(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
-        """Collective over the group.  The tokens are cut into micro-batches (when there are enough of them);
-        the dispatch of micro-batch i + 1 and the combine of micro-batch i - 1 travel while the experts work on
-        micro-batch i.  Tokens are independent of one another, so the result has the same bits either way."""
+        """Collective over the group.  With micro_batches > 1 (and enough tokens) the tokens are cut into
+        micro-batches; the dispatch of micro-batch i + 1 and the combine of micro-batch i - 1 travel while the
+        experts work on micro-batch i.  Tokens are independent of one another, so the result has the same bits
+        either way."""
         T, k = topk_ids.shape
         dev = x.device
         nmb = self.micro_batches if T >= self.micro_batches * self.micro_batch_min_tokens else 1
@@ -217,7 +221,9 @@ def bench_step_setup(args, rank: int, world: int, dev: torch.device):
     E_local = E // world
     w1, w2, w1_s, w2_s = synthetic.make_weights(E_local, H, I, seed=100 + rank, device=dev)
     x, logits = synthetic.make_activations(M, H, E, seed=1 + rank, device=dev, zipf=cfg.get("zipf"))
-    layer = ExpertParallelMoE(w1, w2, w1_s, w2_s, E)
+    import os
+    nmb_env = os.environ.get("LIGHTOP_EP_MICRO_BATCHES")
+    layer = ExpertParallelMoE(w1, w2, w1_s, w2_s, E, **({"micro_batches": int(nmb_env)} if nmb_env else {}))
     tw = torch.empty(M, k, dtype=torch.float32, device=dev)
     ti = torch.empty(M, k, dtype=torch.int32, device=dev)
     stream = torch.cuda.current_stream(dev)
