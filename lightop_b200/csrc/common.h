@@ -130,6 +130,24 @@ struct GemmArgs {
 
 int launch_grouped_gemm(GemmMode mode, const GemmArgs &args, cudaStream_t stream);
 
+#ifdef __CUDACC__
+// Lanes of the warp that hold the same expert as this lane (lanes without an expert match one another).
+// With many steps per warp the mask is built from one ballot per bit of the expert id: the match
+// instruction proper has a throughput of the order of one warp per ~64 cycles and SM here, which made it the
+// bottleneck at prefill sizes; with a few steps per warp (decode sizes) its single round trip is faster
+// than the chain of ballots (nbits <= 0 selects it).
+__device__ __forceinline__ unsigned peers_of(int e, int nbits) {
+  if (nbits <= 0) return __match_any_sync(0xffffffffu, e);
+  const unsigned has = __ballot_sync(0xffffffffu, e >= 0);
+  unsigned peers = e >= 0 ? has : ~has;
+  for (int b = 0; b < nbits; ++b) {
+    const unsigned set = __ballot_sync(0xffffffffu, (e >> b) & 1);
+    peers &= ((e >> b) & 1) ? set : ~set;
+  }
+  return peers;
+}
+#endif
+
 int launch_moe_sum_masked(const __nv_bfloat16 *in, __nv_bfloat16 *out, const __nv_bfloat16 *bias,
                           int64_t M, int topk, int64_t H, float factor, const void *topk_ids,
                           int ids_dtype, const int32_t *expert_map, cudaStream_t stream);

@@ -231,13 +231,15 @@ extern "C" size_t lo_grouped_gemm_workspace_bytes(int64_t sorted_capacity, int b
   return lo::carve_gemm(nullptr, sorted_capacity, block_size, K).bytes;
 }
 
-extern "C" int lo_moe_grouped_gemm_i8_block(const int8_t *A, const float *a_scale, int64_t rows_a, const int8_t *B,
-                                            const float *b_scale, int E, int64_t N, int64_t K, void *C,
-                                            const float *topk_weights, int weight_mode, const int32_t *sorted_ids,
-                                            int64_t sorted_capacity, const int32_t *expert_ids,
-                                            const int32_t *num_tokens_post_pad, int64_t numel_valid, int top_k,
-                                            int block_size, void *workspace, size_t workspace_bytes, void *stream) {
-  using namespace lo;
+namespace lo {
+namespace {
+// Both scale formats of the stand-alone grouped GEMM: chunk table from the caller's block table, rows and
+// scales permuted into sorted order, then the kernel of the format.
+int grouped_gemm_on_blocks(GemmMode mode, const int8_t *A, const float *a_scale, int64_t rows_a, const int8_t *B,
+                           const float *b_scale, int E, int64_t N, int64_t K, void *C, const float *topk_weights,
+                           int weight_mode, const int32_t *sorted_ids, int64_t sorted_capacity,
+                           const int32_t *expert_ids, const int32_t *num_tokens_post_pad, int64_t numel_valid,
+                           int top_k, int block_size, void *workspace, size_t workspace_bytes, void *stream) {
   LO_REQUIRE(A && a_scale && B && b_scale && C && sorted_ids && expert_ids && num_tokens_post_pad && workspace,
              "grouped gemm: null pointer");
   LO_REQUIRE(block_size >= 1 && (block_size <= 128 || block_size % 128 == 0),
@@ -245,14 +247,14 @@ extern "C" int lo_moe_grouped_gemm_i8_block(const int8_t *A, const float *a_scal
   LO_REQUIRE(top_k >= 1 && E >= 1 && rows_a >= 0 && sorted_capacity >= 1, "grouped gemm: bad shape");
   LO_REQUIRE(K % 128 == 0 && N % 128 == 0, "grouped gemm: N and K must be multiples of 128");
   LO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & (ALIGN_BYTES - 1)) == 0, "grouped gemm: workspace must be 256-byte aligned");
-  GemmWs W = carve_gemm(workspace, sorted_capacity, block_size, K);
+  GemmWs W = carve_gemm(workspace, sorted_capacity, block_size, K);   // sized for block scales; per-token scales need less
   LO_REQUIRE(workspace_bytes >= W.bytes, "grouped gemm: workspace of %zu bytes, %zu needed", workspace_bytes, W.bytes);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t max_blocks = ceil_div(sorted_capacity, block_size);
   int rc = launch_chunks_from_blocks(expert_ids, num_tokens_post_pad, block_size, max_blocks, W.chunks, W.num_chunks, st);
   if (rc != LO_OK) return rc;
   rc = launch_permute_rows(A, a_scale, rows_a, K, sorted_ids, sorted_capacity, num_tokens_post_pad, numel_valid, top_k,
-                           W.a_sorted, W.as_sorted, st);
+                           W.a_sorted, W.as_sorted, st, mode == GEMM_CHANNEL ? 1 : 0);
   if (rc != LO_OK) return rc;
   GemmArgs g{};
   g.A = W.a_sorted; g.a_scale = W.as_sorted; g.rows_a = sorted_capacity;
@@ -262,7 +264,20 @@ extern "C" int lo_moe_grouped_gemm_i8_block(const int8_t *A, const float *a_scal
   g.chunks = W.chunks; g.num_chunks = W.num_chunks;
   g.C = static_cast<__nv_bfloat16 *>(C);
   g.topk_weights = topk_weights; g.weight_mode = weight_mode; g.act_eps = 0.f; g.status = nullptr;
-  return launch_grouped_gemm(GEMM_SINGLE, g, st);
+  return launch_grouped_gemm(mode, g, st);
+}
+}  // namespace
+}  // namespace lo
+
+extern "C" int lo_moe_grouped_gemm_i8_block(const int8_t *A, const float *a_scale, int64_t rows_a, const int8_t *B,
+                                            const float *b_scale, int E, int64_t N, int64_t K, void *C,
+                                            const float *topk_weights, int weight_mode, const int32_t *sorted_ids,
+                                            int64_t sorted_capacity, const int32_t *expert_ids,
+                                            const int32_t *num_tokens_post_pad, int64_t numel_valid, int top_k,
+                                            int block_size, void *workspace, size_t workspace_bytes, void *stream) {
+  return lo::grouped_gemm_on_blocks(lo::GEMM_SINGLE, A, a_scale, rows_a, B, b_scale, E, N, K, C, topk_weights, weight_mode,
+                                    sorted_ids, sorted_capacity, expert_ids, num_tokens_post_pad, numel_valid, top_k,
+                                    block_size, workspace, workspace_bytes, stream);
 }
 
 // Per-channel form of the grouped GEMM: a_scale [rows_a] (one per token), b_scale [E, N].
@@ -272,32 +287,9 @@ extern "C" int lo_moe_grouped_gemm_i8_channel(const int8_t *A, const float *a_sc
                                               int64_t sorted_capacity, const int32_t *expert_ids,
                                               const int32_t *num_tokens_post_pad, int64_t numel_valid, int top_k,
                                               int block_size, void *workspace, size_t workspace_bytes, void *stream) {
-  using namespace lo;
-  LO_REQUIRE(A && a_scale && B && b_scale && C && sorted_ids && expert_ids && num_tokens_post_pad && workspace,
-             "grouped gemm: null pointer");
-  LO_REQUIRE(block_size >= 1 && (block_size <= 128 || block_size % 128 == 0),
-             "grouped gemm: block_size %d must be <= 128 or a multiple of 128", block_size);
-  LO_REQUIRE(top_k >= 1 && E >= 1 && rows_a >= 0 && sorted_capacity >= 1, "grouped gemm: bad shape");
-  LO_REQUIRE(K % 128 == 0 && N % 128 == 0, "grouped gemm: N and K must be multiples of 128");
-  LO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & (ALIGN_BYTES - 1)) == 0, "grouped gemm: workspace must be 256-byte aligned");
-  GemmWs W = carve_gemm(workspace, sorted_capacity, block_size, K);   // as_sorted is larger than needed here
-  LO_REQUIRE(workspace_bytes >= W.bytes, "grouped gemm: workspace of %zu bytes, %zu needed", workspace_bytes, W.bytes);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int64_t max_blocks = ceil_div(sorted_capacity, block_size);
-  int rc = launch_chunks_from_blocks(expert_ids, num_tokens_post_pad, block_size, max_blocks, W.chunks, W.num_chunks, st);
-  if (rc != LO_OK) return rc;
-  rc = launch_permute_rows(A, a_scale, rows_a, K, sorted_ids, sorted_capacity, num_tokens_post_pad, numel_valid, top_k,
-                           W.a_sorted, W.as_sorted, st, 1);
-  if (rc != LO_OK) return rc;
-  GemmArgs g{};
-  g.A = W.a_sorted; g.a_scale = W.as_sorted; g.rows_a = sorted_capacity;
-  g.max_chunk_rows = block_size < 128 ? block_size : 128; g.B = B; g.b_scale = b_scale; g.E = E;
-  g.n_rows_per_expert = N; g.K = K; g.n_tiles = (int)(N / 128);
-  g.sorted_ids = sorted_ids; g.numel_valid = numel_valid;
-  g.chunks = W.chunks; g.num_chunks = W.num_chunks;
-  g.C = static_cast<__nv_bfloat16 *>(C);
-  g.topk_weights = topk_weights; g.weight_mode = weight_mode; g.status = nullptr;
-  return launch_grouped_gemm(GEMM_CHANNEL, g, st);
+  return lo::grouped_gemm_on_blocks(lo::GEMM_CHANNEL, A, a_scale, rows_a, B, b_scale, E, N, K, C, topk_weights, weight_mode,
+                                    sorted_ids, sorted_capacity, expert_ids, num_tokens_post_pad, numel_valid, top_k,
+                                    block_size, workspace, workspace_bytes, stream);
 }
 
 // ---------------------------------------------------------------------------

@@ -124,7 +124,7 @@ __device__ __forceinline__ int local_expert(const IdT *ids, int64_t i, const int
 
 // One CTA: aligned exclusive offsets from the per-expert counts, m_indices fill,
 // and the stable destination row of every (token, slot) -> inv_perm.
-// Same warp-histogram scheme as the alignment kernel (32 warps, match_any).
+// Same warp-histogram scheme as the alignment kernel (32 warps, peers_of).
 template <typename IdT>
 __global__ void __launch_bounds__(1024) ep_plan_kernel(const IdT *__restrict__ ids, int64_t numel,
                                                        const int32_t *__restrict__ expert_map,
@@ -144,12 +144,12 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(const IdT *__restrict__ i
   const int64_t seg_begin = (int64_t)warp * seg_len;
   const int64_t seg_end = seg_begin + seg_len < numel ? seg_begin + seg_len : numel;
   int32_t *my_hist = hist + warp * local_E;
+  // bits that distinguish the local expert ids, or 0 = use the match instruction (few steps per warp)
+  const int id_bits = seg_len >= 256 ? 32 - __clz(local_E > 1 ? local_E - 1 : 1) : 0;
   for (int64_t base = seg_begin; base < seg_end; base += 32) {
     const int64_t i = base + lane;
     const int e = i < seg_end ? local_expert<IdT>(ids, i, expert_map, local_E) : -1;
-    const unsigned peers = __match_any_sync(0xffffffffu, e);
-    if (e >= 0 && lane == (__ffs(peers) - 1)) my_hist[e] += __popc(peers);
-    __syncwarp();
+    if (e >= 0) atomicAdd(&my_hist[e], 1);      // counting pass: order does not matter
   }
   __syncthreads();
   for (int e = tid; e < local_E; e += blockDim.x) {
@@ -178,7 +178,7 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(const IdT *__restrict__ i
   for (int64_t base = seg_begin; base < seg_end; base += 32) {
     const int64_t i = base + lane;
     const int e = i < seg_end ? local_expert<IdT>(ids, i, expert_map, local_E) : -1;
-    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const unsigned peers = peers_of(e, id_bits);
     const int rank = __popc(peers & ((1u << lane) - 1u));
     int before = 0;
     if (e >= 0) before = my_hist[e];

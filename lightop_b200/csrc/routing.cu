@@ -115,9 +115,8 @@ int launch_topk_ids(const void *gating, int64_t M, int E, int k, int renorm, flo
 // moe_align_block_size.
 //
 // One CTA of 32 warps.  The flat id list is cut into 32 contiguous segments,
-// one per warp, which the warp walks 32 ids at a time.  A step groups equal
-// experts with __match_any_sync; the group's leader adds the group size to the
-// warp's private histogram row in shared memory (no atomics).  After an
+// one per warp, which the warp walks 32 ids at a time, counting into the
+// warp's private histogram row in shared memory.  After an
 // exclusive prefix over the warps (per expert) and a block-wide exclusive scan
 // of the padded counts (over experts) the warps walk their segments again and
 // scatter: position = segment offset of the expert + ids of the same expert in
@@ -166,15 +165,16 @@ __global__ void __launch_bounds__(ALIGN_WARPS * 32) align_kernel(
   // segment of this warp, a multiple of 32 ids long
   int64_t seg_len = (numel + nw - 1) / nw;
   seg_len = (seg_len + 31) / 32 * 32;
+  // bits that distinguish expert ids 0..E-1, or 0 = use the match instruction (see peers_of)
+  const int id_bits = seg_len >= 256 ? 32 - __clz(E > 1 ? E - 1 : 1) : 0;
   const int64_t seg_begin = (int64_t)warp * seg_len;
   const int64_t seg_end = seg_begin + seg_len < numel ? seg_begin + seg_len : numel;
   int32_t *my_hist = hist + warp * E;
 
+  // counting pass: order does not matter here, a shared-memory atomic per id is the cheapest way
   for (int64_t base = seg_begin; base < seg_end; base += 32) {
     const int e = load_expert<IdT>(ids, base + lane, seg_end, E, expert_map, map_mode);
-    const unsigned peers = __match_any_sync(0xffffffffu, e);
-    if (e >= 0 && lane == (__ffs(peers) - 1)) my_hist[e] += __popc(peers);
-    __syncwarp();
+    if (e >= 0) atomicAdd(&my_hist[e], 1);
   }
   __syncthreads();
 
@@ -269,7 +269,7 @@ __global__ void __launch_bounds__(ALIGN_WARPS * 32) align_kernel(
   // stable scatter
   for (int64_t base = seg_begin; base < seg_end; base += 32) {
     const int e = load_expert<IdT>(ids, base + lane, seg_end, E, expert_map, map_mode);
-    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const unsigned peers = peers_of(e, id_bits);
     const int rank = __popc(peers & ((1u << lane) - 1u));
     int before = 0;
     if (e >= 0) before = my_hist[e];

@@ -1,6 +1,6 @@
 """Generate the golden fixtures of tests/golden/ from the reference's own torch functions.
 
-Run where a reference checkout is available (``$LIGHTOP_REF`` or ``/root/reference``):
+Run where a reference checkout is available (``$LIGHTOP_REF``, see oracle/ref_extract.py):
     python tests/golden/make_golden.py            (all fixtures)
     python tests/golden/make_golden.py channel    (only channel_cases.pt)
     python tests/golden/make_golden.py gate       (only gate_cases.pt)
