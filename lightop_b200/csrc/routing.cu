@@ -1,6 +1,7 @@
 // Routing kernels: softmax + top-k selection, and expert alignment
 // (histogram + prefix scan + stable scatter) with the grouped-GEMM chunk table.
 #include "common.h"
+#include <cooperative_groups.h>
 
 namespace lo {
 namespace {
@@ -286,6 +287,175 @@ __global__ void __launch_bounds__(ALIGN_WARPS * 32) align_kernel(
   }
 }
 
+// ---------------------------------------------------------------------------
+// The same alignment for many ids, as a thread-block CLUSTER of ALIGN_CLUSTER CTAs (one launch).
+// The single-CTA kernel above is bound by the instruction issue rate of its one SM (about 140
+// instructions per warp step over 32 k ids at the prefill size).  Here CTA r of the cluster takes the r-th
+// contiguous slice of the ids; the CTAs exchange their per-expert counts through distributed shared
+// memory, every CTA repeats the (cheap) scans over experts, and the position of an id is
+//   segment offset of its expert + ids of that expert in lower-ranked CTAs + in earlier warps of this
+//   CTA + seen so far by this warp + rank inside the warp step,
+// i.e. still ascending flat index inside an expert: bit-identical to the single-CTA kernel.
+// ---------------------------------------------------------------------------
+constexpr int ALIGN_CLUSTER = 8;
+constexpr int64_t ALIGN_CLUSTER_MIN_IDS = 8192;   // below this the single CTA is as fast and costs one SM
+
+template <typename IdT>
+__global__ void __launch_bounds__(ALIGN_WARPS * 32) align_cluster_kernel(
+    const IdT *__restrict__ ids, int64_t numel, int E, int block_size, const int32_t *__restrict__ expert_map,
+    int map_mode, int32_t *__restrict__ sorted_ids, int64_t sorted_capacity, int32_t *__restrict__ expert_ids,
+    int64_t expert_ids_capacity, int32_t *__restrict__ num_tokens_post_pad, Chunk *__restrict__ chunks,
+    int32_t *__restrict__ num_chunks, int64_t chunk_capacity, int32_t *__restrict__ inv_pos, int chunk_max) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int C = (int)cluster.num_blocks();
+  const int r = (int)cluster.block_rank();
+  extern __shared__ int32_t smem[];
+  int32_t *hist = smem;                       // [ALIGN_WARPS][E] per-warp counts, then exclusive prefixes inside this CTA
+  int32_t *seg_off = smem + ALIGN_WARPS * E;  // [E + 1] padded exclusive offsets
+  int32_t *count = seg_off + (E + 1);         // [E] ids per expert, whole input
+  int32_t *chunk_off = count + E;             // [E + 1]
+  int32_t *warp_tot = chunk_off + (E + 1);    // [2][32]
+  int32_t *cta_cnt = warp_tot + 64;           // [E] ids per expert in this CTA's slice (read by the other CTAs)
+  int32_t *before = cta_cnt + E;              // [E] ids per expert in lower-ranked CTAs
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // sentinel fill: every CTA fills its share
+  for (int64_t i = (int64_t)r * blockDim.x + tid; i < sorted_capacity; i += (int64_t)C * blockDim.x) sorted_ids[i] = (int32_t)numel;
+  for (int i = tid; i < ALIGN_WARPS * E; i += blockDim.x) hist[i] = 0;
+  __syncthreads();
+
+  // slice of this CTA and segment of this warp, both multiples of 32 ids long
+  int64_t cta_len = (numel + C - 1) / C;
+  cta_len = (cta_len + 31) / 32 * 32;
+  const int64_t cta_begin = (int64_t)r * cta_len;
+  const int64_t cta_end = cta_begin + cta_len < numel ? cta_begin + cta_len : numel;
+  int64_t seg_len = (cta_len + ALIGN_WARPS - 1) / ALIGN_WARPS;
+  seg_len = (seg_len + 31) / 32 * 32;
+  const int64_t seg_begin = cta_begin + (int64_t)warp * seg_len;
+  const int64_t seg_end = seg_begin + seg_len < cta_end ? seg_begin + seg_len : cta_end;
+  const int id_bits = seg_len >= 256 ? 32 - __clz(E > 1 ? E - 1 : 1) : 0;
+  int32_t *my_hist = hist + warp * E;
+
+  for (int64_t base = seg_begin; base < seg_end; base += 32) {
+    const int e = load_expert<IdT>(ids, base + lane, seg_end, E, expert_map, map_mode);
+    if (e >= 0) atomicAdd(&my_hist[e], 1);
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += blockDim.x) {
+    int run = 0;
+    for (int w = 0; w < ALIGN_WARPS; ++w) {
+      const int c = hist[w * E + e];
+      hist[w * E + e] = run;
+      run += c;
+    }
+    cta_cnt[e] = run;
+  }
+  cluster.sync();      // every CTA's counts are published (and the sentinel fill is complete everywhere)
+  for (int e = tid; e < E; e += blockDim.x) {
+    int total = 0, lower = 0;
+    for (int rr = 0; rr < C; ++rr) {
+      const int v = cluster.map_shared_rank(cta_cnt, rr)[e];
+      total += v;
+      if (rr < r) lower += v;
+    }
+    count[e] = total;
+    before[e] = lower;
+  }
+  __syncthreads();
+
+  // block-wide exclusive scans over experts (one expert per thread), the same in every CTA
+  {
+    const int c = tid < E ? count[tid] : 0;
+    const int padded = (c + block_size - 1) / block_size * block_size;
+    const int nch = (c + chunk_max - 1) / chunk_max;
+    int a = padded, b = nch;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int ta = __shfl_up_sync(0xffffffffu, a, off);
+      const int tb = __shfl_up_sync(0xffffffffu, b, off);
+      if (lane >= off) { a += ta; b += tb; }
+    }
+    if (lane == 31) { warp_tot[warp] = a; warp_tot[32 + warp] = b; }
+    __syncthreads();
+    if (warp == 0) {
+      int ta = warp_tot[lane], tb = warp_tot[32 + lane];
+      const int ia = ta, ib = tb;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int ua = __shfl_up_sync(0xffffffffu, ta, off);
+        const int ub = __shfl_up_sync(0xffffffffu, tb, off);
+        if (lane >= off) { ta += ua; tb += ub; }
+      }
+      warp_tot[lane] = ta - ia;
+      warp_tot[32 + lane] = tb - ib;
+    }
+    __syncthreads();
+    if (tid < E) {
+      seg_off[tid] = warp_tot[warp] + a - padded;
+      chunk_off[tid] = warp_tot[32 + warp] + b - nch;
+      if (tid == E - 1) {
+        seg_off[E] = warp_tot[warp] + a;
+        chunk_off[E] = warp_tot[32 + warp] + b;
+      }
+    }
+    __syncthreads();
+  }
+  const int total_padded = seg_off[E];
+  if (r == 0 && tid == 0) {
+    *num_tokens_post_pad = total_padded;
+    if (num_chunks) *num_chunks = chunk_off[E] < chunk_capacity ? chunk_off[E] : (int32_t)chunk_capacity;
+  }
+  // block -> expert table and chunk table: CTA r takes the experts e = r, r + C, ...
+  if (expert_ids) {
+    const int64_t total_blocks = total_padded / block_size;
+    for (int64_t b = total_blocks + (int64_t)r * blockDim.x + tid; b < expert_ids_capacity; b += (int64_t)C * blockDim.x) expert_ids[b] = -1;
+    for (int e = r + C * tid; e < E; e += C * blockDim.x) {
+      const int out_e = map_mode == 2 ? expert_map[e] : e;
+      for (int b = seg_off[e] / block_size; b < seg_off[e + 1] / block_size; ++b)
+        if (b < expert_ids_capacity) expert_ids[b] = out_e;
+    }
+  }
+  if (chunks) {
+    for (int e = r + C * tid; e < E; e += C * blockDim.x) {
+      const int c = count[e];
+      const int nch = (c + chunk_max - 1) / chunk_max;
+      const int per = nch > 0 ? (((c + nch - 1) / nch) + 15) / 16 * 16 : 0;
+      int ci = chunk_off[e];
+      for (int rr = 0; rr < c; rr += per, ++ci) {
+        if (ci < chunk_capacity) {
+          Chunk ch;
+          ch.expert = e;
+          ch.row0 = seg_off[e] + rr;
+          ch.rows = c - rr < per ? c - rr : per;
+          ch.pad = rr + per < c ? 1 : 0;
+          chunks[ci] = ch;
+        }
+      }
+    }
+  }
+
+  // stable scatter of this CTA's slice
+  for (int64_t base = seg_begin; base < seg_end; base += 32) {
+    const int e = load_expert<IdT>(ids, base + lane, seg_end, E, expert_map, map_mode);
+    const unsigned peers = peers_of(e, id_bits);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    int prior = 0;
+    if (e >= 0) prior = my_hist[e];
+    __syncwarp();
+    if (e >= 0) {
+      const int64_t pos = (int64_t)seg_off[e] + before[e] + prior + rank;
+      if (pos < sorted_capacity) sorted_ids[pos] = (int32_t)(base + lane);
+      if (inv_pos) inv_pos[base + lane] = (int32_t)pos;
+      if (lane == (__ffs(peers) - 1)) my_hist[e] = prior + __popc(peers);
+    } else if (inv_pos && base + lane < seg_end) {
+      inv_pos[base + lane] = -1;
+    }
+    __syncwarp();
+  }
+  cluster.sync();      // no CTA leaves while another may still read its counts
+}
+
 __global__ void chunks_from_blocks_kernel(const int32_t *__restrict__ expert_ids,
                                           const int32_t *__restrict__ num_tokens_post_pad, int block_size,
                                           int64_t max_blocks, Chunk *__restrict__ chunks,
@@ -321,6 +491,38 @@ int launch_align(const void *topk_ids, int ids_dtype, int64_t numel, int num_exp
   LO_REQUIRE(sorted_ids && num_tokens_post_pad, "moe_align: null output");
   const size_t smem = sizeof(int32_t) * ((size_t)ALIGN_WARPS * num_experts + 3 * (size_t)num_experts + 2 + 64);
   cudaError_t e;
+  if (numel >= ALIGN_CLUSTER_MIN_IDS && (ids_dtype == LO_I32 || ids_dtype == LO_I64)) {
+    // many ids: one cluster of ALIGN_CLUSTER CTAs
+    const size_t csmem = smem + sizeof(int32_t) * 2 * (size_t)num_experts;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(ALIGN_CLUSTER, 1, 1);
+    cfg.blockDim = dim3(ALIGN_WARPS * 32, 1, 1);
+    cfg.dynamicSmemBytes = csmem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = ALIGN_CLUSTER;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (ids_dtype == LO_I32) {
+      if (csmem > 48 * 1024)
+        LO_CUDA_OK(cudaFuncSetAttribute(align_cluster_kernel<int32_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csmem));
+      LO_CUDA_OK(cudaLaunchKernelEx(&cfg, align_cluster_kernel<int32_t>, static_cast<const int32_t *>(topk_ids), numel,
+                                    num_experts, block_size, expert_map, map_mode, sorted_ids, sorted_capacity, expert_ids,
+                                    expert_ids_capacity, num_tokens_post_pad, chunks, num_chunks, chunk_capacity, inv_pos,
+                                    chunk_max));
+    } else {
+      if (csmem > 48 * 1024)
+        LO_CUDA_OK(cudaFuncSetAttribute(align_cluster_kernel<int64_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csmem));
+      LO_CUDA_OK(cudaLaunchKernelEx(&cfg, align_cluster_kernel<int64_t>, static_cast<const int64_t *>(topk_ids), numel,
+                                    num_experts, block_size, expert_map, map_mode, sorted_ids, sorted_capacity, expert_ids,
+                                    expert_ids_capacity, num_tokens_post_pad, chunks, num_chunks, chunk_capacity, inv_pos,
+                                    chunk_max));
+    }
+    return LO_OK;
+  }
   if (ids_dtype == LO_I32) {
     static thread_local size_t set32 = 0;
     if (smem > 48 * 1024 && smem > set32) {

@@ -160,6 +160,21 @@ def test_align_expert_map(lo):
     _check_align(lo, ids, E, 16, expert_map=emap, ignore=False)
 
 
+@pytest.mark.parametrize("M,E,k,bs,dtype", [(8193, 8, 1, 16, torch.int32), (3000, 1024, 4, 8, torch.int64),
+                                            (9001, 160, 6, 64, torch.int32), (65536, 32, 1, 16, torch.int32)])
+def test_align_many_ids(lo, M, E, k, bs, dtype):
+    # at and beyond 8192 ids the alignment runs as a cluster of CTAs: same stable order, ragged slices,
+    # empty experts, many experts, and both expert-map modes
+    g = torch.Generator().manual_seed(M + E)
+    ids = torch.randint(0, E, (M, k), generator=g).to(dtype)
+    ids[ids == 1] = 0          # an empty expert
+    _check_align(lo, ids, E, bs)
+    emap = torch.full((E,), -1, dtype=torch.int32)
+    emap[E // 2:] = torch.arange(E - E // 2, dtype=torch.int32)
+    _check_align(lo, ids, E, bs, expert_map=emap, ignore=True)
+    _check_align(lo, ids, E, bs, expert_map=emap, ignore=False)
+
+
 def test_align_is_deterministic(lo):
     g = torch.Generator().manual_seed(5)
     ids = torch.randint(0, 256, (8192, 8), generator=g, dtype=torch.int32).to(DEV)
