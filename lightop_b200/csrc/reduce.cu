@@ -2,6 +2,7 @@
 // (ep_scatter / ep_build_m_indices / ep_gather).  All are streaming,
 // HBM-bound kernels: 16-byte vector accesses, fp32 accumulation.
 #include "common.h"
+#include <cooperative_groups.h>
 
 namespace lo {
 namespace {
@@ -122,27 +123,41 @@ __device__ __forceinline__ int local_expert(const IdT *ids, int64_t i, const int
   return (int)e;
 }
 
-// One CTA: aligned exclusive offsets from the per-expert counts, m_indices fill,
-// and the stable destination row of every (token, slot) -> inv_perm.
-// Same warp-histogram scheme as the alignment kernel (32 warps, peers_of).
+// Aligned exclusive offsets from the per-expert counts, m_indices fill, and the stable destination row of
+// every (token, slot) -> inv_perm.  Same scheme as the alignment kernels: per-warp histograms, stable rank
+// from peer masks.  Runs as one CTA or, for many ids, as a cluster of EP_PLAN_CLUSTER CTAs that take
+// consecutive slices of the ids and exchange their per-expert counts through distributed shared memory.
+constexpr int EP_PLAN_CLUSTER = 8;
+constexpr int64_t EP_PLAN_CLUSTER_MIN_IDS = 8192;
+
 template <typename IdT>
 __global__ void __launch_bounds__(1024) ep_plan_kernel(const IdT *__restrict__ ids, int64_t numel,
                                                        const int32_t *__restrict__ expert_map,
                                                        const int32_t *__restrict__ counts_in, int local_E,
                                                        int alignment, int32_t *__restrict__ m_indices, int64_t rows,
                                                        int32_t *__restrict__ inv_perm) {
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  const int C = (int)cluster.num_blocks();      // 1 for a plain launch
+  const int r = (int)cluster.block_rank();
   extern __shared__ int32_t smem[];
   int32_t *hist = smem;                 // [32][local_E]
   int32_t *off = smem + 32 * local_E;   // [local_E + 1]
-  int32_t *cnt = off + local_E + 1;     // [local_E]
+  int32_t *cnt = off + local_E + 1;     // [local_E] ids per expert, whole input (or the caller's counts)
+  int32_t *cta_cnt = cnt + local_E;     // [local_E] ids per expert in this CTA's slice
+  int32_t *before = cta_cnt + local_E;  // [local_E] ids per expert in lower-ranked CTAs
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   for (int i = tid; i < 32 * local_E; i += blockDim.x) hist[i] = 0;
-  for (int64_t i = tid; i < rows; i += blockDim.x) m_indices[i] = -1;
+  for (int64_t i = (int64_t)r * blockDim.x + tid; i < rows; i += (int64_t)C * blockDim.x) m_indices[i] = -1;
   __syncthreads();
-  int64_t seg_len = (numel + 31) / 32;
+  int64_t cta_len = (numel + C - 1) / C;
+  cta_len = (cta_len + 31) / 32 * 32;
+  const int64_t cta_begin = (int64_t)r * cta_len;
+  const int64_t cta_end = cta_begin + cta_len < numel ? cta_begin + cta_len : numel;
+  int64_t seg_len = (cta_len + 31) / 32;
   seg_len = (seg_len + 31) / 32 * 32;
-  const int64_t seg_begin = (int64_t)warp * seg_len;
-  const int64_t seg_end = seg_begin + seg_len < numel ? seg_begin + seg_len : numel;
+  const int64_t seg_begin = cta_begin + (int64_t)warp * seg_len;
+  const int64_t seg_end = seg_begin + seg_len < cta_end ? seg_begin + seg_len : cta_end;
   int32_t *my_hist = hist + warp * local_E;
   // bits that distinguish the local expert ids, or 0 = use the match instruction (few steps per warp)
   const int id_bits = seg_len >= 256 ? 32 - __clz(local_E > 1 ? local_E - 1 : 1) : 0;
@@ -159,7 +174,18 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(const IdT *__restrict__ i
       hist[w * local_E + e] = run;
       run += c;
     }
-    cnt[e] = counts_in ? counts_in[e] : run;
+    cta_cnt[e] = run;
+  }
+  cluster.sync();      // counts of every CTA published, m_indices cleared everywhere
+  for (int e = tid; e < local_E; e += blockDim.x) {
+    int total = 0, lower = 0;
+    for (int rr = 0; rr < C; ++rr) {
+      const int v = cluster.map_shared_rank(cta_cnt, rr)[e];
+      total += v;
+      if (rr < r) lower += v;
+    }
+    cnt[e] = counts_in ? counts_in[e] : total;
+    before[e] = lower;
   }
   __syncthreads();
   if (tid == 0) {
@@ -171,22 +197,53 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(const IdT *__restrict__ i
     off[local_E] = run;
   }
   __syncthreads();
-  for (int e = warp; e < local_E; e += 32)
-    for (int r = lane; r < cnt[e]; r += 32)
-      if (off[e] + r < rows) m_indices[off[e] + r] = e;
-  if (inv_perm == nullptr) return;
-  for (int64_t base = seg_begin; base < seg_end; base += 32) {
-    const int64_t i = base + lane;
-    const int e = i < seg_end ? local_expert<IdT>(ids, i, expert_map, local_E) : -1;
-    const unsigned peers = peers_of(e, id_bits);
-    const int rank = __popc(peers & ((1u << lane) - 1u));
-    int before = 0;
-    if (e >= 0) before = my_hist[e];
-    __syncwarp();
-    if (i < seg_end) inv_perm[i] = e >= 0 ? off[e] + before + rank : -1;
-    if (e >= 0 && lane == (__ffs(peers) - 1)) my_hist[e] = before + __popc(peers);
-    __syncwarp();
+  // expert id of every row: the CTAs share the experts
+  for (int e = r * 32 + warp; e < local_E; e += C * 32)
+    for (int q = lane; q < cnt[e]; q += 32)
+      if (off[e] + q < rows) m_indices[off[e] + q] = e;
+  if (inv_perm != nullptr) {
+    for (int64_t base = seg_begin; base < seg_end; base += 32) {
+      const int64_t i = base + lane;
+      const int e = i < seg_end ? local_expert<IdT>(ids, i, expert_map, local_E) : -1;
+      const unsigned peers = peers_of(e, id_bits);
+      const int rank = __popc(peers & ((1u << lane) - 1u));
+      int prior = 0;
+      if (e >= 0) prior = my_hist[e];
+      __syncwarp();
+      if (i < seg_end) inv_perm[i] = e >= 0 ? off[e] + before[e] + prior + rank : -1;
+      if (e >= 0 && lane == (__ffs(peers) - 1)) my_hist[e] = prior + __popc(peers);
+      __syncwarp();
+    }
   }
+  cluster.sync();      // no CTA leaves while another may still read its counts
+}
+
+template <typename IdT>
+int launch_ep_plan(const void *ids, int64_t numel, const int32_t *expert_map, const int32_t *counts_in, int local_E,
+                   int alignment, int32_t *m_indices, int64_t rows, int32_t *inv_perm, cudaStream_t st) {
+  const size_t smem = sizeof(int32_t) * (36 * (size_t)local_E + 1);
+  LO_CUDA_OK(cudaFuncSetAttribute(ep_plan_kernel<IdT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const IdT *idp = static_cast<const IdT *>(ids);
+  if (numel >= EP_PLAN_CLUSTER_MIN_IDS) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(EP_PLAN_CLUSTER, 1, 1);
+    cfg.blockDim = dim3(1024, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = EP_PLAN_CLUSTER;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    LO_CUDA_OK(cudaLaunchKernelEx(&cfg, ep_plan_kernel<IdT>, idp, numel, expert_map, counts_in, local_E, alignment,
+                                  m_indices, rows, inv_perm));
+    return LO_OK;
+  }
+  ep_plan_kernel<IdT><<<1, 1024, smem, st>>>(idp, numel, expert_map, counts_in, local_E, alignment, m_indices, rows, inv_perm);
+  LO_LAUNCH_OK("ep_plan_kernel");
+  return LO_OK;
 }
 
 // One CTA per (token, slot): copy the int8 row and its scales to inv_perm[token, slot].
@@ -297,21 +354,12 @@ extern "C" int lo_ep_build_m_indices(const void *topk_ids, int ids_dtype, int64_
   using namespace lo;
   LO_REQUIRE(local_num_experts >= 1 && local_num_experts <= 1024, "ep_build_m_indices: local_num_experts out of range");
   LO_REQUIRE(alignment >= 1 && m_indices && (topk_ids || numel == 0), "ep_build_m_indices: bad argument");
-  const size_t smem = sizeof(int32_t) * (34 * (size_t)local_num_experts + 1);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (ids_dtype == LO_I64) {
-    LO_CUDA_OK(cudaFuncSetAttribute(ep_plan_kernel<int64_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    ep_plan_kernel<int64_t><<<1, 1024, smem, st>>>(static_cast<const int64_t *>(topk_ids), numel, nullptr, nullptr,
-                                                  local_num_experts, alignment, m_indices, rows, nullptr);
-  } else if (ids_dtype == LO_I32) {
-    LO_CUDA_OK(cudaFuncSetAttribute(ep_plan_kernel<int32_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    ep_plan_kernel<int32_t><<<1, 1024, smem, st>>>(static_cast<const int32_t *>(topk_ids), numel, nullptr, nullptr,
-                                                  local_num_experts, alignment, m_indices, rows, nullptr);
-  } else {
-    return fail(LO_ERR_UNSUPPORTED, "ep_build_m_indices: unsupported id dtype code %d", ids_dtype);
-  }
-  LO_LAUNCH_OK("ep_plan_kernel");
-  return LO_OK;
+  if (ids_dtype == LO_I64)
+    return launch_ep_plan<int64_t>(topk_ids, numel, nullptr, nullptr, local_num_experts, alignment, m_indices, rows, nullptr, st);
+  if (ids_dtype == LO_I32)
+    return launch_ep_plan<int32_t>(topk_ids, numel, nullptr, nullptr, local_num_experts, alignment, m_indices, rows, nullptr, st);
+  return fail(LO_ERR_UNSUPPORTED, "ep_build_m_indices: unsupported id dtype code %d", ids_dtype);
 }
 
 extern "C" int lo_ep_scatter(const int8_t *aq, const float *aq_scale, int scale_cols, const void *topk_ids,
@@ -325,19 +373,14 @@ extern "C" int lo_ep_scatter(const int8_t *aq, const float *aq_scale, int scale_
   LO_REQUIRE(aq && aq_scale && topk_ids && aq_out && aq_scale_out && m_indices && inv_perm, "ep_scatter: null pointer");
   LO_REQUIRE(T * k <= 0x7fffffffLL, "ep_scatter: too many (token, slot) pairs");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const size_t smem = sizeof(int32_t) * (34 * (size_t)local_num_experts + 1);
-  if (ids_dtype == LO_I64) {
-    LO_CUDA_OK(cudaFuncSetAttribute(ep_plan_kernel<int64_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    ep_plan_kernel<int64_t><<<1, 1024, smem, st>>>(static_cast<const int64_t *>(topk_ids), T * k, expert_map,
-                                                  expert_num_tokens, local_num_experts, alignment, m_indices, rows, inv_perm);
-  } else if (ids_dtype == LO_I32) {
-    LO_CUDA_OK(cudaFuncSetAttribute(ep_plan_kernel<int32_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    ep_plan_kernel<int32_t><<<1, 1024, smem, st>>>(static_cast<const int32_t *>(topk_ids), T * k, expert_map,
-                                                  expert_num_tokens, local_num_experts, alignment, m_indices, rows, inv_perm);
-  } else {
+  int rc;
+  if (ids_dtype == LO_I64)
+    rc = launch_ep_plan<int64_t>(topk_ids, T * k, expert_map, expert_num_tokens, local_num_experts, alignment, m_indices, rows, inv_perm, st);
+  else if (ids_dtype == LO_I32)
+    rc = launch_ep_plan<int32_t>(topk_ids, T * k, expert_map, expert_num_tokens, local_num_experts, alignment, m_indices, rows, inv_perm, st);
+  else
     return fail(LO_ERR_UNSUPPORTED, "ep_scatter: unsupported id dtype code %d", ids_dtype);
-  }
-  LO_LAUNCH_OK("ep_plan_kernel");
+  if (rc != LO_OK) return rc;
   if (T * k > 0) {
     ep_copy_rows_kernel<<<(unsigned)(T * k), 128, 0, st>>>(aq, aq_scale, scale_cols, inv_perm, aq_out, aq_scale_out, k, H, rows);
     LO_LAUNCH_OK("ep_copy_rows_kernel");

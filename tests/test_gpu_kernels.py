@@ -229,6 +229,33 @@ def test_ep_build_m_indices_known_answer(lo):
     assert m.cpu().tolist() == [0, 0, 1, 1, 2, -1]
 
 
+@pytest.mark.parametrize("T,k,E,world", [(2100, 4, 16, 2), (8192, 8, 256, 8), (9000, 1, 8, 1)])
+def test_ep_scatter_many_rows(lo, T, k, E, world):
+    # from 8192 (token, slot) pairs on the plan runs as a cluster of CTAs; rank-as-expert packing as the
+    # expert-parallel driver uses it (the "expert" of a row is its destination rank)
+    g = torch.Generator().manual_seed(T + E)
+    H, align = 128, 1
+    aq = torch.randint(-127, 128, (T, H), generator=g, dtype=torch.int8)
+    scales = torch.rand(T, 1, generator=g)
+    ids = torch.randint(0, E, (T, k), generator=g, dtype=torch.int32)
+    rank_of_expert = (torch.arange(E) // (E // world)).to(torch.int32)
+    rows = T * k
+    out = torch.zeros(rows, H, dtype=torch.int8, device=DEV)
+    out_s = torch.zeros(rows, 1, device=DEV)
+    m_idx = torch.empty(rows, dtype=torch.int32, device=DEV)
+    inv = torch.empty(T, k, dtype=torch.int32, device=DEV)
+    lo.moe.ep_scatter(aq.to(DEV), scales.to(DEV), ids.to(DEV), rank_of_expert.to(DEV), None, out, out_s, m_idx, inv, world, align)
+    dest = rank_of_expert[ids.long()].reshape(-1)
+    # stable counting sort by destination rank
+    order = torch.sort(dest, stable=True).indices
+    inv_ref = torch.empty(rows, dtype=torch.int64)
+    inv_ref[order] = torch.arange(rows)
+    assert torch.equal(inv.cpu().reshape(-1).long(), inv_ref)
+    assert torch.equal(m_idx.cpu(), dest[order])
+    tok = torch.arange(T).repeat_interleave(k)
+    assert torch.equal(out.cpu()[inv_ref], aq[tok]) and torch.equal(out_s.cpu()[inv_ref], scales[tok])
+
+
 def test_ep_scatter_gather_roundtrip(lo):
     # the structure of the reference's tests (test/test_native_categorized_moe_api.py:77-144)
     g = torch.Generator().manual_seed(0)
