@@ -8,11 +8,12 @@
 // (HBM-bound) MoE needs, and the same kernel serves prefill and decode sizes.
 // In tensor memory a lane is an output column n and a column is a token.
 //
-// Work item = (chunk of <=128 expert-sorted rows, 128-row output tile).  Items
-// are ordered chunk-major so that CTAs running side by side share the chunk's
-// activation rows, and the chunks of one expert (adjacent in the table) read the
-// same weight tiles at about the same time out of L2.  Persistent CTAs take
-// items round-robin.
+// Work item = (chunk of <=128 expert-sorted rows, 128-row output tile; per-channel
+// mode: <=256 rows).  Items are ordered chunk-major so that CTAs running side by
+// side share the chunk's activation rows, and the chunks of one expert (adjacent
+// in the table) read the same weight tiles at about the same time: weight tiles
+// are loaded with an evict-first L2 policy unless the chunk table says that
+// another chunk of the expert follows.  Persistent CTAs take items round-robin.
 //
 // Warp roles in a CTA of 20 warps:
 //   warp 0      : TMA producer (one elected lane): weight tiles and the chunk's token rows.
