@@ -229,6 +229,35 @@ __global__ void __launch_bounds__(TOKEN_QUANT_THREADS) silu_mul_token_quant_kern
   const __nv_bfloat16 *u = g + d;
   const int64_t vecs = d / 8;
   float amax = 0.f;
+  if (vecs <= 2 * TOKEN_QUANT_THREADS) {
+    // rows of up to 4096 channels: the activations stay in registers between the maximum and the
+    // quantisation (one read of the row, one evaluation of the SiLU)
+    float av[2][8];
+#pragma unroll
+    for (int v = 0; v < 2; ++v) {
+      const int64_t i = threadIdx.x + (int64_t)v * TOKEN_QUANT_THREADS;
+      if (i < vecs) {
+        float gv[8], uv[8];
+        Load8<__nv_bfloat16>::load(g + i * 8, gv);
+        Load8<__nv_bfloat16>::load(u + i * 8, uv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float sl = __bfloat162float(__float2bfloat16_rn(__fdiv_rn(gv[j], 1.0f + expf(-gv[j]))));
+          av[v][j] = __bfloat162float(__float2bfloat16_rn(sl * uv[j]));
+          amax = fmaxf(amax, fabsf(av[v][j]));
+        }
+      }
+    }
+    amax = block_max_256(amax, red);
+    const float inv = amax == 0.f ? 0.f : __fdiv_rn(127.0f, amax);
+#pragma unroll
+    for (int v = 0; v < 2; ++v) {
+      const int64_t i = threadIdx.x + (int64_t)v * TOKEN_QUANT_THREADS;
+      if (i < vecs) *reinterpret_cast<uint2 *>(q + row * d + i * 8) = quant8_rn(av[v], inv);
+    }
+    if (threadIdx.x == 0) s[row] = __fdiv_rn(amax, 127.0f);
+    return;
+  }
   for (int64_t i = threadIdx.x; i < vecs; i += TOKEN_QUANT_THREADS) {
     float gv[8], uv[8];
     Load8<__nv_bfloat16>::load(g + i * 8, gv);
