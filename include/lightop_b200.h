@@ -246,6 +246,30 @@ int lo_moe_fused_gate(const void *x, int x_dtype, const void *bias, int bias_dty
                       float *topk_weights, void *topk_ids, int ids_dtype, void *stream);
 
 /*
+ * The general form of the gate above, which also covers the reference's ungrouped variants:
+ *   score p = sigmoid(x) (LO_GATE_SIGMOID) or sqrt(log1p(exp(x))) (LO_GATE_SQRT_SOFTPLUS); selection on p + bias with
+ *   the group limit (num_expert_group = topk_group = 1 for none); routed weight = p / (renormalize ? sum + norm_eps : 1)
+ *   * out_scale; shared-expert slots (ids E + j) carry p = sum / shared_div through the same formula.
+ *   bias_row_stride: 0 for one bias [E] shared by all tokens, else the element stride of a per-token bias [M, E].
+ *   num_token_non_padded (device scalar, LO_I32 / LO_I64, or NULL): rows at or beyond it get weight 0 and id
+ *   padding_id; the count is read on the device, so it may change between replays of a captured graph.
+ * Replaces (with the parameters its Python layer derives, lightop_b200/moe/routing.py): op.kimi_k2_moe_fused_gate
+ * (csrc/kernels/moe_gate/moe_fused_gate_kimi_k2.cu; model test/ci_tests/test_kimi_k2_moe_fused_gate.py:14-43) and
+ * op.moe_fused_gate_sqrtsoftplus (csrc/kernels/moe_gate/moe_fused_gate_sqrtsoftplus.cu; model
+ * test/ci_tests/test_moe_fused_gate_sqrtsoftplus.py:9-45), with its padded forms ..._v41_hcu_fused (padding id 0)
+ * and ..._v41_hcu_deepep (padding id -1) (csrc/kernels/moe_gate/moe_fused_gate_sqrtsoftplus.cu:205-212, :378-421).
+ */
+#define LO_GATE_SIGMOID 0
+#define LO_GATE_SQRT_SOFTPLUS 1
+#define LO_GATE_SQRT_SOFTPLUS_SAFE 2 /* softplus(x) = x beyond 20: the reference's "v41" entry points */
+int lo_moe_gate_topk(const void *x, int x_dtype, const void *bias, int bias_dtype, int64_t bias_row_stride,
+                     int64_t M, int E,
+                     int num_expert_group, int topk_group, int topk, int n_shared, int score_fn,
+                     int renormalize, float norm_eps, float out_scale, float shared_div,
+                     const void *num_token_non_padded, int num_token_dtype, int padding_id,
+                     float *topk_weights, void *topk_ids, int ids_dtype, void *stream);
+
+/*
  * In-place post-processing of top-k ids: ids of tokens at or beyond *num_token_non_padded become -1, the others
  * go through the logical -> physical expert map (ids outside [0, map_size) become -1).  Either pointer may be
  * NULL to skip that step.  topk_ids [M,topk] LO_I32 / LO_I64; the map and the count are LO_I32 / LO_I64 device data.

@@ -15,6 +15,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("LIGHTOP_B200_LIB") or os.path.join(_HERE, "liblightop_b200.so")
 
 LO_F32, LO_F16, LO_BF16, LO_I32, LO_I64, LO_U32 = 0, 1, 2, 3, 4, 5
+LO_GATE_SIGMOID, LO_GATE_SQRT_SOFTPLUS, LO_GATE_SQRT_SOFTPLUS_SAFE = 0, 1, 2
 LO_WEIGHT_NONE, LO_WEIGHT_FP32, LO_WEIGHT_BF16_PRODUCT = 0, 1, 2
 
 _DTYPE_CODE = {
@@ -57,6 +58,8 @@ PROTOTYPES = {
                                      c_void_p, c_size_t, c_void_p, c_void_p]),
     "lo_moe_fused_gate": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int64, c_int, c_int, c_int, c_int, c_int, c_float,
                                   c_int, c_void_p, c_void_p, c_int, c_void_p]),
+    "lo_moe_gate_topk": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                 c_float, c_float, c_float, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "lo_topk_ids_postprocess": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_int, c_int64, c_void_p, c_int,
                                         c_void_p]),
     "lo_per_token_quant_int8": (c_int, [c_void_p, c_int, c_int64, c_int64, c_void_p, c_void_p, c_void_p]),

@@ -175,6 +175,116 @@ def moe_fused_gate(x: torch.Tensor, bias: torch.Tensor, num_expert_group: int, t
     return weights, ids
 
 
+def _gate_topk(x, bias, groups, topk_group, topk, n_shared, score_fn, renormalize, norm_eps, out_scale, shared_div,
+               ids_dtype=torch.int32, num_token_non_padded=None, padding_id=0, per_token_bias=False, what="gate"):
+    _lib.require_cuda(x, bias, num_token_non_padded)
+    n = num_token_non_padded
+    if n is not None and (n.dtype not in (torch.int32, torch.int64) or n.numel() != 1 or not n.is_contiguous()):
+        raise RuntimeError(f"{what}: num_token_non_padded must be one contiguous int32 or int64 element")
+    if x.dim() != 2:
+        raise RuntimeError(f"{what}: input must have shape [tokens, experts], got {tuple(x.shape)}")
+    M, E = x.shape
+    if bias.dim() == 2 and per_token_bias:
+        if tuple(bias.shape) != (M, E):
+            raise RuntimeError(f"{what}: a 2D bias must have shape [tokens, experts], got {tuple(bias.shape)}")
+    elif bias.dim() != 1 or bias.numel() != E:
+        raise RuntimeError(f"{what}: bias must have shape [experts], got {tuple(bias.shape)}")
+    if not (x.is_contiguous() and bias.is_contiguous()):
+        raise RuntimeError(f"{what}: input and bias must be contiguous")
+    weights = torch.empty(M, topk, dtype=torch.float32, device=x.device)
+    ids = torch.empty(M, topk, dtype=ids_dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        st = _lib.load().lo_moe_gate_topk(_lib.ptr(x), _lib.dtype_code(x.dtype), _lib.ptr(bias), _lib.dtype_code(bias.dtype),
+                                          E if bias.dim() == 2 else 0, M, E, int(groups), int(topk_group), int(topk),
+                                          int(n_shared), int(score_fn), int(bool(renormalize)), float(norm_eps),
+                                          float(out_scale), float(shared_div), _lib.ptr(n) if n is not None else 0,
+                                          _lib.dtype_code(n.dtype) if n is not None else 0, int(padding_id),
+                                          _lib.ptr(weights), _lib.ptr(ids), _lib.dtype_code(ids.dtype),
+                                          _lib.current_stream(x.device))
+    _lib.check(st, what)
+    return weights, ids
+
+
+def kimi_k2_moe_fused_gate(x: torch.Tensor, bias: torch.Tensor, topk: int, renormalize: bool = True,
+                           routed_scaling_factor: float = 1.0,
+                           apply_routed_scaling_factor_on_output: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Ungrouped bias-corrected sigmoid gate (Kimi-K2): top-k on ``sigmoid(x) + bias``, weights ``sigmoid(x)`` of the
+    chosen experts, divided by ``sum + 1e-20`` when ``renormalize`` and then (only then) scaled on request.
+
+    Signature of the reference (python/lightop/moe_fused_gate.py:34-49); semantics of its torch model
+    (test/ci_tests/test_kimi_k2_moe_fused_gate.py:14-43).  Ids come out in descending order of the selection
+    score, ties to the lower id.
+    """
+    scale = float(routed_scaling_factor) if (renormalize and apply_routed_scaling_factor_on_output) else 1.0
+    return _gate_topk(x, bias, 1, 1, topk, 0, _lib.LO_GATE_SIGMOID, renormalize, 1e-20, scale, 1.0,
+                      what="kimi_k2_moe_fused_gate")
+
+
+def _sqrtsoftplus(x, bias, topk, num_fused_shared_experts, renormalize, routed_scaling_factor,
+                  apply_routed_scaling_factor_on_output, score_fn, what, ids_dtype=torch.int32,
+                  num_token_non_padded=None, padding_id=0):
+    # argument rules of csrc/kernels/moe_gate/moe_fused_gate_sqrtsoftplus.cu:267-294 (any expert count is accepted here)
+    if not routed_scaling_factor > 0.0:
+        raise RuntimeError(f"{what}: routed_scaling_factor must be positive")
+    scale = float(routed_scaling_factor) if apply_routed_scaling_factor_on_output else 1.0
+    return _gate_topk(x, bias, 1, 1, topk, num_fused_shared_experts, score_fn, renormalize, 0.0, scale,
+                      float(routed_scaling_factor), ids_dtype=ids_dtype, num_token_non_padded=num_token_non_padded,
+                      padding_id=padding_id, per_token_bias=True, what=what)
+
+
+def moe_fused_gate_sqrtsoftplus(x: torch.Tensor, bias: torch.Tensor, topk: int, num_fused_shared_experts: int = 0,
+                                renormalize: bool = True, routed_scaling_factor: float = 1.0,
+                                apply_routed_scaling_factor_on_output: bool = False
+                                ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Ungrouped gate with scores ``sqrt(softplus(x))``: top-k on score + bias, weights = scores of the chosen experts
+    over their sum (when ``renormalize``), shared experts as extra slots with ids ``E + j`` and score
+    ``sum / routed_scaling_factor``, everything times the factor when it is applied on the output.  ``bias`` is
+    ``[experts]`` or, per token, ``[tokens, experts]``.
+
+    Signature of the reference (python/lightop/moe_fused_gate.py:52-69); semantics of its torch model
+    (test/ci_tests/test_moe_fused_gate_sqrtsoftplus.py:9-45).
+    """
+    return _sqrtsoftplus(x, bias, topk, num_fused_shared_experts, renormalize, routed_scaling_factor,
+                         apply_routed_scaling_factor_on_output, _lib.LO_GATE_SQRT_SOFTPLUS, "moe_fused_gate_sqrtsoftplus")
+
+
+def moe_fused_gate_sqrtsoftplus_v41_hcu(x: torch.Tensor, bias: torch.Tensor, topk: int, num_fused_shared_experts: int = 0,
+                                        renormalize: bool = True, routed_scaling_factor: float = 1.0,
+                                        apply_routed_scaling_factor_on_output: bool = False
+                                        ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The same gate with ``softplus(x) = x`` for ``x > 20`` (equal to fp32 precision, and free of the overflow of
+    ``exp``): python/lightop/moe_fused_gate.py:72-88, csrc/kernels/moe_gate/moe_fused_gate_sqrtsoftplus.cu:66-69."""
+    return _sqrtsoftplus(x, bias, topk, num_fused_shared_experts, renormalize, routed_scaling_factor,
+                         apply_routed_scaling_factor_on_output, _lib.LO_GATE_SQRT_SOFTPLUS_SAFE,
+                         "moe_fused_gate_sqrtsoftplus_v41_hcu")
+
+
+def moe_fused_gate_sqrtsoftplus_v41_hcu_fused(x: torch.Tensor, bias: torch.Tensor, topk: int,
+                                              num_fused_shared_experts: int = 0, renormalize: bool = True,
+                                              routed_scaling_factor: float = 1.0,
+                                              apply_routed_scaling_factor_on_output: bool = False,
+                                              num_token_non_padded: Optional[torch.Tensor] = None
+                                              ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """The ``v41`` gate with int64 ids; rows at or beyond the device-side ``num_token_non_padded`` get weight 0 and
+    id 0 (python/lightop/moe_fused_gate.py:91-107, csrc/kernels/moe_gate/moe_fused_gate_sqrtsoftplus.cu:378-399)."""
+    return _sqrtsoftplus(x, bias, topk, num_fused_shared_experts, renormalize, routed_scaling_factor,
+                         apply_routed_scaling_factor_on_output, _lib.LO_GATE_SQRT_SOFTPLUS_SAFE,
+                         "moe_fused_gate_sqrtsoftplus_v41_hcu_fused", torch.int64, num_token_non_padded, 0)
+
+
+def moe_fused_gate_sqrtsoftplus_v41_hcu_deepep(x: torch.Tensor, bias: torch.Tensor, topk: int,
+                                               num_fused_shared_experts: int = 0, renormalize: bool = True,
+                                               routed_scaling_factor: float = 1.0,
+                                               apply_routed_scaling_factor_on_output: bool = False,
+                                               num_token_non_padded: Optional[torch.Tensor] = None
+                                               ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """As the ``_fused`` form, with id -1 on the padded rows: the value an expert-parallel dispatch skips
+    (python/lightop/moe_fused_gate.py:110-127, csrc/kernels/moe_gate/moe_fused_gate_sqrtsoftplus.cu:401-421)."""
+    return _sqrtsoftplus(x, bias, topk, num_fused_shared_experts, renormalize, routed_scaling_factor,
+                         apply_routed_scaling_factor_on_output, _lib.LO_GATE_SQRT_SOFTPLUS_SAFE,
+                         "moe_fused_gate_sqrtsoftplus_v41_hcu_deepep", torch.int64, num_token_non_padded, -1)
+
+
 def topk_ids_postprocess(topk_ids: torch.Tensor, logical_to_physical_map: Optional[torch.Tensor] = None,
                          num_token_non_padded: Optional[torch.Tensor] = None) -> None:
     """In place: padded tokens' ids become -1, the others are mapped logical -> physical

@@ -141,3 +141,13 @@ def reference_grouped_layout_models():
     masked = extract_functions("test/deepgemm/w8a8_moe_groupgemm_mask_marlin_correctness.py",
                                ["native_w8a8_perChannel_batch_matmul"])["native_w8a8_perChannel_batch_matmul"]
     return contig, masked
+
+
+def reference_gate_variant_models():
+    """(Kimi-K2 gate model, sqrt-softplus gate model) from test/ci_tests/test_kimi_k2_moe_fused_gate.py:14-43 and
+    test/ci_tests/test_moe_fused_gate_sqrtsoftplus.py:9-45."""
+    kimi = extract_functions("test/ci_tests/test_kimi_k2_moe_fused_gate.py",
+                             ["kimi_k2_biased_topk_impl_ref"])["kimi_k2_biased_topk_impl_ref"]
+    ssp = extract_functions("test/ci_tests/test_moe_fused_gate_sqrtsoftplus.py",
+                            ["reference_moe_fused_gate_sqrtsoftplus"])["reference_moe_fused_gate_sqrtsoftplus"]
+    return kimi, ssp

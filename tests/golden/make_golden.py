@@ -3,7 +3,7 @@
 Run where a reference checkout is available (``$LIGHTOP_REF``, see oracle/ref_extract.py):
     python tests/golden/make_golden.py            (all fixtures)
     python tests/golden/make_golden.py channel    (only channel_cases.pt)
-    python tests/golden/make_golden.py gate       (only gate_cases.pt)
+    python tests/golden/make_golden.py gate       (only gate_cases.pt and gate_variant_cases.pt)
 The outputs are produced by the reference code itself (loaded by oracle/ref_extract.py),
 not by the restatement in oracle/moe_block_int8.py; the tests then hold both the oracle
 and the CUDA kernels to these files.  Inputs are not stored: they are regenerated from
@@ -127,12 +127,43 @@ def main_gate() -> None:
     print("wrote gate_cases.pt")
 
 
+KIMI_CASES = [  # (tokens, experts, topk, renormalize, factor, apply on output, seed)
+    (48, 384, 8, True, 2.0, True, 41), (17, 384, 8, True, 2.0, False, 42), (9, 256, 6, False, 3.0, True, 43)]
+SSP_CASES = [   # (tokens, experts, topk, shared, renormalize, factor, apply on output, seed)
+    (16, 256, 6, 0, True, 2.5, False, 51), (33, 256, 6, 1, True, 2.5, False, 52), (20, 256, 6, 1, True, 2.5, True, 53),
+    (11, 128, 7, 2, False, 1.5, True, 54)]
+
+
+def variant_inputs(M, E, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(M, E, generator=g), torch.randn(E, generator=g)
+
+
+def main_gate_variants() -> None:
+    """Fixtures of the Kimi-K2 and sqrt-softplus gates (tests/golden/gate_variant_cases.pt), canonicalised by id."""
+    kimi, ssp = ref_extract.reference_gate_variant_models()
+    out = {"kimi": [], "ssp": []}
+    for case in KIMI_CASES:
+        x, b = variant_inputs(case[0], case[1], case[-1])
+        w, i = kimi(None, x, b, case[2], case[3], case[4], case[5])
+        order = torch.argsort(i, dim=-1)
+        out["kimi"].append(dict(case=case, ids=torch.gather(i, 1, order), weights=torch.gather(w, 1, order).float()))
+    for case in SSP_CASES:
+        x, b = variant_inputs(case[0], case[1], case[-1])
+        w, i = ssp(x, b, case[2], case[3], case[4], case[5], case[6])
+        out["ssp"].append(dict(case=case, ids=i, weights=w))        # this model's order is part of its contract
+    torch.save(out, os.path.join(HERE, "gate_variant_cases.pt"))
+    print("wrote gate_variant_cases.pt")
+
+
 if __name__ == "__main__":
     if len(sys.argv) > 1 and sys.argv[1] == "channel":
         main_channel()
     elif len(sys.argv) > 1 and sys.argv[1] == "gate":
         main_gate()
+        main_gate_variants()
     else:
         main()
         main_channel()
         main_gate()
+        main_gate_variants()

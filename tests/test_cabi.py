@@ -93,7 +93,9 @@ def test_api_names_present():
     import lightop_b200
     for name in ["topk_softmax", "moe_align_block_size", "moe_align_block_size_out", "moe_sum", "moe_gemm_w8a8",
                  "fused_experts_impl_int8", "fused_experts_impl_int8_marlin", "ep_scatter", "ep_gather",
-                 "ep_build_m_indices"]:
+                 "ep_build_m_indices", "moe_fused_gate", "kimi_k2_moe_fused_gate", "moe_fused_gate_sqrtsoftplus",
+                 "moe_fused_gate_sqrtsoftplus_v41_hcu", "moe_fused_gate_sqrtsoftplus_v41_hcu_fused",
+                 "moe_fused_gate_sqrtsoftplus_v41_hcu_deepep", "topk_ids_postprocess"]:
         assert hasattr(lightop_b200.moe, name)
     assert hasattr(lightop_b200.quant, "per_token_group_quant_int8")
     assert hasattr(lightop_b200.quant, "per_token_quant_int8")

@@ -145,3 +145,147 @@ def test_topk_ids_postprocess(lo):
         lo.moe.topk_ids_postprocess(t, m.to(DEV) if m is not None else None, n.to(DEV) if n is not None else None)
         assert torch.equal(t.cpu(), OG.topk_ids_postprocess(base, m, n))
     lo.moe.topk_ids_postprocess(torch.empty(0, 8, dtype=torch.int32, device=DEV))
+
+
+def _variant_ids_match(ids, ref_ids, score, bias):
+    """Exact, except rows where the oracle's own selection scores tie within a few ulps (device vs torch math)."""
+    if torch.equal(ids, ref_ids):
+        return True
+    s = score + bias.float().unsqueeze(0)
+    E = s.shape[1]
+    for r in (ids != ref_ids).any(dim=1).nonzero().reshape(-1).tolist():
+        a = set(ids[r].tolist()) - set(ref_ids[r].tolist())
+        b = set(ref_ids[r].tolist()) - set(ids[r].tolist())
+        if any(e >= E for e in a | b) or len(a) != len(b):
+            return False
+        sa = sorted(float(s[r, e]) for e in a)
+        sb = sorted(float(s[r, e]) for e in b)
+        if any(abs(u - v) > 4e-7 * max(1.0, abs(v)) for u, v in zip(sa, sb)):
+            return False
+        if not a:                   # same set in another order: only neighbours with tied scores may swap
+            sr = s[r, ref_ids[r].long().clamp(max=E - 1)]
+            so = s[r, ids[r].long().clamp(max=E - 1)]
+            if float((sr - so).abs().max()) > 4e-7 * max(1.0, float(sr.abs().max())):
+                return False
+    return True
+
+
+def test_gate_variants_against_golden(lo, golden_dir):
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(golden_dir, "make_golden.py"))
+    mg = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mg)
+    fx = torch.load(os.path.join(golden_dir, "gate_variant_cases.pt"))
+    for entry in fx["kimi"]:
+        M, E, k, renorm, rsf, apply, seed = entry["case"]
+        x, b = mg.variant_inputs(M, E, seed)
+        w, i = lo.moe.kimi_k2_moe_fused_gate(x.to(DEV), b.to(DEV), k, renorm, rsf, apply)
+        assert w.dtype == torch.float32 and i.dtype == torch.int32
+        wc, ic = canon(w.cpu(), i.cpu())
+        assert torch.equal(ic, entry["ids"]), entry["case"]
+        torch.testing.assert_close(wc, entry["weights"], rtol=1e-5, atol=1e-6)
+    for entry in fx["ssp"]:
+        M, E, k, sh, renorm, rsf, apply, seed = entry["case"]
+        x, b = mg.variant_inputs(M, E, seed)
+        for fn in (lo.moe.moe_fused_gate_sqrtsoftplus, lo.moe.moe_fused_gate_sqrtsoftplus_v41_hcu):
+            w, i = fn(x.to(DEV), b.to(DEV), k, sh, renorm, rsf, apply)
+            assert torch.equal(i.cpu(), entry["ids"]), entry["case"]        # order included
+            torch.testing.assert_close(w.cpu(), entry["weights"], rtol=1e-5, atol=1e-5)   # the reference test's bars
+
+
+@pytest.mark.parametrize("M", [1, 16, 256, 513, 4096])
+@pytest.mark.parametrize("E,k", [(384, 8), (256, 6)])
+@pytest.mark.parametrize("renorm,apply", [(True, True), (True, False), (False, True)])
+def test_kimi_gate_vs_oracle(lo, M, E, k, renorm, apply):
+    g = torch.Generator().manual_seed(M * 3 + E + k)
+    x, b = torch.randn(M, E, generator=g), torch.randn(E, generator=g)
+    w, i = lo.moe.kimi_k2_moe_fused_gate(x.to(DEV), b.to(DEV), k, renorm, 2.5, apply)
+    w_ref, i_ref = OG.kimi_k2_gate(x, b, k, renorm, 2.5, apply)
+    w, i = w.cpu(), i.cpu()
+    assert _variant_ids_match(i, i_ref, torch.sigmoid(x), b)
+    same = (i == i_ref).all(dim=1)
+    assert float(same.float().mean()) >= 0.99
+    torch.testing.assert_close(w[same], w_ref[same], rtol=2e-5, atol=2e-6)
+
+
+@pytest.mark.parametrize("M", [1, 16, 256, 513, 4096])
+@pytest.mark.parametrize("k,sh", [(6, 0), (6, 1), (8, 0), (9, 2)])
+@pytest.mark.parametrize("renorm,apply", [(True, False), (True, True), (False, False)])
+def test_sqrtsoftplus_gate_vs_oracle(lo, M, k, sh, renorm, apply):
+    # shapes and options of test/ci_tests/test_moe_fused_gate_sqrtsoftplus.py:89-99 and more
+    g = torch.Generator().manual_seed(M * 5 + k + sh)
+    x, b = torch.randn(M, 256, generator=g), torch.randn(256, generator=g)
+    w, i = lo.moe.moe_fused_gate_sqrtsoftplus(x.to(DEV), b.to(DEV), k, sh, renorm, 2.5, apply)
+    w_ref, i_ref = OG.sqrtsoftplus_gate(x, b, k, sh, renorm, 2.5, apply)
+    w, i = w.cpu(), i.cpu()
+    assert _variant_ids_match(i, i_ref, torch.sqrt(torch.log1p(torch.exp(x))), b)
+    same = (i == i_ref).all(dim=1)
+    assert float(same.float().mean()) >= 0.99
+    torch.testing.assert_close(w[same], w_ref[same], rtol=1e-5, atol=1e-5)
+
+
+def test_sqrtsoftplus_gate_padded_forms(lo):
+    g = torch.Generator().manual_seed(77)
+    x, b = torch.randn(40, 256, generator=g), torch.randn(256, generator=g)
+    w_ref, i_ref = OG.sqrtsoftplus_gate(x, b, 7, 1, True, 2.5, True)
+    for fn, pad in ((lo.moe.moe_fused_gate_sqrtsoftplus_v41_hcu_fused, 0), (lo.moe.moe_fused_gate_sqrtsoftplus_v41_hcu_deepep, -1)):
+        for count in (torch.tensor([25], dtype=torch.int32), torch.tensor([0], dtype=torch.int64),
+                      torch.tensor([40], dtype=torch.int64), torch.tensor([1000], dtype=torch.int32), None):
+            w, i = fn(x.to(DEV), b.to(DEV), 7, 1, True, 2.5, True, count.to(DEV) if count is not None else None)
+            assert i.dtype == torch.int64
+            wr, ir = OG.mask_padded_rows(w_ref, i_ref, int(count) if count is not None else 40, pad)
+            assert torch.equal(i.cpu(), ir)
+            torch.testing.assert_close(w.cpu(), wr, rtol=1e-5, atol=1e-5)
+    # the count lives on the device: a captured graph follows its changes
+    count = torch.tensor([10], dtype=torch.int64, device=DEV)
+    xd, bd = x.to(DEV), b.to(DEV)
+    s = torch.cuda.Stream()
+    with torch.cuda.stream(s):
+        lo.moe.moe_fused_gate_sqrtsoftplus_v41_hcu_deepep(xd, bd, 7, 1, True, 2.5, True, count)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=s):
+            w, i = lo.moe.moe_fused_gate_sqrtsoftplus_v41_hcu_deepep(xd, bd, 7, 1, True, 2.5, True, count)
+    for n in (10, 33):
+        count.fill_(n)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(i.cpu(), OG.mask_padded_rows(w_ref, i_ref, n, -1)[1])
+
+
+def test_sqrtsoftplus_gate_per_token_bias_and_large_logits(lo):
+    g = torch.Generator().manual_seed(78)
+    x, b2 = torch.randn(37, 256, generator=g), torch.randn(37, 256, generator=g)
+    for fn, safe in ((lo.moe.moe_fused_gate_sqrtsoftplus, False), (lo.moe.moe_fused_gate_sqrtsoftplus_v41_hcu, True)):
+        w, i = fn(x.to(DEV), b2.to(DEV), 8, 1, True, 2.5, False)
+        w_ref, i_ref = OG.sqrtsoftplus_gate(x, b2, 8, 1, True, 2.5, False, softplus_linear_above_20=safe)
+        assert torch.equal(i.cpu(), i_ref)
+        torch.testing.assert_close(w.cpu(), w_ref, rtol=1e-5, atol=1e-5)
+    # logits beyond the overflow of exp: the second form keeps finite scores sqrt(x)
+    xl = torch.randn(9, 256, generator=g) * 60
+    w, i = lo.moe.moe_fused_gate_sqrtsoftplus_v41_hcu(xl.to(DEV), b2[0].contiguous().to(DEV), 6, 0, True, 1.0, False)
+    w_ref, i_ref = OG.sqrtsoftplus_gate(xl, b2[0], 6, 0, True, 1.0, False, softplus_linear_above_20=True)
+    assert torch.isfinite(w).all() and torch.equal(i.cpu(), i_ref)
+    torch.testing.assert_close(w.cpu(), w_ref, rtol=1e-5, atol=1e-5)
+    with pytest.raises(RuntimeError):
+        lo.moe.moe_fused_gate_sqrtsoftplus(x.to(DEV), b2[:5].contiguous().to(DEV), 8)          # 2D bias of the wrong height
+    with pytest.raises(RuntimeError):
+        lo.moe.moe_fused_gate_sqrtsoftplus(x.to(DEV), b2[0].contiguous().to(DEV), 8, 0, True, 0.0)   # factor must be > 0
+
+
+def test_gate_variants_edge_cases(lo):
+    from lightop_b200._lib import LightopError
+    b = torch.zeros(256, device=DEV)
+    # logits so negative that every sqrt-softplus score is 0: no division by the zero sum
+    w, i = lo.moe.moe_fused_gate_sqrtsoftplus(torch.full((2, 256), -200.0, device=DEV), b, 6, 0, True, 2.5, False)
+    assert torch.equal(w.cpu(), torch.zeros(2, 6)) and i.cpu().tolist() == [list(range(6))] * 2
+    # Kimi-K2 with every sigmoid 0: the 1e-20 keeps the quotient finite
+    w, _ = lo.moe.kimi_k2_moe_fused_gate(torch.full((2, 384), -200.0, device=DEV), torch.zeros(384, device=DEV), 8)
+    assert torch.equal(w.cpu(), torch.zeros(2, 8))
+    w0, i0 = lo.moe.kimi_k2_moe_fused_gate(torch.empty(0, 384, device=DEV), torch.zeros(384, device=DEV), 8)
+    assert w0.shape == (0, 8) and i0.shape == (0, 8)
+    with pytest.raises(LightopError):
+        lo.moe.moe_fused_gate_sqrtsoftplus(torch.zeros(2, 256, device=DEV), b, 6, 6)       # only shared slots
+    with pytest.raises(LightopError):
+        lo.moe.kimi_k2_moe_fused_gate(torch.zeros(2, 384, device=DEV), torch.zeros(384, device=DEV), 40)
+    with pytest.raises(RuntimeError):
+        lo.moe.moe_fused_gate_sqrtsoftplus_v41_hcu_fused(torch.zeros(2, 256, device=DEV), b, 6, 0, True, 1.0, False,
+                                                         torch.zeros(1, device=DEV))      # a float count
