@@ -142,10 +142,11 @@ extern "C" int lo_fused_moe_block_int8(const void *x, const int8_t *w1, const in
   const int64_t numel = M * topk;
   int rc;
 
-  // Largest chunk of one expert's rows handed to a CTA.  128 (the MMA N limit used here) is best at every
-  // size measured: an M=128, K=32 MMA costs the same ~96 cycles for any N <= 128, so smaller chunks only
-  // multiply the MMA count (64 -> 1.3x, 32 -> 1.9x the layer time at 128 rows per expert).
-  const int chunk_max = 128;
+  // Largest chunk of one expert's rows handed to a CTA.  An M=128, K=32 MMA costs the same ~96 cycles for any
+  // N <= 128, so chunks smaller than 128 only multiply the MMA count (64 -> 1.3x, 32 -> 1.9x the layer time at
+  // 128 rows per expert).  With about 128 rows per expert (uniform routing at prefill sizes) half of the experts
+  // get a few rows more than 128: chunks of up to 160 rows take those in one pass over the weights instead of two.
+  const int chunk_max = numel / align_E >= 64 ? 160 : 128;
   // 1. expert-major stable order, chunk table, position of every (token, slot)
   prof_mark(0, st);
   rc = launch_align(topk_ids, ids_dtype, numel, align_E, FUSED_ALIGN_BLOCK, expert_map, expert_map ? 1 : 0,
@@ -509,10 +510,8 @@ extern "C" int lo_expert_rows_block_int8(const int8_t *xq, const float *xs, cons
   FusedLayout L = carve_fused(workspace, T, E_local, 1, H, I);
   LO_REQUIRE(workspace_bytes >= L.bytes, "expert rows: workspace of %zu bytes, %zu needed", workspace_bytes, L.bytes);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // Largest chunk of one expert's rows handed to a CTA.  128 (the MMA N limit used here) is best at every
-  // size measured: an M=128, K=32 MMA costs the same ~96 cycles for any N <= 128, so smaller chunks only
-  // multiply the MMA count (64 -> 1.3x, 32 -> 1.9x the layer time at 128 rows per expert).
-  const int chunk_max = 128;
+  // chunk size: the rule of lo_fused_moe_block_int8
+  const int chunk_max = T / E_local >= 64 ? 160 : 128;
   // 1. expert-major stable order of the rows (ids outside [0, E_local) are dropped)
   int rc = launch_align(row_expert, LO_I32, T, E_local, FUSED_ALIGN_BLOCK, nullptr, 0, L.sorted_ids, L.sorted_cap,
                         nullptr, 0, L.header, L.chunks, L.header + 1, L.chunk_cap, nullptr, chunk_max, st);

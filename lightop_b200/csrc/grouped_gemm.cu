@@ -3,13 +3,16 @@
 //
 // Orientation ("swap-AB").  The 128 rows of a weight tile are the M side of the
 // MMA and the tokens of one expert are its N side (N = tokens rounded up to 16,
-// at most 128).  A chunk of 1..128 tokens therefore costs one pass over the
-// weight tile with no padding to 128 rows, which is what a weight-streaming
-// (HBM-bound) MoE needs, and the same kernel serves prefill and decode sizes.
-// In tensor memory a lane is an output column n and a column is a token.
+// at most 160 with block scales).  A chunk of 1..160 tokens therefore costs one
+// pass over the weight tile with no padding to 128 rows, which is what a
+// weight-streaming (HBM-bound) MoE needs, and the same kernel serves prefill and
+// decode sizes.  In tensor memory a lane is an output column n and a column is a token.
 //
-// Work item = (chunk of <=128 expert-sorted rows, 128-row output tile; per-channel
-// mode: <=256 rows).  Items are ordered chunk-major so that CTAs running side by
+// Work item = (chunk of <=160 expert-sorted rows, 128-row output tile; per-channel
+// mode: <=256 rows).  The 160-row instantiation exists for prefill sizes with about
+// 128 rows per expert, where many experts get a few rows more than 128: its three
+// sets of 160 tensor-memory columns (running sums, partials) just fit into the 512,
+// which leaves gate_up a single partial buffer.  Items are ordered chunk-major so that CTAs running side by
 // side share the chunk's activation rows, and the chunks of one expert (adjacent
 // in the table) read the same weight tiles at about the same time: weight tiles
 // are loaded with an evict-first L2 policy unless the chunk table says that
@@ -58,7 +61,8 @@ namespace {
 
 constexpr int TILE_N = 128;      // weight rows per accumulator (MMA M)
 constexpr int TILE_K = 128;      // int8 elements (= bytes) per K block
-constexpr int T_MAX = 128;       // tokens per chunk (MMA N upper bound)
+constexpr int T_MAX = 128;       // tokens per chunk unless the caller asks for the wide block-scaled chunks
+constexpr int T_WIDE = 160;      // widest block-scaled chunk: 3 x 160 tensor-memory columns (sums + partials) fit into 512
 constexpr int NUM_THREADS = 640;
 constexpr int SCALE_THREADS = 64;
 constexpr int EPI_WARPS = 16;
@@ -79,7 +83,9 @@ constexpr float MAGIC_F = 12582912.0f;
 template <int MODE, int A_ROWS> struct Cfg {
   static constexpr int NUM_W = MODE == GEMM_GATE_UP ? 2 : 1;   // gate tile + up tile
   static constexpr int STAGE_BYTES = NUM_W * W_TILE_BYTES + A_ROWS * TILE_K;
-  static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 10 ? 10 : (200 * 1024) / STAGE_BYTES;
+  // shared-memory budget of the stages: 200 KB, 208 KB where that buys a fourth stage (gate_up with 160-row chunks)
+  static constexpr int STAGE_BUDGET = (MODE == GEMM_GATE_UP && A_ROWS == T_WIDE ? 208 : 200) * 1024;
+  static constexpr int STAGES = STAGE_BUDGET / STAGE_BYTES > 10 ? 10 : STAGE_BUDGET / STAGE_BYTES;
   // tensor memory: columns [0, NUM_W * A_ROWS) hold the fp32 running sums (gate, then up); the rest is
   // cut into partial buffers of A_ROWS columns, one accumulator each (at most 8 are used)
   // (per-channel mode keeps no running sums: a buffer is the int32 accumulator of a whole item)
@@ -101,7 +107,7 @@ template <int MODE, int A_ROWS> struct Smem {
   static constexpr int SC_SLOTS = Cfg<MODE, A_ROWS>::SC_SLOTS;
   float sc[SC_SLOTS][NUM_W][A_ROWS];       // token scale x weight-block scale, ring indexed by the K-block counter
   // gate_up epilogue: |act| maxima per (item parity, lane quarter, token); a stub in the other modes
-  uint32_t amax[MODE == GEMM_GATE_UP ? 2 : 1][4][MODE == GEMM_GATE_UP ? T_MAX : 1];
+  uint32_t amax[MODE == GEMM_GATE_UP ? 2 : 1][4][MODE == GEMM_GATE_UP ? A_ROWS : 1];
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
   uint64_t tmem_full[NBUF];
@@ -163,6 +169,45 @@ __device__ __forceinline__ bool mbar_wait(S &sm, uint64_t *bar, uint32_t parity,
       }
     }
   }
+}
+
+// The same wait and arrive for a barrier given by its shared-memory address.
+__device__ __forceinline__ bool mbar_try_wait_addr(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(200000u)
+      : "memory");
+  return ok != 0;
+}
+template <class S>
+__device__ __forceinline__ bool mbar_wait_addr(S &sm, uint32_t bar, uint32_t parity, int32_t *status, int code) {
+  if (mbar_try_wait_addr(bar, parity)) return true;
+  long long t0 = 0;
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait_addr(bar, parity)) return true;
+    if ((++spins & 255u) == 0u) {
+      if (sm.abort_flag) return false;
+      const long long now = clock64();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > WAIT_LIMIT_CYCLES) {
+        sm.abort_flag = 1;
+        if (status) atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void mbar_arrive_addr(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Two 64-bit words from shared memory (16-byte aligned address in the shared window).
+__device__ __forceinline__ void lds_2x64(uint32_t addr, uint64_t &a, uint64_t &b) {
+  asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "r"(addr));
 }
 
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
@@ -283,6 +328,32 @@ __device__ __forceinline__ uint64_t mul2_rounded(uint64_t a, uint64_t b, uint64_
   uint64_t r;
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(negzero2));
   return r;
+}
+
+// One promotion step on 16 tokens of this thread's output channel: acc += float(raw) * scale product, the
+// product and the sum rounded separately.  `sc_addr` is the shared-memory address of the 16 scale products.
+__device__ __forceinline__ void promote16(const uint32_t (&raw)[16], uint32_t (&accv)[16], uint32_t sc_addr,
+                                          uint64_t neg_magic2, uint64_t negzero2) {
+#pragma unroll
+  for (int j4 = 0; j4 < 4; ++j4) {
+    uint64_t sc01, sc23;               // scale products of four tokens
+    lds_2x64(sc_addr + 16u * j4, sc01, sc23);
+    const uint32_t *r = &raw[j4 * 4];
+    // exact int -> float: add MAGIC_I as an integer, read as fp32, subtract MAGIC_F
+    const uint64_t f01 = add2(pack2(__uint_as_float(r[0] + MAGIC_I), __uint_as_float(r[1] + MAGIC_I)), neg_magic2);
+    const uint64_t f23 = add2(pack2(__uint_as_float(r[2] + MAGIC_I), __uint_as_float(r[3] + MAGIC_I)), neg_magic2);
+    const uint64_t a01 = add2(pack2(__uint_as_float(accv[j4 * 4 + 0]), __uint_as_float(accv[j4 * 4 + 1])),
+                              mul2_rounded(f01, sc01, negzero2));
+    const uint64_t a23 = add2(pack2(__uint_as_float(accv[j4 * 4 + 2]), __uint_as_float(accv[j4 * 4 + 3])),
+                              mul2_rounded(f23, sc23, negzero2));
+    float o0, o1, o2, o3;
+    unpack2(a01, o0, o1);
+    unpack2(a23, o2, o3);
+    accv[j4 * 4 + 0] = __float_as_uint(o0);
+    accv[j4 * 4 + 1] = __float_as_uint(o1);
+    accv[j4 * 4 + 2] = __float_as_uint(o2);
+    accv[j4 * 4 + 3] = __float_as_uint(o3);
+  }
 }
 
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
@@ -461,9 +532,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       }
     } else if (MODE != GEMM_CHANNEL) {
       // ========================= scale producers (2 warps) ====================
-      // Thread g owns tokens g and g + 64 of the chunk.  Token scales and weight-block scales are
+      // Thread g owns tokens g, g + 64 (and g + 128) of the chunk.  Token scales and weight-block scales are
       // read four K blocks at a time and one group ahead, so the loop never waits on memory.
       const int g = tid - 64;            // 0..63
+      constexpr int NU = (A_ROWS + SCALE_THREADS - 1) / SCALE_THREADS < 2 ? 2 : (A_ROWS + SCALE_THREADS - 1) / SCALE_THREADS;
       uint32_t it = 0;
       bool ok = true;
       const bool vec4 = (KB & 3) == 0;
@@ -473,10 +545,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         const int nt = (int)(item % p.n_tiles);
         if (ch.expert < 0) continue;
         const int T = (ch.rows + 15) & ~15;
-        const float *as_ptr[2];
-        bool live[2];
+        const float *as_ptr[NU];
+        bool live[NU];
 #pragma unroll
-        for (int u = 0; u < 2; ++u) {
+        for (int u = 0; u < NU; ++u) {
           const int t = g + u * SCALE_THREADS;
           live[u] = t < ch.rows;
           as_ptr[u] = p.a_scale + (int64_t)(ch.row0 + (live[u] ? t : 0)) * KB;
@@ -485,22 +557,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
 #pragma unroll
         for (int w = 0; w < NUM_W; ++w)
           bs_ptr[w] = p.b_scale + ((int64_t)ch.expert * nblk + nt + (int64_t)w * p.n_tiles) * KB;
-        float4 cur_a[2], nxt_a[2], cur_b[NUM_W], nxt_b[NUM_W];
+        float4 cur_a[NU], nxt_a[NU], cur_b[NUM_W], nxt_b[NUM_W];
         const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
         if (vec4) {
 #pragma unroll
-          for (int u = 0; u < 2; ++u) nxt_a[u] = live[u] ? __ldg(reinterpret_cast<const float4 *>(as_ptr[u])) : zero4;
+          for (int u = 0; u < NU; ++u) nxt_a[u] = live[u] ? __ldg(reinterpret_cast<const float4 *>(as_ptr[u])) : zero4;
 #pragma unroll
           for (int w = 0; w < NUM_W; ++w) nxt_b[w] = __ldg(reinterpret_cast<const float4 *>(bs_ptr[w]));
         }
         for (int kb = 0; kb < KB; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
-          float as_now[2], bs_now[NUM_W];
+          float as_now[NU], bs_now[NUM_W];
           if (vec4) {
             if ((kb & 3) == 0) {
 #pragma unroll
-              for (int u = 0; u < 2; ++u) {
+              for (int u = 0; u < NU; ++u) {
                 cur_a[u] = nxt_a[u];
                 if (kb + 4 < KB && live[u]) nxt_a[u] = __ldg(reinterpret_cast<const float4 *>(as_ptr[u] + kb + 4));
               }
@@ -512,14 +584,14 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
             }
             const int sel = kb & 3;
 #pragma unroll
-            for (int u = 0; u < 2; ++u)
+            for (int u = 0; u < NU; ++u)
               as_now[u] = sel == 0 ? cur_a[u].x : (sel == 1 ? cur_a[u].y : (sel == 2 ? cur_a[u].z : cur_a[u].w));
 #pragma unroll
             for (int w = 0; w < NUM_W; ++w)
               bs_now[w] = sel == 0 ? cur_b[w].x : (sel == 1 ? cur_b[w].y : (sel == 2 ? cur_b[w].z : cur_b[w].w));
           } else {
 #pragma unroll
-            for (int u = 0; u < 2; ++u) as_now[u] = live[u] ? __ldg(as_ptr[u] + kb) : 0.f;
+            for (int u = 0; u < NU; ++u) as_now[u] = live[u] ? __ldg(as_ptr[u] + kb) : 0.f;
 #pragma unroll
             for (int w = 0; w < NUM_W; ++w) bs_now[w] = __ldg(bs_ptr[w] + kb);
           }
@@ -527,7 +599,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.empty[s], ph ^ 1u, p.status, 4))) { ok = false; break; }
           const int slot = it % SC_SLOTS;
 #pragma unroll
-          for (int u = 0; u < 2; ++u) {
+          for (int u = 0; u < NU; ++u) {
             const int t = g + u * SCALE_THREADS;
             if (t < T) {
 #pragma unroll
@@ -547,7 +619,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const uint64_t neg_magic2 = pack2(-MAGIC_F, -MAGIC_F);
     const uint64_t negzero2 = pack2(p.neg_zero, p.neg_zero);
-    uint32_t it = 0, ab = 0, eph = 0, item_par = 0;
+    uint32_t ab = 0, eph = 0, item_par = 0;
+    uint32_t sc_slot = 0, buf = 0, buf_ph = 0;   // block-scaled modes: ring positions of the K loop
     bool ok = true;
     for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
       const Chunk ch = p.chunks[item / p.n_tiles];
@@ -566,15 +639,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         continue;
       }
       // The chunk's T columns (a multiple of 16) are dealt to the four column groups in pieces of 16,
-      // as evenly as that allows; a group owns at most two pieces (32 tokens).
+      // as evenly as that allows; a group owns at most two pieces (32 tokens) of a chunk of up to 128 tokens,
+      // three of a chunk of up to 160, four of a chunk of up to 256.
       const int T = (ch.rows + 15) & ~15;
       const int n_pieces = T >> 4;
       const int my_p = n_pieces / 4 + (cg < (n_pieces & 3) ? 1 : 0);
       const int col_begin = (cg * (n_pieces / 4) + min(cg, n_pieces & 3)) * 16;
 
       // Row id and routed weight of token col_begin + 32 * u + lane, fetched now so that the latency is
-      // hidden behind the K loop; broadcast by shuffle in the epilogue.  (A column group owns at most
-      // 32 tokens of a chunk of up to 128, 64 of a chunk of up to 256.)
+      // hidden behind the K loop; broadcast by shuffle in the epilogue: piece pc of the group is in
+      // register set pc / 2, lanes 16 * (pc & 1) .. + 15.
       constexpr int NPF = A_ROWS > 128 ? 2 : 1;
       int32_t sid_r[NPF];
       float wgt_r[NPF];
@@ -660,51 +734,68 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         tmem_st_wait();
       }
       const int kb_end = MODE == GEMM_CHANNEL ? 0 : KB;   // the block-scaled modes promote once per K block
-      for (int kb = 0; kb < kb_end && ok; ++kb, ++it) {
-        const int slot = it % SC_SLOTS;
+      // Addresses of this item, formed once: the loops below only add constants to them.  Ring positions
+      // (scale slot, partial buffer and its phase) are carried as counters instead of being divided out of
+      // the step numbers.
+      const uint32_t part0 = tmem_base + lane_off + ACC_COLS + (uint32_t)col_begin;
+      const uint32_t accp0 = tmem_base + lane_off + (uint32_t)col_begin;
+      const uint32_t sc0 = smem_u32(&sm.sc[0][0][0]) + (uint32_t)col_begin * 4u;
+      const uint32_t full0 = smem_u32(&sm.tmem_full[0]), empty0 = smem_u32(&sm.tmem_empty[0]);
+      for (int kb = 0; kb < kb_end && ok; ++kb) {
+        const uint32_t sc_step = sc0 + sc_slot * (uint32_t)(NUM_W * A_ROWS * 4);
+        sc_slot = sc_slot + 1 == (uint32_t)SC_SLOTS ? 0u : sc_slot + 1;
 #pragma unroll
-        for (int w = 0; w < NUM_W; ++w, ++ab) {
-          const uint32_t b = ab % NBUF;
-          const uint32_t aph = (ab / NBUF) & 1u;
+        for (int w = 0; w < NUM_W; ++w) {
+          const uint32_t b = buf, aph = buf_ph;
+          buf = buf + 1 == (uint32_t)NBUF ? 0u : buf + 1;
+          buf_ph ^= buf == 0u ? 1u : 0u;
           // The scale products of this step were written to shared memory before the stage's full
           // barrier completed, which the MMA thread observed before it issued the MMAs whose
           // completion this wait observes.  Warp-uniform outcome: the accesses below are warp-collective.
-          if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.tmem_full[b], aph, p.status, 5))) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, mbar_wait_addr(sm, full0 + 8u * b, aph, p.status, 5))) { ok = false; break; }
           tc_fence_after();
-          const uint32_t part = tmem_base + lane_off + ACC_COLS + b * (uint32_t)A_ROWS + (uint32_t)col_begin;
-          const uint32_t accp = tmem_base + lane_off + (uint32_t)(w * A_ROWS + col_begin);
-#pragma unroll 1
-          for (int pc = 0; pc < my_p; ++pc) {
-            uint32_t raw[16], accv[16];
-            tmem_ld16(part + pc * 16, raw);
-            tmem_ld16(accp + pc * 16, accv);
-            tmem_ld_wait();
-            const ulonglong2 *scv = reinterpret_cast<const ulonglong2 *>(&sm.sc[slot][w][col_begin + pc * 16]);
+          uint32_t part = part0 + b * (uint32_t)A_ROWS;
+          uint32_t accp = accp0 + (uint32_t)(w * A_ROWS);
+          uint32_t scp = sc_step + (uint32_t)(w * A_ROWS * 4);
+          if constexpr (NBUF == 1) {
+            // One partial buffer only (gate_up with 160-row chunks): this warp's share of the partial (at most
+            // three pieces) goes to registers first and the buffer is handed back at once, so that the MMAs of
+            // the next half-step run while the sums are updated.
+            constexpr int MAXP = (A_ROWS / 16 + 3) / 4;
+            uint32_t raw[MAXP][16];
 #pragma unroll
-            for (int j4 = 0; j4 < 4; ++j4) {
-              const ulonglong2 sc = scv[j4];     // scale products of four tokens
-              const uint32_t *r = &raw[j4 * 4];
-              // exact int -> float: add MAGIC_I as an integer, read as fp32, subtract MAGIC_F
-              const uint64_t f01 = add2(pack2(__uint_as_float(r[0] + MAGIC_I), __uint_as_float(r[1] + MAGIC_I)), neg_magic2);
-              const uint64_t f23 = add2(pack2(__uint_as_float(r[2] + MAGIC_I), __uint_as_float(r[3] + MAGIC_I)), neg_magic2);
-              const uint64_t a01 = add2(pack2(__uint_as_float(accv[j4 * 4 + 0]), __uint_as_float(accv[j4 * 4 + 1])),
-                                        mul2_rounded(f01, sc.x, negzero2));
-              const uint64_t a23 = add2(pack2(__uint_as_float(accv[j4 * 4 + 2]), __uint_as_float(accv[j4 * 4 + 3])),
-                                        mul2_rounded(f23, sc.y, negzero2));
-              float o0, o1, o2, o3;
-              unpack2(a01, o0, o1);
-              unpack2(a23, o2, o3);
-              accv[j4 * 4 + 0] = __float_as_uint(o0);
-              accv[j4 * 4 + 1] = __float_as_uint(o1);
-              accv[j4 * 4 + 2] = __float_as_uint(o2);
-              accv[j4 * 4 + 3] = __float_as_uint(o3);
+            for (int pc = 0; pc < MAXP; ++pc)
+              if (pc < my_p) tmem_ld16(part + pc * 16, raw[pc]);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_addr(empty0 + 8u * b);
+#pragma unroll
+            for (int pc = 0; pc < MAXP; ++pc) {
+              if (pc < my_p) {
+                uint32_t accv[16];
+                tmem_ld16(accp + pc * 16, accv);
+                tmem_ld_wait();
+                promote16(raw[pc], accv, scp + 64u * pc, neg_magic2, negzero2);
+                tmem_st16(accp + pc * 16, accv);
+              }
             }
-            tmem_st16(accp + pc * 16, accv);
+            tmem_st_wait();
+          } else {
+#pragma unroll 1
+            for (int pc = 0; pc < my_p; ++pc, part += 16, accp += 16, scp += 64) {
+              uint32_t raw[16], accv[16];
+              tmem_ld16(part, raw);
+              tmem_ld16(accp, accv);
+              tmem_ld_wait();
+              promote16(raw, accv, scp, neg_magic2, negzero2);
+              tmem_st16(accp, accv);
+            }
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_addr(empty0 + 8u * b);
           }
-          tmem_st_wait();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&sm.tmem_empty[b]);
         }
       }
       if (!ok) break;
@@ -714,7 +805,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       if constexpr (MODE == GEMM_GATE_UP) {
         const int64_t I = (int64_t)p.n_tiles * TILE_N;
         const uint32_t acc1 = acc0 + (uint32_t)A_ROWS;                              // up sums
-        uint32_t(*amax_tab)[T_MAX] = sm.amax[item_par];
+        uint32_t(*amax_tab)[A_ROWS] = sm.amax[item_par];
         // Pass A, per piece of 16 tokens: act = bf16(bf16(silu(bf16(gate))) * bf16(up)), kept in tensor
         // memory in place of the gate sums; maximum of |act| over this warp's 32 output columns.
 #pragma unroll 1
@@ -728,7 +819,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           for (int j = 0; j < 16; ++j) {
             float gte = __uint_as_float(gv[j]), up = __uint_as_float(uv[j]);
             if (p.weight_mode == LO_WEIGHT_FP32) {
-              const float wgt = __shfl_sync(0xffffffffu, wgt_r[0], pc * 16 + j);
+              const float wgt = __shfl_sync(0xffffffffu, NPF > 1 && (pc >> 1) ? wgt_r[NPF - 1] : wgt_r[0], (pc & 1) * 16 + j);
               gte *= wgt;
               up *= wgt;
             }
@@ -782,8 +873,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
-            const int32_t sid = __shfl_sync(0xffffffffu, sid_r[0], pc * 16 + j);
-            const float wgt = __shfl_sync(0xffffffffu, wgt_r[0], pc * 16 + j);
+            const int32_t sid = __shfl_sync(0xffffffffu, NPF > 1 && (pc >> 1) ? sid_r[NPF - 1] : sid_r[0], (pc & 1) * 16 + j);
+            const float wgt = __shfl_sync(0xffffffffu, NPF > 1 && (pc >> 1) ? wgt_r[NPF - 1] : wgt_r[0], (pc & 1) * 16 + j);
             if (sid >= 0) {
               float v = __uint_as_float(av[j]);
               if (p.weight_mode == LO_WEIGHT_FP32) {
@@ -917,9 +1008,11 @@ int launch_grouped_gemm(GemmMode mode, const GemmArgs &a, cudaStream_t stream) {
   const int cap = a.max_chunk_rows <= 0 ? T_MAX : a.max_chunk_rows;
   if (mode == GEMM_GATE_UP) {
     LO_REQUIRE(a.n_rows_per_expert == 2 * (int64_t)a.n_tiles * TILE_N, "grouped gemm: gate_up needs N = 2*I");
+    LO_REQUIRE(cap <= T_WIDE, "grouped gemm: block-scaled chunks hold at most 160 rows");
     if (cap <= 32) return launch_mode<GEMM_GATE_UP, 32>(a, stream);
     if (cap <= 64) return launch_mode<GEMM_GATE_UP, 64>(a, stream);
-    return launch_mode<GEMM_GATE_UP, 128>(a, stream);
+    if (cap <= 128) return launch_mode<GEMM_GATE_UP, 128>(a, stream);
+    return launch_mode<GEMM_GATE_UP, T_WIDE>(a, stream);
   }
   LO_REQUIRE((int64_t)a.n_tiles * TILE_N >= a.n_rows_per_expert && (int64_t)(a.n_tiles - 1) * TILE_N < a.n_rows_per_expert,
              "grouped gemm: tile count mismatch");
@@ -930,10 +1023,11 @@ int launch_grouped_gemm(GemmMode mode, const GemmArgs &a, cudaStream_t stream) {
     if (cap <= 128) return launch_mode<GEMM_CHANNEL, 128>(a, stream);
     return launch_mode<GEMM_CHANNEL, 256>(a, stream);
   }
-  LO_REQUIRE(cap <= T_MAX, "grouped gemm: block-scaled chunks hold at most 128 rows");
+  LO_REQUIRE(cap <= T_WIDE, "grouped gemm: block-scaled chunks hold at most 160 rows");
   if (cap <= 32) return launch_mode<GEMM_SINGLE, 32>(a, stream);
   if (cap <= 64) return launch_mode<GEMM_SINGLE, 64>(a, stream);
-  return launch_mode<GEMM_SINGLE, 128>(a, stream);
+  if (cap <= 128) return launch_mode<GEMM_SINGLE, 128>(a, stream);
+  return launch_mode<GEMM_SINGLE, T_WIDE>(a, stream);
 }
 
 }  // namespace lo

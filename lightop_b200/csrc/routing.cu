@@ -483,7 +483,7 @@ int launch_align(const void *topk_ids, int ids_dtype, int64_t numel, int num_exp
                  int32_t *expert_ids, int64_t expert_ids_capacity, int32_t *num_tokens_post_pad,
                  Chunk *chunks, int32_t *num_chunks, int64_t chunk_capacity, int32_t *inv_pos,
                  int chunk_max, cudaStream_t stream) {
-  if (chunk_max != 32 && chunk_max != 64 && chunk_max != 256) chunk_max = 128;
+  if (chunk_max != 32 && chunk_max != 64 && chunk_max != 160 && chunk_max != 256) chunk_max = 128;
   LO_REQUIRE(num_experts >= 1 && num_experts <= 1024, "moe_align: num_experts %d outside [1,1024]", num_experts);
   LO_REQUIRE(block_size >= 1, "moe_align: block_size must be positive");
   LO_REQUIRE(numel >= 0 && numel < (1LL << 30), "moe_align: numel out of range");

@@ -141,7 +141,8 @@ def _stage2_from_workspace(lo, M, E, k, H, I, x, w1, w2, w1_s, w2_s, w, ids):
     return out.cpu(), header, xq, xs, sorted_ids, act_q, act_s
 
 
-@pytest.mark.parametrize("name,shape", [("c0", (8, 2, 32, 256, 512)), ("ragged", (16, 4, 77, 512, 256)), ("big_chunk", (2, 1, 300, 256, 256))])
+@pytest.mark.parametrize("name,shape", [("c0", (8, 2, 32, 256, 512)), ("ragged", (16, 4, 77, 512, 256)), ("big_chunk", (2, 1, 300, 256, 256)),
+                                        ("wide_pair", (2, 1, 620, 256, 256)), ("wide_many", (8, 2, 580, 384, 256))])
 def test_fused_intermediates_bit_exact(lo, name, shape):
     E, k, M, H, I = shape
     w1, w2, w1_s, w2_s = synthetic.make_weights(E, H, I, seed=0)
@@ -201,8 +202,9 @@ def test_fused_options(lo, monkeypatch):
     assert out.data_ptr() == xd.data_ptr() and torch.equal(out, base)
 
 
-def test_fused_router_weight_on_input(lo):
-    E, M, H, I = 4, 40, 256, 256
+@pytest.mark.parametrize("E,M", [(4, 40), (2, 300)])     # 10 and 150 rows per expert (narrow and wide chunks)
+def test_fused_router_weight_on_input(lo, E, M):
+    H, I = 256, 256
     w1, w2, w1_s, w2_s = synthetic.make_weights(E, H, I, seed=7)
     x, logits = synthetic.make_activations(M, H, E, seed=8)
     w, ids = O.route_topk_softmax(logits, 1, renormalize=False)
