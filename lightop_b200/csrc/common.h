@@ -57,8 +57,8 @@ int sm_count();
 struct Chunk {
   int32_t expert;
   int32_t row0;   // first position in sorted_ids
-  int32_t rows;   // positions covered (<= 128); validity of each is the sentinel test
-  int32_t pad;    // 1 = the next chunk reads the same weight tiles (keep them in L2), else 0
+  int32_t rows;   // positions covered (<= the chunk size of the table); validity of each is the sentinel test
+  int32_t pad;    // chunks of the same expert that follow (non-zero: the next chunk reads the same weight tiles, keep them in L2)
 };
 
 // Align + (optionally) chunk table, see routing.cu.
@@ -67,6 +67,10 @@ int launch_align(const void *topk_ids, int ids_dtype, int64_t numel, int num_exp
                  int32_t *expert_ids, int64_t expert_ids_capacity, int32_t *num_tokens_post_pad,
                  Chunk *chunks, int32_t *num_chunks, int64_t chunk_capacity, int32_t *inv_pos,
                  int chunk_max, cudaStream_t stream);
+
+// A second chunk table with chunks of up to `chunk_max` rows from the table launch_align wrote, see routing.cu.
+int launch_rechunk(const Chunk *chunks, const int32_t *num_chunks, int chunk_max, Chunk *out, int32_t *num_out,
+                   int64_t capacity, cudaStream_t stream);
 
 // Group quantisation of bf16 rows [M, H] written straight into the expert-sorted layout:
 // the int8 row and its scales of token t go to every position inv_pos[t * topk + j] >= 0.  quant.cu

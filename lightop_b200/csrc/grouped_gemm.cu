@@ -3,16 +3,16 @@
 //
 // Orientation ("swap-AB").  The 128 rows of a weight tile are the M side of the
 // MMA and the tokens of one expert are its N side (N = tokens rounded up to 16,
-// at most 160 with block scales).  A chunk of 1..160 tokens therefore costs one
-// pass over the weight tile with no padding to 128 rows, which is what a
-// weight-streaming (HBM-bound) MoE needs, and the same kernel serves prefill and
-// decode sizes.  In tensor memory a lane is an output column n and a column is a token.
+// at most 128; 160 for the single-matrix block-scaled mode).  A chunk of 1..128
+// tokens therefore costs one pass over the weight tile with no padding to 128
+// rows, which is what a weight-streaming (HBM-bound) MoE needs, and the same
+// kernel serves prefill and decode sizes.  In tensor memory a lane is an output
+// column n and a column is a token.
 //
-// Work item = (chunk of <=160 expert-sorted rows, 128-row output tile; per-channel
-// mode: <=256 rows).  The 160-row instantiation exists for prefill sizes with about
-// 128 rows per expert, where many experts get a few rows more than 128: its three
-// sets of 160 tensor-memory columns (running sums, partials) just fit into the 512,
-// which leaves gate_up a single partial buffer.  Items are ordered chunk-major so that CTAs running side by
+// Work item = (chunk of expert-sorted rows, 128-row output tile).  Chunk widths: gate_up
+// <=128 (two sets of running sums + two partial buffers of 128 columns fill the 512
+// columns of tensor memory), single-matrix block-scaled <=160 (sums + two partials of
+// 160), per-channel <=256.  Items are ordered chunk-major so that CTAs running side by
 // side share the chunk's activation rows, and the chunks of one expert (adjacent
 // in the table) read the same weight tiles at about the same time: weight tiles
 // are loaded with an evict-first L2 policy unless the chunk table says that
@@ -62,7 +62,7 @@ namespace {
 constexpr int TILE_N = 128;      // weight rows per accumulator (MMA M)
 constexpr int TILE_K = 128;      // int8 elements (= bytes) per K block
 constexpr int T_MAX = 128;       // tokens per chunk unless the caller asks for the wide block-scaled chunks
-constexpr int T_WIDE = 160;      // widest block-scaled chunk: 3 x 160 tensor-memory columns (sums + partials) fit into 512
+constexpr int T_WIDE = 160;      // widest single-matrix block-scaled chunk: sums + two partial buffers = 3 x 160 columns
 constexpr int NUM_THREADS = 640;
 constexpr int SCALE_THREADS = 64;
 constexpr int EPI_WARPS = 16;
@@ -83,9 +83,7 @@ constexpr float MAGIC_F = 12582912.0f;
 template <int MODE, int A_ROWS> struct Cfg {
   static constexpr int NUM_W = MODE == GEMM_GATE_UP ? 2 : 1;   // gate tile + up tile
   static constexpr int STAGE_BYTES = NUM_W * W_TILE_BYTES + A_ROWS * TILE_K;
-  // shared-memory budget of the stages: 200 KB, 208 KB where that buys a fourth stage (gate_up with 160-row chunks)
-  static constexpr int STAGE_BUDGET = (MODE == GEMM_GATE_UP && A_ROWS == T_WIDE ? 208 : 200) * 1024;
-  static constexpr int STAGES = STAGE_BUDGET / STAGE_BYTES > 10 ? 10 : STAGE_BUDGET / STAGE_BYTES;
+  static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 10 ? 10 : (200 * 1024) / STAGE_BYTES;
   // tensor memory: columns [0, NUM_W * A_ROWS) hold the fp32 running sums (gate, then up); the rest is
   // cut into partial buffers of A_ROWS columns, one accumulator each (at most 8 are used)
   // (per-channel mode keeps no running sums: a buffer is the int32 accumulator of a whole item)
@@ -330,12 +328,13 @@ __device__ __forceinline__ uint64_t mul2_rounded(uint64_t a, uint64_t b, uint64_
   return r;
 }
 
-// One promotion step on 16 tokens of this thread's output channel: acc += float(raw) * scale product, the
-// product and the sum rounded separately.  `sc_addr` is the shared-memory address of the 16 scale products.
-__device__ __forceinline__ void promote16(const uint32_t (&raw)[16], uint32_t (&accv)[16], uint32_t sc_addr,
-                                          uint64_t neg_magic2, uint64_t negzero2) {
+// One promotion step on N (8 or 16) tokens of this thread's output channel: acc += float(raw) * scale product,
+// the product and the sum rounded separately.  `sc_addr` is the shared-memory address of the N scale products.
+template <int N>
+__device__ __forceinline__ void promote(const uint32_t *raw, uint32_t (&accv)[N], uint32_t sc_addr,
+                                        uint64_t neg_magic2, uint64_t negzero2) {
 #pragma unroll
-  for (int j4 = 0; j4 < 4; ++j4) {
+  for (int j4 = 0; j4 < N / 4; ++j4) {
     uint64_t sc01, sc23;               // scale products of four tokens
     lds_2x64(sc_addr + 16u * j4, sc01, sc23);
     const uint32_t *r = &raw[j4 * 4];
@@ -757,45 +756,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           uint32_t part = part0 + b * (uint32_t)A_ROWS;
           uint32_t accp = accp0 + (uint32_t)(w * A_ROWS);
           uint32_t scp = sc_step + (uint32_t)(w * A_ROWS * 4);
-          if constexpr (NBUF == 1) {
-            // One partial buffer only (gate_up with 160-row chunks): this warp's share of the partial (at most
-            // three pieces) goes to registers first and the buffer is handed back at once, so that the MMAs of
-            // the next half-step run while the sums are updated.
-            constexpr int MAXP = (A_ROWS / 16 + 3) / 4;
-            uint32_t raw[MAXP][16];
-#pragma unroll
-            for (int pc = 0; pc < MAXP; ++pc)
-              if (pc < my_p) tmem_ld16(part + pc * 16, raw[pc]);
-            tmem_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_addr(empty0 + 8u * b);
-#pragma unroll
-            for (int pc = 0; pc < MAXP; ++pc) {
-              if (pc < my_p) {
-                uint32_t accv[16];
-                tmem_ld16(accp + pc * 16, accv);
-                tmem_ld_wait();
-                promote16(raw[pc], accv, scp + 64u * pc, neg_magic2, negzero2);
-                tmem_st16(accp + pc * 16, accv);
-              }
-            }
-            tmem_st_wait();
-          } else {
 #pragma unroll 1
-            for (int pc = 0; pc < my_p; ++pc, part += 16, accp += 16, scp += 64) {
-              uint32_t raw[16], accv[16];
-              tmem_ld16(part, raw);
-              tmem_ld16(accp, accv);
-              tmem_ld_wait();
-              promote16(raw, accv, scp, neg_magic2, negzero2);
-              tmem_st16(accp, accv);
-            }
-            tmem_st_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive_addr(empty0 + 8u * b);
+          for (int pc = 0; pc < my_p; ++pc, part += 16, accp += 16, scp += 64) {
+            uint32_t raw[16], accv[16];
+            tmem_ld16(part, raw);
+            tmem_ld16(accp, accv);
+            tmem_ld_wait();
+            promote<16>(raw, accv, scp, neg_magic2, negzero2);
+            tmem_st16(accp, accv);
           }
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_addr(empty0 + 8u * b);
         }
       }
       if (!ok) break;
@@ -1008,11 +981,11 @@ int launch_grouped_gemm(GemmMode mode, const GemmArgs &a, cudaStream_t stream) {
   const int cap = a.max_chunk_rows <= 0 ? T_MAX : a.max_chunk_rows;
   if (mode == GEMM_GATE_UP) {
     LO_REQUIRE(a.n_rows_per_expert == 2 * (int64_t)a.n_tiles * TILE_N, "grouped gemm: gate_up needs N = 2*I");
-    LO_REQUIRE(cap <= T_WIDE, "grouped gemm: block-scaled chunks hold at most 160 rows");
+    // two sets of running sums and two partial buffers of `cap` columns each: 128 is the widest that fits
+    LO_REQUIRE(cap <= T_MAX, "grouped gemm: gate_up chunks hold at most 128 rows");
     if (cap <= 32) return launch_mode<GEMM_GATE_UP, 32>(a, stream);
     if (cap <= 64) return launch_mode<GEMM_GATE_UP, 64>(a, stream);
-    if (cap <= 128) return launch_mode<GEMM_GATE_UP, 128>(a, stream);
-    return launch_mode<GEMM_GATE_UP, T_WIDE>(a, stream);
+    return launch_mode<GEMM_GATE_UP, 128>(a, stream);
   }
   LO_REQUIRE((int64_t)a.n_tiles * TILE_N >= a.n_rows_per_expert && (int64_t)(a.n_tiles - 1) * TILE_N < a.n_rows_per_expert,
              "grouped gemm: tile count mismatch");
@@ -1023,7 +996,7 @@ int launch_grouped_gemm(GemmMode mode, const GemmArgs &a, cudaStream_t stream) {
     if (cap <= 128) return launch_mode<GEMM_CHANNEL, 128>(a, stream);
     return launch_mode<GEMM_CHANNEL, 256>(a, stream);
   }
-  LO_REQUIRE(cap <= T_WIDE, "grouped gemm: block-scaled chunks hold at most 160 rows");
+  LO_REQUIRE(cap <= T_WIDE, "grouped gemm: block-scaled single-matrix chunks hold at most 160 rows");
   if (cap <= 32) return launch_mode<GEMM_SINGLE, 32>(a, stream);
   if (cap <= 64) return launch_mode<GEMM_SINGLE, 64>(a, stream);
   if (cap <= 128) return launch_mode<GEMM_SINGLE, 128>(a, stream);

@@ -260,7 +260,7 @@ __global__ void __launch_bounds__(ALIGN_WARPS * 32) align_kernel(
           ch.expert = e;
           ch.row0 = seg_off[e] + r;
           ch.rows = c - r < per ? c - r : per;
-          ch.pad = r + per < c ? 1 : 0;      // another chunk of this expert follows: its weight tiles are read again soon
+          ch.pad = (c - r - 1) / per;        // chunks of this expert that follow (their weight tiles are read again soon)
           chunks[ci] = ch;
         }
       }
@@ -428,7 +428,7 @@ __global__ void __launch_bounds__(ALIGN_WARPS * 32) align_cluster_kernel(
           ch.expert = e;
           ch.row0 = seg_off[e] + rr;
           ch.rows = c - rr < per ? c - rr : per;
-          ch.pad = rr + per < c ? 1 : 0;
+          ch.pad = (c - rr - 1) / per;
           chunks[ci] = ch;
         }
       }
@@ -474,6 +474,74 @@ __global__ void chunks_from_blocks_kernel(const int32_t *__restrict__ expert_ids
     chunks[i] = ch;
   }
   if (blockIdx.x == 0 && threadIdx.x == 0) *num_chunks = (int32_t)(total_blocks * per_block);
+}
+
+
+// Second chunk table with another chunk size, derived from the table the align kernel wrote (whose `pad` field
+// counts the chunks of the same expert that follow, so the head chunk of an expert finds the tail directly).
+// One CTA; the new chunks keep the expert order (block-wide exclusive scan of the new chunk counts, 1024 table
+// entries per round).
+__global__ void __launch_bounds__(1024) rechunk_kernel(const Chunk *__restrict__ in, const int32_t *__restrict__ n_in,
+                                                       int chunk_max, Chunk *__restrict__ out,
+                                                       int32_t *__restrict__ n_out, int64_t capacity) {
+  __shared__ int32_t warp_tot[32];
+  __shared__ int32_t round_total;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int n = *n_in;
+  int carry = 0;
+  for (int base = 0; base < n; base += 1024) {
+    const int i = base + tid;
+    int c = 0, per = 0, emit = 0;
+    Chunk head{};
+    if (i < n) {
+      head = in[i];
+      const bool is_head = i == 0 || in[i - 1].pad == 0;
+      if (is_head) {
+        const int t = i + head.pad < n ? i + head.pad : n - 1;
+        const Chunk tail = in[t];
+        c = tail.row0 + tail.rows - head.row0;
+        if (c > 0) {
+          const int nch = (c + chunk_max - 1) / chunk_max;
+          per = (((c + nch - 1) / nch) + 15) / 16 * 16;
+          emit = (c + per - 1) / per;
+        }
+      }
+    }
+    int a = emit;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, a, off);
+      if (lane >= off) a += t;
+    }
+    if (lane == 31) warp_tot[warp] = a;
+    __syncthreads();
+    if (warp == 0) {
+      int t = warp_tot[lane];
+      const int own = t;
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, t, off);
+        if (lane >= off) t += u;
+      }
+      warp_tot[lane] = t - own;
+      if (lane == 31) round_total = t;
+    }
+    __syncthreads();
+    int ci = carry + warp_tot[warp] + a - emit;
+    for (int k = 0, r = 0; k < emit; ++k, r += per, ++ci) {
+      if (ci < capacity) {
+        Chunk ch;
+        ch.expert = head.expert;
+        ch.row0 = head.row0 + r;
+        ch.rows = c - r < per ? c - r : per;
+        ch.pad = emit - 1 - k;
+        out[ci] = ch;
+      }
+    }
+    carry += round_total;
+    __syncthreads();
+  }
+  if (tid == 0) *n_out = carry < capacity ? carry : (int32_t)capacity;
 }
 
 }  // namespace
@@ -590,3 +658,12 @@ extern "C" int lo_moe_align_block_size(const void *topk_ids, int ids_dtype, int6
                           sorted_capacity, expert_ids, expert_ids_capacity, num_tokens_post_pad, nullptr, nullptr,
                           0, nullptr, 128, static_cast<cudaStream_t>(stream));
 }
+
+namespace lo {
+int launch_rechunk(const Chunk *chunks, const int32_t *num_chunks, int chunk_max, Chunk *out, int32_t *num_out,
+                   int64_t capacity, cudaStream_t stream) {
+  rechunk_kernel<<<1, 1024, 0, stream>>>(chunks, num_chunks, chunk_max, out, num_out, capacity);
+  LO_LAUNCH_OK("rechunk_kernel");
+  return LO_OK;
+}
+}  // namespace lo

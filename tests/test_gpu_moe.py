@@ -177,6 +177,17 @@ def test_fused_edge_shapes(lo, E, k, M, H, I):
     assert_out_close(y, y_ref, f"E{E}k{k}M{M}")
 
 
+def test_fused_many_chunks(lo):
+    # more than 1024 entries in the 128-row chunk table: the wide table of the down GEMM is derived in several rounds
+    E, k, M, H, I = 8, 4, 36000, 256, 128
+    w1, w2, w1_s, w2_s = synthetic.make_weights(E, H, I, seed=5)
+    x, logits = synthetic.make_activations(M, H, E, seed=6)
+    w, ids = _route(logits, k)
+    y_ref = O.fused_moe_block_int8(x, w1, w2, w1_s, w2_s, w, ids)
+    y = _run_fused(lo, x, w1, w2, w1_s, w2_s, w, ids)
+    assert_out_close(y, y_ref, "many chunks")
+
+
 def test_fused_options(lo, monkeypatch):
     E, k, M, H, I = 8, 2, 50, 256, 256
     w1, w2, w1_s, w2_s = synthetic.make_weights(E, H, I, seed=5)
