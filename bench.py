@@ -264,9 +264,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                     + rows_routed * (2.0 * 2 * I * 2 + I + 4.0))
     g1_s = stage[2] * 1e-3
     # DRAM traffic of the dominant kernel from the committed ncu captures (profiles/), scaled by the experts hit:
-    # 128 rows per expert -> 1.208 GB read + 4.3 MB written per 32 experts; decode-size chunks -> no re-reads.
+    # 128 rows per expert -> 1.318 GB read + 10.8 MB written per 32 experts; decode-size chunks -> no re-reads.
     if rows_routed / max(experts_hit, 1) > 64:
-        traffic = experts_hit / 32.0 * (1.208155e9 + 4.270e6)
+        traffic = experts_hit / 32.0 * (1.317944e9 + 10.758912e6)
         traffic_src = "profiles/grouped_gemm_prefill_e32_m512.md (ncu dram bytes of the E=32, M=512 case) x experts_hit/32"
     else:
         traffic = experts_hit / 32.0 * (0.945233e9 + 4.008e6)
@@ -309,7 +309,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "e2e": {"value": M / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                 "h2d_bytes_per_step": x_h.numel() * 2 + l_h.numel() * 4, "d2h_bytes_per_step": y_h[0].numel() * 2,
                 "overlap": "copies of neighbouring steps overlap compute (double-buffered, 3 streams)"},
-        "gpu_launches": (7 if channel else 6) * args.steps,
+        # router, align, [wide chunk table of the down GEMM from 64 rows per expert on], quantise, two GEMMs
+        # [+ SiLU/quant kernel in the per-channel mode], top-k sum
+        "gpu_launches": (7 if channel else (7 if M * k // E >= 64 else 6)) * args.steps,
         "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu,
     }
     return line

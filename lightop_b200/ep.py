@@ -286,7 +286,9 @@ def bench_step_setup(args, rank: int, world: int, dev: torch.device):
                 "h2d_bytes_per_step": (x_h.numel() * 2 + l_h.numel() * 4) * world,
                 "d2h_bytes_per_step": y_h.numel() * 2 * world},
         # own kernels per step: the router, then per micro-batch quantise, pack (2), align, permute, two GEMMs, gather ...
-        "gpu_launches": (1 + 10 * (layer.micro_batches if M >= layer.micro_batches * layer.micro_batch_min_tokens else 1))
+        # (+ the wide chunk table of the down GEMM when a rank receives 64 rows per local expert or more)
+        "gpu_launches": (1 + (10 + (1 if rows_recv // max(E_local, 1) >= 64 else 0))
+                         * (layer.micro_batches if M >= layer.micro_batches * layer.micro_batch_min_tokens else 1))
         * args.steps,
         "clocks": clocks,
         "roofline": {"bound": "hbm", "kernel": "grouped_gemm_kernel<gate_up>", "achieved": None, "peak": hbm_peak,
