@@ -1,6 +1,7 @@
 // Shared host-side helpers of the lightop_b200 C-ABI library.
 #pragma once
 #include <cuda_runtime.h>
+#include <utility>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cstdint>
@@ -135,6 +136,30 @@ struct GemmArgs {
 int launch_grouped_gemm(GemmMode mode, const GemmArgs &args, cudaStream_t stream);
 
 #ifdef __CUDACC__
+// Programmatic dependent launch.  A kernel launched with launch_dependent() may start while the kernel before it
+// in the stream is still running; it must call dependency_wait() before it touches anything that kernel writes
+// (the call returns once the earlier grid has completed and its writes are visible; in a launch without the
+// attribute it returns at once).  dependency_release() in the earlier kernel lets the next grid's blocks become
+// resident as soon as every block of this grid has passed the call.
+__device__ __forceinline__ void dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void dependency_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args &&...args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 // Lanes of the warp that hold the same expert as this lane (lanes without an expert match one another).
 // With many steps per warp the mask is built from one ballot per bit of the expert id: the match
 // instruction proper has a throughput of the order of one warp per ~64 cycles and SM here, which made it the

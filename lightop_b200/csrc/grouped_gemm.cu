@@ -426,10 +426,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
                  : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
+  if (tid == 32) {
+    // descriptors into the descriptor cache while the set-up runs
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&w_map)) : "memory");
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&a_maps.m[i])) : "memory");
+  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = sm.tmem_base;
+
+  // Everything above touches this CTA's shared and tensor memory only and may run while the kernel before this
+  // one in the stream is still at work (dependent launch); its outputs (chunk table, activations, scales) are
+  // read from here on.
+  dependency_wait();
+  dependency_release();
 
   const int num_chunks = *p.num_chunks;
   const int64_t num_items = (int64_t)num_chunks * p.n_tiles;
@@ -960,8 +973,8 @@ int launch_mode(const GemmArgs &a, cudaStream_t stream) {
   p.out_by_position = a.out_by_position;
   const int grid = sm_count();
   if (grid <= 0) return fail(LO_ERR_CUDA, "no CUDA device");
-  grouped_gemm_kernel<MODE, A_ROWS><<<grid, NUM_THREADS, smem_bytes, stream>>>(wmap, amaps, p);
-  LO_LAUNCH_OK("grouped_gemm_kernel");
+  LO_CUDA_OK(launch_dependent(grouped_gemm_kernel<MODE, A_ROWS>, dim3(grid), dim3(NUM_THREADS), smem_bytes, stream, wmap,
+                              amaps, p));
   return LO_OK;
 }
 

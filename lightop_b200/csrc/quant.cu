@@ -98,7 +98,7 @@ __global__ void __launch_bounds__(256) group_quant_scatter_kernel(const __nv_bfl
   }
 #pragma unroll
   for (int off = 8; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
-  if (!active) return;
+  if (!active) return;          // (an exited block counts as released for the dependent launch)
   amax = fmaxf(amax, eps_t);
   const float scale = __fdiv_rn(amax, 127.0f);
   uint32_t packed[2] = {0u, 0u};
@@ -110,6 +110,9 @@ __global__ void __launch_bounds__(256) group_quant_scatter_kernel(const __nv_bfl
   }
   const int64_t token = group / groups_per_row;
   const int64_t gi = group % groups_per_row;
+  // everything above reads the caller's activations only; the positions come from the align kernel before this one
+  dependency_wait();
+  dependency_release();
   for (int j = 0; j < topk; ++j) {
     const int32_t pos = inv_pos[token * topk + j];
     if (pos < 0) continue;
@@ -321,10 +324,9 @@ int launch_group_quant_scatter(const void *x, int64_t M, int64_t H, int topk, co
   const int64_t total_threads = M * (H / 128) * 16;
   const int64_t blocks = ceil_div(total_threads, 256);
   LO_REQUIRE(blocks <= 0x7fffffffLL, "group quant: too many groups");
-  group_quant_scatter_kernel<<<(unsigned)blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16 *>(x), M, H / 128, topk,
-                                                                   inv_pos, round_eps_to_dtype(eps, LO_BF16), q_sorted,
-                                                                   s_sorted);
-  LO_LAUNCH_OK("group_quant_scatter_kernel");
+  LO_CUDA_OK(launch_dependent(group_quant_scatter_kernel, dim3((unsigned)blocks), dim3(256), 0, stream,
+                              static_cast<const __nv_bfloat16 *>(x), M, H / 128, topk, inv_pos,
+                              round_eps_to_dtype(eps, LO_BF16), q_sorted, s_sorted));
   return LO_OK;
 }
 

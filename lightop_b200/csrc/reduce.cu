@@ -67,6 +67,7 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(const T *__restrict__ in, 
                                                       const IdT *__restrict__ ids, const int32_t *__restrict__ expert_map) {
   using V = Vec8<T>;
   const int64_t t = blockIdx.y;
+  dependency_wait();            // the rows come from the kernel before this one
   if (num_local_tokens && t >= *num_local_tokens) return;
   const V *in_v = reinterpret_cast<const V *>(in) + t * topk * H8;
   for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < H8; c += (int64_t)gridDim.x * blockDim.x) {
@@ -103,10 +104,9 @@ int launch_sum(const void *in, void *out, const void *bias, int64_t M, int topk,
                cudaStream_t st) {
   const int64_t H8 = H / 8;
   dim3 grid((unsigned)(ceil_div(H8, 256) > 65535 ? 65535 : ceil_div(H8, 256)), (unsigned)M);
-  moe_sum_kernel<T, IdT><<<grid, 256, 0, st>>>(static_cast<const T *>(in), static_cast<T *>(out),
-                                              static_cast<const T *>(bias), M, topk, H8, factor, mask, nlt,
-                                              static_cast<const IdT *>(ids), expert_map);
-  LO_LAUNCH_OK("moe_sum_kernel");
+  LO_CUDA_OK(launch_dependent(moe_sum_kernel<T, IdT>, grid, dim3(256), 0, st, static_cast<const T *>(in),
+                              static_cast<T *>(out), static_cast<const T *>(bias), M, topk, H8, factor, mask, nlt,
+                              static_cast<const IdT *>(ids), expert_map));
   return LO_OK;
 }
 

@@ -155,6 +155,7 @@ __global__ void __launch_bounds__(ALIGN_WARPS * 32) align_kernel(
   int32_t *warp_tot = chunk_off + (E + 1);    // [2][32]
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  dependency_release();      // the next kernel may get its blocks resident; it waits for this grid before reading
 
   // warps that get a segment: with few ids (decode) only the first ones, so that the histogram rows to
   // clear and to scan shrink with the input
@@ -320,6 +321,7 @@ __global__ void __launch_bounds__(ALIGN_WARPS * 32) align_cluster_kernel(
   int32_t *before = cta_cnt + E;              // [E] ids per expert in lower-ranked CTAs
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  dependency_release();
   // sentinel fill: every CTA fills its share
   for (int64_t i = (int64_t)r * blockDim.x + tid; i < sorted_capacity; i += (int64_t)C * blockDim.x) sorted_ids[i] = (int32_t)numel;
   for (int i = tid; i < ALIGN_WARPS * E; i += blockDim.x) hist[i] = 0;
