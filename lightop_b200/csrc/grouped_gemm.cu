@@ -26,7 +26,8 @@
 //   warps 2-3   : scale producers: the token scales of the K block (prefetched four K
 //                 blocks ahead) times the weight-block scale(s) -> per-step table in
 //                 shared memory
-//   warps 4-19  : promotion / epilogue.  The fp32 running sums live in tensor memory next to
+//   warps 4-19  : promotion / epilogue (gate_up: warps 4-11 promote the gate partials, warps 12-19 the up
+//                 partials; all sixteen share the epilogue).  The fp32 running sums live in tensor memory next to
 //                 the int32 partials: per K block a warp loads 16 columns of the partial and of
 //                 the running sum, converts exactly (2^23+2^22 offset trick), multiplies by the
 //                 scale product, adds (packed f32x2; mul and add kept separate: the rounding
@@ -414,7 +415,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
     }
     for (int b = 0; b < NBUF; ++b) {
       mbar_init(&sm.tmem_full[b], 1);
-      mbar_init(&sm.tmem_empty[b], EPI_WARPS);
+      // gate_up: the promotion warps are split into a gate half and an up half, one of them releases a buffer
+      mbar_init(&sm.tmem_empty[b], MODE == GEMM_GATE_UP ? EPI_WARPS / 2 : EPI_WARPS);
     }
     for (int b = 0; b < 4; ++b) mbar_init(&sm.esync[b], 128);
     mbar_init(&sm.isync, EPI_WARPS);
@@ -631,8 +633,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
     const uint64_t neg_magic2 = pack2(-MAGIC_F, -MAGIC_F);
     const uint64_t negzero2 = pack2(p.neg_zero, p.neg_zero);
-    uint32_t ab = 0, eph = 0, item_par = 0;
+    uint32_t ab = 0, eph = 0, item_par = 0, isync_ph = 0;
     uint32_t sc_slot = 0, buf = 0, buf_ph = 0;   // block-scaled modes: ring positions of the K loop
+    // gate_up: warps 0-7 of the sixteen promote the gate partials, warps 8-15 the up partials (the two sets of
+    // running sums are independent), each half as 4 lane quarters x 2 column groups.  While one half works on its
+    // partial the MMAs of the other half-step run, and the two halves are in different phases of their loops
+    // (tensor-memory loads, arithmetic, stores), which overlaps their latencies on the four schedulers.
+    constexpr bool SPLIT = MODE == GEMM_GATE_UP;
+    const int half = pw >> 3;            // SPLIT: 0 = gate, 1 = up
+    const int cgk = (pw >> 2) & 1;       // SPLIT: column group inside the half
+    if (SPLIT) {                         // first unit of this half: partial number `half`
+      buf = (uint32_t)half % (uint32_t)NBUF;
+      buf_ph = ((uint32_t)half / (uint32_t)NBUF) & 1u;
+    }
     bool ok = true;
     for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
       const Chunk ch = p.chunks[item / p.n_tiles];
@@ -657,6 +670,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       const int n_pieces = T >> 4;
       const int my_p = n_pieces / 4 + (cg < (n_pieces & 3) ? 1 : 0);
       const int col_begin = (cg * (n_pieces / 4) + min(cg, n_pieces & 3)) * 16;
+      // columns of this warp in the K loop: the epilogue's split, or (gate_up) the pieces dealt to two groups
+      const int k_p = SPLIT ? n_pieces / 2 + (cgk < (n_pieces & 1) ? 1 : 0) : my_p;
+      const int k_col = SPLIT ? (cgk * (n_pieces / 2) + min(cgk, n_pieces & 1)) * 16 : col_begin;
 
       // Row id and routed weight of token col_begin + 32 * u + lane, fetched now so that the latency is
       // hidden behind the K loop; broadcast by shuffle in the epilogue: piece pc of the group is in
@@ -739,9 +755,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       if (MODE != GEMM_CHANNEL) {
         // the running sums of this item start at zero (all warps have left the previous item's epilogue:
         // see the rendezvous at the end of the item loop), so the K loop below needs no first-block case
-        for (int pc = 0; pc < my_p * NUM_W; ++pc) {
-          const int w = pc / my_p, pq = pc % my_p;
-          tmem_st16_fill(tmem_base + lane_off + (uint32_t)(w * A_ROWS + col_begin + pq * 16), 0u);
+        if (SPLIT) {
+          for (int pc = 0; pc < k_p; ++pc)
+            tmem_st16_fill(tmem_base + lane_off + (uint32_t)(half * A_ROWS + k_col + pc * 16), 0u);
+        } else {
+          for (int pc = 0; pc < my_p; ++pc) tmem_st16_fill(tmem_base + lane_off + (uint32_t)(col_begin + pc * 16), 0u);
         }
         tmem_st_wait();
       }
@@ -749,18 +767,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       // Addresses of this item, formed once: the loops below only add constants to them.  Ring positions
       // (scale slot, partial buffer and its phase) are carried as counters instead of being divided out of
       // the step numbers.
-      const uint32_t part0 = tmem_base + lane_off + ACC_COLS + (uint32_t)col_begin;
-      const uint32_t accp0 = tmem_base + lane_off + (uint32_t)col_begin;
-      const uint32_t sc0 = smem_u32(&sm.sc[0][0][0]) + (uint32_t)col_begin * 4u;
+      const uint32_t part0 = tmem_base + lane_off + ACC_COLS + (uint32_t)k_col;
+      const uint32_t accp0 = tmem_base + lane_off + (uint32_t)k_col;
+      const uint32_t sc0 = smem_u32(&sm.sc[0][0][0]) + (uint32_t)k_col * 4u;
       const uint32_t full0 = smem_u32(&sm.tmem_full[0]), empty0 = smem_u32(&sm.tmem_empty[0]);
       for (int kb = 0; kb < kb_end && ok; ++kb) {
         const uint32_t sc_step = sc0 + sc_slot * (uint32_t)(NUM_W * A_ROWS * 4);
         sc_slot = sc_slot + 1 == (uint32_t)SC_SLOTS ? 0u : sc_slot + 1;
 #pragma unroll
         for (int w = 0; w < NUM_W; ++w) {
+          if (SPLIT && w != half) continue;        // the other half of the warps has this partial
           const uint32_t b = buf, aph = buf_ph;
-          buf = buf + 1 == (uint32_t)NBUF ? 0u : buf + 1;
-          buf_ph ^= buf == 0u ? 1u : 0u;
+          if (SPLIT) {                             // this half takes every second partial
+            buf += 2u;
+            if (buf >= (uint32_t)NBUF) { buf -= (uint32_t)NBUF; buf_ph ^= 1u; }
+          } else {
+            buf = buf + 1 == (uint32_t)NBUF ? 0u : buf + 1;
+            buf_ph ^= buf == 0u ? 1u : 0u;
+          }
           // The scale products of this step were written to shared memory before the stage's full
           // barrier completed, which the MMA thread observed before it issued the MMAs whose
           // completion this wait observes.  Warp-uniform outcome: the accesses below are warp-collective.
@@ -770,7 +794,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           uint32_t accp = accp0 + (uint32_t)(w * A_ROWS);
           uint32_t scp = sc_step + (uint32_t)(w * A_ROWS * 4);
 #pragma unroll 1
-          for (int pc = 0; pc < my_p; ++pc, part += 16, accp += 16, scp += 64) {
+          for (int pc = 0; pc < k_p; ++pc, part += 16, accp += 16, scp += 64) {
             uint32_t raw[16], accv[16];
             tmem_ld16(part, raw);
             tmem_ld16(accp, accv);
@@ -785,6 +809,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         }
       }
       if (!ok) break;
+      if (SPLIT) {
+        // the epilogue reads gate and up sums of columns dealt differently from the K loop: every promotion warp
+        // has to be through its last K block before any of them reads
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.isync);
+        if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.isync, isync_ph, p.status, 12))) { ok = false; break; }
+        isync_ph ^= 1u;
+        tc_fence_after();
+      }
 
       // ------------------------------ epilogue -------------------------------
       const uint32_t acc0 = tmem_base + lane_off + (uint32_t)col_begin;            // gate (or the only) sums
@@ -881,7 +915,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       if (MODE != GEMM_CHANNEL) {
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.isync);
-        if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.isync, item_par, p.status, 11))) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.isync, isync_ph, p.status, 11))) { ok = false; break; }
+        isync_ph ^= 1u;
         item_par ^= 1u;
       }
     }
