@@ -264,9 +264,9 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                     + rows_routed * (2.0 * 2 * I * 2 + I + 4.0))
     g1_s = stage[2] * 1e-3
     # DRAM traffic of the dominant kernel from the committed ncu captures (profiles/), scaled by the experts hit:
-    # 128 rows per expert -> 1.318 GB read + 10.8 MB written per 32 experts; decode-size chunks -> no re-reads.
+    # 128 rows per expert -> 1.316 GB read + 10.4 MB written per 32 experts; decode-size chunks -> no re-reads.
     if rows_routed / max(experts_hit, 1) > 64:
-        traffic = experts_hit / 32.0 * (1.317944e9 + 10.758912e6)
+        traffic = experts_hit / 32.0 * (1.316404e9 + 10.436608e6)
         traffic_src = "profiles/grouped_gemm_prefill_e32_m512.md (ncu dram bytes of the E=32, M=512 case) x experts_hit/32"
     else:
         traffic = experts_hit / 32.0 * (0.945233e9 + 4.008e6)
