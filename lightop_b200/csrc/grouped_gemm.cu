@@ -66,17 +66,10 @@ constexpr int T_MAX = 128;       // tokens per chunk unless the caller asks for 
 constexpr int T_WIDE = 160;      // widest single-matrix block-scaled chunk: sums + two partial buffers = 3 x 160 columns
 constexpr int NUM_THREADS = 640;
 constexpr int SCALE_THREADS = 64;
+constexpr int FIRST_EPI_WARP = 4;
 constexpr int EPI_WARPS = 16;
 constexpr int W_TILE_BYTES = TILE_N * TILE_K;   // 16 KiB
 constexpr uint32_t TMEM_COLS = 512;
-// 2^23 + 2^22: adding it to an int32 of magnitude < 2^22 and reading the bits as fp32 gives
-// 12582912 + value exactly, so (that - 12582912.0f) is the exact int->float conversion
-// (|128-long int8 dot| <= 128 * 127 * 127 < 2^21).  The integer addition runs on the integer pipe,
-// which the promotion loop leaves idle; the conversion instruction proper is an order of magnitude
-// slower.  (Letting the tensor core add the offset, by keeping free partial buffers filled with it,
-// was measured slower: the refill is one more tensor-memory store per piece.)
-constexpr uint32_t MAGIC_I = 0x4B400000u;
-constexpr float MAGIC_F = 12582912.0f;
 
 // A_ROWS is the largest chunk (token count) the instantiation accepts: with few tokens per call no
 // expert can receive more than that many rows, the activation tile of a stage shrinks and more
@@ -85,16 +78,16 @@ template <int MODE, int A_ROWS> struct Cfg {
   static constexpr int NUM_W = MODE == GEMM_GATE_UP ? 2 : 1;   // gate tile + up tile
   static constexpr int STAGE_BYTES = NUM_W * W_TILE_BYTES + A_ROWS * TILE_K;
   static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 10 ? 10 : (200 * 1024) / STAGE_BYTES;
-  // tensor memory: columns [0, NUM_W * A_ROWS) hold the fp32 running sums (gate, then up); the rest is
-  // cut into partial buffers of A_ROWS columns, one accumulator each (at most 8 are used)
-  // (per-channel mode keeps no running sums: a buffer is the int32 accumulator of a whole item)
-  static constexpr int ACC_COLS = MODE == GEMM_CHANNEL ? 0 : NUM_W * A_ROWS;
-  static constexpr int NBUF = ((int)TMEM_COLS - ACC_COLS) / A_ROWS > 8 ? 8 : ((int)TMEM_COLS - ACC_COLS) / A_ROWS;
+  // tensor memory is cut into partial buffers of A_ROWS columns, one int32 accumulator each (at most 8 are used):
+  // the partial of one 128-wide K block in the block-scaled modes (the fp32 running sums live in the registers of
+  // the promotion warps), the accumulator of a whole item in the per-channel mode
+  static constexpr int NBUF = (int)TMEM_COLS / A_ROWS > 8 ? 8 : (int)TMEM_COLS / A_ROWS;
   // Ring of scale-product tables.  A slot written for K-block step i was last read at step
   // i - SC_SLOTS; the producer of step i has seen the MMAs of step i - STAGES complete, which were
   // issued after the promotion of step i - STAGES - NBUF finished, so STAGES + NBUF slots suffice.
   static constexpr int SC_SLOTS = MODE == GEMM_CHANNEL ? 1 : STAGES + NBUF;
 };
+
 
 template <int MODE, int A_ROWS> struct Smem {
   static constexpr int STAGES = Cfg<MODE, A_ROWS>::STAGES;
@@ -112,7 +105,6 @@ template <int MODE, int A_ROWS> struct Smem {
   uint64_t tmem_full[NBUF];
   uint64_t tmem_empty[NBUF];
   uint64_t esync[4];                       // rendezvous of the 128 epilogue threads of a column group
-  uint64_t isync;                          // rendezvous of all promotion warps between two items
   uint32_t tmem_base;
   volatile int abort_flag;
 };
@@ -285,25 +277,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-// Store 16 consecutive tensor-memory columns of this thread's lane.
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-      : "memory");
-}
-// Store one value to 16 consecutive tensor-memory columns of this thread's lane.
-__device__ __forceinline__ void tmem_st16_fill(uint32_t taddr, uint32_t v) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-      "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
-      ::"r"(taddr), "r"(v)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
 // Packed fp32 pair arithmetic (two IEEE round-to-nearest operations per instruction).
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
   uint64_t r;
@@ -313,46 +286,27 @@ __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
 __device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) {
   asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
 }
-__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
   uint64_t r;
-  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-// Rounded product as ONE instruction: fma(a, b, -0.0) == round(a * b).  A separate mul.rn.f32x2
-// followed by add.rn.f32x2 was observed to be contracted into a fused multiply-add by the
-// assembler (results differed from the scalar mul-then-add sequence in the last bit); an fma is
-// never merged with a following add.  `negzero2` comes from a kernel parameter so that the
-// addend is not a compile-time constant.
-__device__ __forceinline__ uint64_t mul2_rounded(uint64_t a, uint64_t b, uint64_t negzero2) {
-  uint64_t r;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(negzero2));
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
   return r;
 }
 
-// One promotion step on N (8 or 16) tokens of this thread's output channel: acc += float(raw) * scale product,
-// the product and the sum rounded separately.  `sc_addr` is the shared-memory address of the N scale products.
+// One promotion step on N (8 or 16) tokens of this thread's output channel: acc = fma(float(raw), scale product, acc).
+// The 128-long int8 dot is below 2^21 in magnitude, so the conversion is exact; one rounding per K block.
+// `sc_addr` is the shared-memory address of the N scale products.
 template <int N>
-__device__ __forceinline__ void promote(const uint32_t *raw, uint32_t (&accv)[N], uint32_t sc_addr,
-                                        uint64_t neg_magic2, uint64_t negzero2) {
+__device__ __forceinline__ void promote(const uint32_t (&raw)[N], float *acc, uint32_t sc_addr) {
 #pragma unroll
   for (int j4 = 0; j4 < N / 4; ++j4) {
     uint64_t sc01, sc23;               // scale products of four tokens
     lds_2x64(sc_addr + 16u * j4, sc01, sc23);
-    const uint32_t *r = &raw[j4 * 4];
-    // exact int -> float: add MAGIC_I as an integer, read as fp32, subtract MAGIC_F
-    const uint64_t f01 = add2(pack2(__uint_as_float(r[0] + MAGIC_I), __uint_as_float(r[1] + MAGIC_I)), neg_magic2);
-    const uint64_t f23 = add2(pack2(__uint_as_float(r[2] + MAGIC_I), __uint_as_float(r[3] + MAGIC_I)), neg_magic2);
-    const uint64_t a01 = add2(pack2(__uint_as_float(accv[j4 * 4 + 0]), __uint_as_float(accv[j4 * 4 + 1])),
-                              mul2_rounded(f01, sc01, negzero2));
-    const uint64_t a23 = add2(pack2(__uint_as_float(accv[j4 * 4 + 2]), __uint_as_float(accv[j4 * 4 + 3])),
-                              mul2_rounded(f23, sc23, negzero2));
-    float o0, o1, o2, o3;
-    unpack2(a01, o0, o1);
-    unpack2(a23, o2, o3);
-    accv[j4 * 4 + 0] = __float_as_uint(o0);
-    accv[j4 * 4 + 1] = __float_as_uint(o1);
-    accv[j4 * 4 + 2] = __float_as_uint(o2);
-    accv[j4 * 4 + 3] = __float_as_uint(o3);
+    const uint64_t f01 = pack2(__int2float_rn((int32_t)raw[j4 * 4 + 0]), __int2float_rn((int32_t)raw[j4 * 4 + 1]));
+    const uint64_t f23 = pack2(__int2float_rn((int32_t)raw[j4 * 4 + 2]), __int2float_rn((int32_t)raw[j4 * 4 + 3]));
+    const uint64_t a01 = fma2(f01, sc01, pack2(acc[j4 * 4 + 0], acc[j4 * 4 + 1]));
+    const uint64_t a23 = fma2(f23, sc23, pack2(acc[j4 * 4 + 2], acc[j4 * 4 + 3]));
+    unpack2(a01, acc[j4 * 4 + 0], acc[j4 * 4 + 1]);
+    unpack2(a23, acc[j4 * 4 + 2], acc[j4 * 4 + 3]);
   }
 }
 
@@ -376,7 +330,6 @@ struct KParams {
   int weight_mode;
   float act_eps;
   int32_t *status;
-  float neg_zero;           // -0.0f, see mul2_rounded
   int out_by_position;      // bf16 output row = sorted position instead of the sorted id
 };
 
@@ -396,7 +349,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   constexpr int STAGES = SM::STAGES;
   constexpr int NUM_W = SM::NUM_W;
   constexpr int NBUF = SM::NBUF;
-  constexpr uint32_t ACC_COLS = Cfg<MODE, A_ROWS>::ACC_COLS;
   extern __shared__ uint8_t smem_raw[];
   SM &sm = *reinterpret_cast<SM *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -415,11 +367,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
     }
     for (int b = 0; b < NBUF; ++b) {
       mbar_init(&sm.tmem_full[b], 1);
-      // gate_up: the promotion warps are split into a gate half and an up half, one of them releases a buffer
-      mbar_init(&sm.tmem_empty[b], MODE == GEMM_GATE_UP ? EPI_WARPS / 2 : EPI_WARPS);
+      mbar_init(&sm.tmem_empty[b], EPI_WARPS);
     }
     for (int b = 0; b < 4; ++b) mbar_init(&sm.esync[b], 128);
-    mbar_init(&sm.isync, EPI_WARPS);
     sm.abort_flag = 0;
     fence_barrier_init();
   }
@@ -450,7 +400,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   const int64_t num_items = (int64_t)num_chunks * p.n_tiles;
   const int KB = p.KB;
 
-  if (warp < 4) {
+  if (warp < FIRST_EPI_WARP) {
     if (warp == 0) {
       // ============ TMA producer: weight tiles + the chunk's token rows ============
       if (lane == 0) {
@@ -532,7 +482,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
                 if (!mbar_wait(sm, &sm.tmem_empty[b], aph ^ 1u, p.status, 2)) { ok = false; break; }
                 tc_fence_after();
                 const uint64_t adesc = make_smem_desc(smem_u32(sm.w[s][w]));
-                const uint32_t d = tmem_base + ACC_COLS + b * (uint32_t)A_ROWS;
+                const uint32_t d = tmem_base + b * (uint32_t)A_ROWS;
 #pragma unroll
                 for (int k4 = 0; k4 < TILE_K / 32; ++k4)
                   umma_i8(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, k4 != 0 ? 1u : 0u);
@@ -627,25 +577,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
     }
   } else {
     // ====================== promotion + epilogue (16 warps) ====================
-    const int pw = warp - 4;             // 0..15
+    const int pw = warp - FIRST_EPI_WARP;   // 0..15; every group of four consecutive warps covers the four lane quarters
     const int q = warp & 3;              // lane quarter of tensor memory this warp may access
     const int cg = pw >> 2;              // column group: which share of the chunk's tokens
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
-    const uint64_t neg_magic2 = pack2(-MAGIC_F, -MAGIC_F);
-    const uint64_t negzero2 = pack2(p.neg_zero, p.neg_zero);
-    uint32_t ab = 0, eph = 0, item_par = 0, isync_ph = 0;
+    uint32_t ab = 0, eph = 0, item_par = 0;
     uint32_t sc_slot = 0, buf = 0, buf_ph = 0;   // block-scaled modes: ring positions of the K loop
-    // gate_up: warps 0-7 of the sixteen promote the gate partials, warps 8-15 the up partials (the two sets of
-    // running sums are independent), each half as 4 lane quarters x 2 column groups.  While one half works on its
-    // partial the MMAs of the other half-step run, and the two halves are in different phases of their loops
-    // (tensor-memory loads, arithmetic, stores), which overlaps their latencies on the four schedulers.
-    constexpr bool SPLIT = MODE == GEMM_GATE_UP;
-    const int half = pw >> 3;            // SPLIT: 0 = gate, 1 = up
-    const int cgk = (pw >> 2) & 1;       // SPLIT: column group inside the half
-    if (SPLIT) {                         // first unit of this half: partial number `half`
-      buf = (uint32_t)half % (uint32_t)NBUF;
-      buf_ph = ((uint32_t)half / (uint32_t)NBUF) & 1u;
-    }
     bool ok = true;
     for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
       const Chunk ch = p.chunks[item / p.n_tiles];
@@ -670,9 +607,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       const int n_pieces = T >> 4;
       const int my_p = n_pieces / 4 + (cg < (n_pieces & 3) ? 1 : 0);
       const int col_begin = (cg * (n_pieces / 4) + min(cg, n_pieces & 3)) * 16;
-      // columns of this warp in the K loop: the epilogue's split, or (gate_up) the pieces dealt to two groups
-      const int k_p = SPLIT ? n_pieces / 2 + (cgk < (n_pieces & 1) ? 1 : 0) : my_p;
-      const int k_col = SPLIT ? (cgk * (n_pieces / 2) + min(cgk, n_pieces & 1)) * 16 : col_begin;
 
       // Row id and routed weight of token col_begin + 32 * u + lane, fetched now so that the latency is
       // hidden behind the K loop; broadcast by shuffle in the epilogue: piece pc of the group is in
@@ -750,174 +684,147 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           __syncwarp();
           if (lane == 0) mbar_arrive(&sm.tmem_empty[b]);
         }
-      }
-
-      if (MODE != GEMM_CHANNEL) {
-        // the running sums of this item start at zero (all warps have left the previous item's epilogue:
-        // see the rendezvous at the end of the item loop), so the K loop below needs no first-block case
-        if (SPLIT) {
-          for (int pc = 0; pc < k_p; ++pc)
-            tmem_st16_fill(tmem_base + lane_off + (uint32_t)(half * A_ROWS + k_col + pc * 16), 0u);
-        } else {
-          for (int pc = 0; pc < my_p; ++pc) tmem_st16_fill(tmem_base + lane_off + (uint32_t)(col_begin + pc * 16), 0u);
-        }
-        tmem_st_wait();
-      }
-      const int kb_end = MODE == GEMM_CHANNEL ? 0 : KB;   // the block-scaled modes promote once per K block
-      // Addresses of this item, formed once: the loops below only add constants to them.  Ring positions
-      // (scale slot, partial buffer and its phase) are carried as counters instead of being divided out of
-      // the step numbers.
-      const uint32_t part0 = tmem_base + lane_off + ACC_COLS + (uint32_t)k_col;
-      const uint32_t accp0 = tmem_base + lane_off + (uint32_t)k_col;
-      const uint32_t sc0 = smem_u32(&sm.sc[0][0][0]) + (uint32_t)k_col * 4u;
-      const uint32_t full0 = smem_u32(&sm.tmem_full[0]), empty0 = smem_u32(&sm.tmem_empty[0]);
-      for (int kb = 0; kb < kb_end && ok; ++kb) {
-        const uint32_t sc_step = sc0 + sc_slot * (uint32_t)(NUM_W * A_ROWS * 4);
-        sc_slot = sc_slot + 1 == (uint32_t)SC_SLOTS ? 0u : sc_slot + 1;
+      } else {
+        // ---------------- block-scaled modes: promotion once per K block, sums in registers ----------------
+        // This warp owns the columns [col_begin, col_begin + 16 * my_p) of its 32 lanes, for the gate and the up
+        // tile alike.  Their fp32 running sums stay in registers over the whole K loop (NP pieces of 16 columns at
+        // most; the piece loop is unrolled and a piece beyond the chunk's width is skipped), so tensor memory holds
+        // nothing but partial buffers and a K block costs one tensor-memory load per piece.
+        constexpr int NP = (A_ROWS / 16 + 3) / 4;
+        float acc[NUM_W][NP][16];
 #pragma unroll
-        for (int w = 0; w < NUM_W; ++w) {
-          if (SPLIT && w != half) continue;        // the other half of the warps has this partial
-          const uint32_t b = buf, aph = buf_ph;
-          if (SPLIT) {                             // this half takes every second partial
-            buf += 2u;
-            if (buf >= (uint32_t)NBUF) { buf -= (uint32_t)NBUF; buf_ph ^= 1u; }
-          } else {
+        for (int w = 0; w < NUM_W; ++w)
+#pragma unroll
+          for (int pc = 0; pc < NP; ++pc)
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[w][pc][j] = 0.f;
+        // Addresses of this item, formed once: the loops below only add constants to them.  Ring positions
+        // (scale slot, partial buffer and its phase) are carried as counters instead of being divided out of
+        // the step numbers.
+        const uint32_t part0 = tmem_base + lane_off + (uint32_t)col_begin;
+        const uint32_t sc0 = smem_u32(&sm.sc[0][0][0]) + (uint32_t)col_begin * 4u;
+        const uint32_t full0 = smem_u32(&sm.tmem_full[0]), empty0 = smem_u32(&sm.tmem_empty[0]);
+#pragma unroll 1
+        for (int kb = 0; kb < KB; ++kb) {
+          const uint32_t sc_step = sc0 + sc_slot * (uint32_t)(NUM_W * A_ROWS * 4);
+          sc_slot = sc_slot + 1 == (uint32_t)SC_SLOTS ? 0u : sc_slot + 1;
+#pragma unroll
+          for (int w = 0; w < NUM_W; ++w) {
+            const uint32_t b = buf, aph = buf_ph;
             buf = buf + 1 == (uint32_t)NBUF ? 0u : buf + 1;
             buf_ph ^= buf == 0u ? 1u : 0u;
-          }
-          // The scale products of this step were written to shared memory before the stage's full
-          // barrier completed, which the MMA thread observed before it issued the MMAs whose
-          // completion this wait observes.  Warp-uniform outcome: the accesses below are warp-collective.
-          if (!__all_sync(0xffffffffu, mbar_wait_addr(sm, full0 + 8u * b, aph, p.status, 5))) { ok = false; break; }
-          tc_fence_after();
-          uint32_t part = part0 + b * (uint32_t)A_ROWS;
-          uint32_t accp = accp0 + (uint32_t)(w * A_ROWS);
-          uint32_t scp = sc_step + (uint32_t)(w * A_ROWS * 4);
-#pragma unroll 1
-          for (int pc = 0; pc < k_p; ++pc, part += 16, accp += 16, scp += 64) {
-            uint32_t raw[16], accv[16];
-            tmem_ld16(part, raw);
-            tmem_ld16(accp, accv);
-            tmem_ld_wait();
-            promote<16>(raw, accv, scp, neg_magic2, negzero2);
-            tmem_st16(accp, accv);
-          }
-          tmem_st_wait();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_addr(empty0 + 8u * b);
-        }
-      }
-      if (!ok) break;
-      if (SPLIT) {
-        // the epilogue reads gate and up sums of columns dealt differently from the K loop: every promotion warp
-        // has to be through its last K block before any of them reads
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.isync);
-        if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.isync, isync_ph, p.status, 12))) { ok = false; break; }
-        isync_ph ^= 1u;
-        tc_fence_after();
-      }
-
-      // ------------------------------ epilogue -------------------------------
-      const uint32_t acc0 = tmem_base + lane_off + (uint32_t)col_begin;            // gate (or the only) sums
-      if constexpr (MODE == GEMM_GATE_UP) {
-        const int64_t I = (int64_t)p.n_tiles * TILE_N;
-        const uint32_t acc1 = acc0 + (uint32_t)A_ROWS;                              // up sums
-        uint32_t(*amax_tab)[A_ROWS] = sm.amax[item_par];
-        // Pass A, per piece of 16 tokens: act = bf16(bf16(silu(bf16(gate))) * bf16(up)), kept in tensor
-        // memory in place of the gate sums; maximum of |act| over this warp's 32 output columns.
-#pragma unroll 1
-        for (int pc = 0; pc < my_p; ++pc) {
-          uint32_t gv[16], uv[16];
-          tmem_ld16(acc0 + pc * 16, gv);
-          tmem_ld16(acc1 + pc * 16, uv);
-          tmem_ld_wait();
-          uint32_t own = 0u;
+            // The scale products of this step were written to shared memory before the stage's full
+            // barrier completed, which the MMA thread observed before it issued the MMAs whose
+            // completion this wait observes.  Warp-uniform outcome: the accesses below are warp-collective.
+            if (!__all_sync(0xffffffffu, mbar_wait_addr(sm, full0 + 8u * b, aph, p.status, 5))) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t part = part0 + b * (uint32_t)A_ROWS;
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            float gte = __uint_as_float(gv[j]), up = __uint_as_float(uv[j]);
-            if (p.weight_mode == LO_WEIGHT_FP32) {
-              const float wgt = __shfl_sync(0xffffffffu, NPF > 1 && (pc >> 1) ? wgt_r[NPF - 1] : wgt_r[0], (pc & 1) * 16 + j);
-              gte *= wgt;
-              up *= wgt;
-            }
-            gte = bf16_round(gte);
-            up = bf16_round(up);
-            const float sl = bf16_round(__fdiv_rn(gte, 1.0f + expf(-gte)));
-            const float a = bf16_round(sl * up);
-            gv[j] = __float_as_uint(a);
-            const uint32_t m = __reduce_max_sync(0xffffffffu, __float_as_uint(a) & 0x7fffffffu);
-            if (j == lane) own = m;
-          }
-          tmem_st16(acc0 + pc * 16, gv);
-          if (lane < 16) amax_tab[q][col_begin + pc * 16 + lane] = own;
-        }
-        tmem_st_wait();
-        // the four warps of this column group exchange their maxima (the table alternates between two
-        // copies from item to item, so one rendezvous per item is enough)
-        mbar_arrive(&sm.esync[cg]);
-        if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.esync[cg], eph, p.status, 9))) { ok = false; break; }
-        eph ^= 1u;
-        // Pass B: lane j (< 16) forms the group scale of token j of the piece, amax / 127; every thread then
-        // quantises its column of the 16 tokens: q = trunc(clamp(act / scale)).
-#pragma unroll 1
-        for (int pc = 0; pc < my_p; ++pc) {
-          uint32_t av[16];
-          tmem_ld16(acc0 + pc * 16, av);
-          float scale_r = 1.f;
-          const int t_own = col_begin + pc * 16 + (lane & 15);
-          {
-            const uint32_t m = max(max(amax_tab[0][t_own], amax_tab[1][t_own]), max(amax_tab[2][t_own], amax_tab[3][t_own]));
-            scale_r = __fdiv_rn(fmaxf(__uint_as_float(m), p.act_eps), 127.0f);
-            if (q == 0 && lane < 16 && t_own < ch.rows) p.act_s[((int64_t)ch.row0 + t_own) * p.n_tiles + nt] = scale_r;
-          }
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int t = col_begin + pc * 16 + j;
-            const float scale = __shfl_sync(0xffffffffu, scale_r, j);
-            if (t < ch.rows) {
-              float r = __fdiv_rn(__uint_as_float(av[j]), scale);
-              r = fminf(fmaxf(r, -128.0f), 127.0f);
-              p.act_q[((int64_t)ch.row0 + t) * I + (int64_t)nt * TILE_N + n_local] = (int8_t)__float2int_rz(r);
-            }
-          }
-        }
-      } else if (MODE == GEMM_SINGLE) {
-#pragma unroll 1
-        for (int pc = 0; pc < my_p; ++pc) {
-          uint32_t av[16];
-          tmem_ld16(acc0 + pc * 16, av);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int32_t sid = __shfl_sync(0xffffffffu, NPF > 1 && (pc >> 1) ? sid_r[NPF - 1] : sid_r[0], (pc & 1) * 16 + j);
-            const float wgt = __shfl_sync(0xffffffffu, NPF > 1 && (pc >> 1) ? wgt_r[NPF - 1] : wgt_r[0], (pc & 1) * 16 + j);
-            if (sid >= 0) {
-              float v = __uint_as_float(av[j]);
-              if (p.weight_mode == LO_WEIGHT_FP32) {
-                v = v * wgt;
-              } else if (p.weight_mode == LO_WEIGHT_BF16_PRODUCT) {
-                v = bf16_round(v) * bf16_round(wgt);
+            for (int pc = 0; pc < NP; ++pc) {
+              if (pc < my_p) {
+                uint32_t raw[16];
+                tmem_ld16(part + pc * 16, raw);
+                tmem_ld_wait();
+                promote<16>(raw, &acc[w][pc][0], sc_step + (uint32_t)(w * A_ROWS * 4 + pc * 64));
               }
-              if ((int64_t)nt * TILE_N + n_local < p.n_store)
-                p.C[(int64_t)sid * p.n_store + (int64_t)nt * TILE_N + n_local] = __float2bfloat16_rn(v);
             }
+            // every load of the partial has completed: hand the buffer back to the MMA warp
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_addr(empty0 + 8u * b);
+          }
+          if (!ok) break;
+        }
+        if (!ok) break;
+
+        // ------------------------------ epilogue -------------------------------
+        // One rolled loop over the warp's pieces: the body always works on piece 0 of the register sums and the
+        // remaining pieces move down one place afterwards (registers cannot be indexed by a loop counter, and an
+        // epilogue unrolled over the pieces would be fetched cold once per item).
+        if constexpr (MODE == GEMM_GATE_UP) {
+          const int64_t I = (int64_t)p.n_tiles * TILE_N;
+          uint32_t(*amax_tab)[A_ROWS] = sm.amax[item_par];
+#pragma unroll 1
+          for (int pc = 0; pc < my_p; ++pc) {
+            float *gv = &acc[0][0][0], *uv = &acc[NUM_W - 1][0][0];
+            // Pass A: act = bf16(bf16(silu(bf16(gate))) * bf16(up)) in place of the gate sums; maximum of |act|
+            // over this warp's 32 output columns, lane j keeps the one of token j.
+            uint32_t own = 0u;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float gte = gv[j], up = uv[j];
+              if (p.weight_mode == LO_WEIGHT_FP32) {
+                const float wgt = __shfl_sync(0xffffffffu, NPF > 1 && (pc >> 1) ? wgt_r[NPF - 1] : wgt_r[0], (pc & 1) * 16 + j);
+                gte *= wgt;
+                up *= wgt;
+              }
+              gte = bf16_round(gte);
+              up = bf16_round(up);
+              const float sl = bf16_round(__fdiv_rn(gte, 1.0f + expf(-gte)));
+              const float a = bf16_round(sl * up);
+              gv[j] = a;
+              const uint32_t m = __reduce_max_sync(0xffffffffu, __float_as_uint(a) & 0x7fffffffu);
+              if (j == lane) own = m;
+            }
+            if (lane < 16) amax_tab[q][col_begin + pc * 16 + lane] = own;
+            // the four warps of this column group exchange their maxima (the table alternates between two
+            // copies from item to item; the pieces of one item use different entries)
+            mbar_arrive(&sm.esync[cg]);
+            if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.esync[cg], eph, p.status, 9))) { ok = false; break; }
+            eph ^= 1u;
+            // Pass B: lane j (< 16) forms the group scale of token j of the piece, amax / 127; every thread then
+            // quantises its column of the 16 tokens: q = trunc(clamp(act / scale)).
+            float scale_r = 1.f;
+            const int t_own = col_begin + pc * 16 + (lane & 15);
+            {
+              const uint32_t m = max(max(amax_tab[0][t_own], amax_tab[1][t_own]), max(amax_tab[2][t_own], amax_tab[3][t_own]));
+              scale_r = __fdiv_rn(fmaxf(__uint_as_float(m), p.act_eps), 127.0f);
+              if (q == 0 && lane < 16 && t_own < ch.rows) p.act_s[((int64_t)ch.row0 + t_own) * p.n_tiles + nt] = scale_r;
+            }
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int t = col_begin + pc * 16 + j;
+              const float scale = __shfl_sync(0xffffffffu, scale_r, j);
+              if (t < ch.rows) {
+                float r = __fdiv_rn(gv[j], scale);
+                r = fminf(fmaxf(r, -128.0f), 127.0f);
+                p.act_q[((int64_t)ch.row0 + t) * I + (int64_t)nt * TILE_N + n_local] = (int8_t)__float2int_rz(r);
+              }
+            }
+#pragma unroll
+            for (int w = 0; w < NUM_W; ++w)
+#pragma unroll
+              for (int pp = 0; pp + 1 < NP; ++pp)
+#pragma unroll
+                for (int j = 0; j < 16; ++j) acc[w][pp][j] = acc[w][pp + 1][j];
+          }
+          if (!ok) break;
+          item_par ^= 1u;
+        } else {
+#pragma unroll 1
+          for (int pc = 0; pc < my_p; ++pc) {
+            const float *av = &acc[0][0][0];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const int32_t sid = __shfl_sync(0xffffffffu, NPF > 1 && (pc >> 1) ? sid_r[NPF - 1] : sid_r[0], (pc & 1) * 16 + j);
+              const float wgt = __shfl_sync(0xffffffffu, NPF > 1 && (pc >> 1) ? wgt_r[NPF - 1] : wgt_r[0], (pc & 1) * 16 + j);
+              if (sid >= 0) {
+                float v = av[j];
+                if (p.weight_mode == LO_WEIGHT_FP32) {
+                  v = v * wgt;
+                } else if (p.weight_mode == LO_WEIGHT_BF16_PRODUCT) {
+                  v = bf16_round(v) * bf16_round(wgt);
+                }
+                if ((int64_t)nt * TILE_N + n_local < p.n_store)
+                  p.C[(int64_t)sid * p.n_store + (int64_t)nt * TILE_N + n_local] = __float2bfloat16_rn(v);
+              }
+            }
+#pragma unroll
+            for (int pp = 0; pp + 1 < NP; ++pp)
+#pragma unroll
+              for (int j = 0; j < 16; ++j) acc[0][pp][j] = acc[0][pp + 1][j];
           }
         }
-      }
-      // Column ownership changes from item to item (it depends on the chunk size), so the next item's
-      // first K block may store running sums into columns another warp is still reading in the passes
-      // above: all promotion warps meet before any of them goes on.
-      // (Per-channel mode needs none: an item's buffer is private to it until all 16 warps released it.)
-      if (MODE != GEMM_CHANNEL) {
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.isync);
-        if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.isync, isync_ph, p.status, 11))) { ok = false; break; }
-        isync_ph ^= 1u;
-        item_par ^= 1u;
       }
     }
   }
@@ -1004,7 +911,7 @@ int launch_mode(const GemmArgs &a, cudaStream_t stream) {
   p.n_rows_per_expert = a.n_rows_per_expert; p.n_store = a.n_store > 0 ? a.n_store : a.n_rows_per_expert; p.KB = (int)(a.K / TILE_K); p.n_tiles = a.n_tiles;
   p.sorted_ids = a.sorted_ids; p.numel_valid = a.numel_valid;
   p.chunks = a.chunks; p.num_chunks = a.num_chunks; p.act_q = a.act_q; p.act_s = a.act_s; p.C = a.C;
-  p.topk_weights = a.topk_weights; p.weight_mode = a.weight_mode; p.act_eps = a.act_eps; p.status = a.status; p.neg_zero = -0.0f;
+  p.topk_weights = a.topk_weights; p.weight_mode = a.weight_mode; p.act_eps = a.act_eps; p.status = a.status;
   p.out_by_position = a.out_by_position;
   const int grid = sm_count();
   if (grid <= 0) return fail(LO_ERR_CUDA, "no CUDA device");
