@@ -69,10 +69,6 @@ int launch_align(const void *topk_ids, int ids_dtype, int64_t numel, int num_exp
                  Chunk *chunks, int32_t *num_chunks, int64_t chunk_capacity, int32_t *inv_pos,
                  int chunk_max, cudaStream_t stream);
 
-// A second chunk table with chunks of up to `chunk_max` rows from the table launch_align wrote, see routing.cu.
-int launch_rechunk(const Chunk *chunks, const int32_t *num_chunks, int chunk_max, Chunk *out, int32_t *num_out,
-                   int64_t capacity, cudaStream_t stream);
-
 // Group quantisation of bf16 rows [M, H] written straight into the expert-sorted layout:
 // the int8 row and its scales of token t go to every position inv_pos[t * topk + j] >= 0.  quant.cu
 int launch_group_quant_scatter(const void *x, int64_t M, int64_t H, int topk, const int32_t *inv_pos, float eps,

@@ -25,11 +25,10 @@ struct Carver {
 struct FusedLayout {
   int8_t *xq;           // [sorted_cap, H] quantised activations in sorted-position order
   float *xs;            // [sorted_cap, H/128]
-  int32_t *header;      // [0] num_tokens_post_pad, [1] num_chunks, [2] number of wide chunks
+  int32_t *header;      // [0] num_tokens_post_pad, [1] num_chunks
   int32_t *sorted_ids;
   int32_t *inv_pos;     // [M*topk] position of every (token, slot), -1 if dropped
   Chunk *chunks;
-  Chunk *chunks_wide;   // the same rows cut into chunks of up to 160 (down GEMM at prefill sizes)
   int8_t *act_q;
   float *act_s;
   int64_t sorted_cap;
@@ -51,21 +50,18 @@ FusedLayout carve_fused(void *ws, int64_t M, int num_experts_for_align, int topk
   L.chunks = c.take<Chunk>(L.chunk_cap);
   L.act_q = c.take<int8_t>(L.sorted_cap * I);
   L.act_s = c.take<float>(L.sorted_cap * (I / 128));
-  L.chunks_wide = c.take<Chunk>(L.chunk_cap);
   L.bytes = c.off;
   return L;
 }
 
-// Chunk sizes of the block-scaled layer.  An M=128, K=32 MMA costs the same ~96 cycles for any N <= 128, so chunks
-// smaller than 128 only multiply the MMA count (64 -> 1.3x, 32 -> 1.9x the layer time at 128 rows per expert).
-// The down GEMM gains from chunks of up to 160 rows once experts get 64 rows or more on average (fewer passes
-// over the weights: -19 % at 128 rows per expert, where half of the experts have a few rows more than 128, equal
-// at 2048 rows per expert); gate_up does not, its two sets of running sums leave one partial buffer at that width
-// (+15..25 % measured at 64..2048 rows per expert).  So gate_up always runs on 128-row chunks and down gets its
-// own table above that load.
+// Chunk sizes of the block-scaled layer.  An M=128, K=32 MMA costs the same ~96 cycles for any N <= 128 (128 cycles
+// up to N = 256), so chunks smaller than 128 only multiply the MMA count.  Once experts get 64 rows or more on average
+// the table is cut into chunks of up to 160 rows, the widest whose partial buffers still number three: at 128 rows per
+// expert about half of the experts have a few rows more than 128, and a second chunk means a second pass over the
+// expert's weights.
 constexpr int CHUNK_ROWS = 128;
 constexpr int CHUNK_ROWS_WIDE = 160;
-inline bool wide_down_chunks(int64_t rows, int experts) { return rows / experts >= 64; }
+inline int chunk_rows_for(int64_t rows, int experts) { return rows / experts >= 64 ? CHUNK_ROWS_WIDE : CHUNK_ROWS; }
 
 // Optional per-stage timing of the fused call (cudaEvents recorded between its five kernels).
 struct StageProfile {
@@ -155,18 +151,13 @@ extern "C" int lo_fused_moe_block_int8(const void *x, const int8_t *w1, const in
   const int64_t numel = M * topk;
   int rc;
 
-  const int chunk_max = CHUNK_ROWS;
-  const bool wide = wide_down_chunks(numel, align_E);
+  const int chunk_max = chunk_rows_for(numel, align_E);
   // 1. expert-major stable order, chunk table, position of every (token, slot)
   prof_mark(0, st);
   rc = launch_align(topk_ids, ids_dtype, numel, align_E, FUSED_ALIGN_BLOCK, expert_map, expert_map ? 1 : 0,
                     L.sorted_ids, L.sorted_cap, nullptr, 0, L.header, L.chunks, L.header + 1, L.chunk_cap, L.inv_pos,
                     chunk_max, st);
   if (rc != LO_OK) return rc;
-  if (wide) {
-    rc = launch_rechunk(L.chunks, L.header + 1, CHUNK_ROWS_WIDE, L.chunks_wide, L.header + 2, L.chunk_cap, st);
-    if (rc != LO_OK) return rc;
-  }
 
   // 2. activations -> int8 + per-128 scales, written once per routed slot into sorted order so
   //    that every chunk of the grouped GEMM is a run of consecutive rows (one TMA box)
@@ -199,10 +190,6 @@ extern "C" int lo_fused_moe_block_int8(const void *x, const int8_t *w1, const in
   g2.n_rows_per_expert = H; g2.K = I; g2.n_tiles = (int)(H / 128);
   g2.sorted_ids = L.sorted_ids; g2.numel_valid = numel;
   g2.chunks = L.chunks; g2.num_chunks = L.header + 1;
-  if (wide) {
-    g2.chunks = L.chunks_wide; g2.num_chunks = L.header + 2;
-    g2.max_chunk_rows = (int)(M < CHUNK_ROWS_WIDE ? M : CHUNK_ROWS_WIDE);
-  }
   g2.C = static_cast<__nv_bfloat16 *>(cache3);
   g2.topk_weights = topk_weights;
   g2.weight_mode = apply_router_weight_on_input ? LO_WEIGHT_NONE : LO_WEIGHT_BF16_PRODUCT;
@@ -529,16 +516,11 @@ extern "C" int lo_expert_rows_block_int8(const int8_t *xq, const float *xs, cons
   LO_REQUIRE(workspace_bytes >= L.bytes, "expert rows: workspace of %zu bytes, %zu needed", workspace_bytes, L.bytes);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // chunk sizes: the rule of lo_fused_moe_block_int8
-  const int chunk_max = CHUNK_ROWS;
-  const bool wide = wide_down_chunks(T, E_local);
+  const int chunk_max = chunk_rows_for(T, E_local);
   // 1. expert-major stable order of the rows (ids outside [0, E_local) are dropped)
   int rc = launch_align(row_expert, LO_I32, T, E_local, FUSED_ALIGN_BLOCK, nullptr, 0, L.sorted_ids, L.sorted_cap,
                         nullptr, 0, L.header, L.chunks, L.header + 1, L.chunk_cap, nullptr, chunk_max, st);
   if (rc != LO_OK) return rc;
-  if (wide) {
-    rc = launch_rechunk(L.chunks, L.header + 1, CHUNK_ROWS_WIDE, L.chunks_wide, L.header + 2, L.chunk_cap, st);
-    if (rc != LO_OK) return rc;
-  }
   // 2. rows and scales into sorted order
   rc = launch_permute_rows(xq, xs, T, H, L.sorted_ids, L.sorted_cap, L.header, T, 1, L.xq, L.xs, st);
   if (rc != LO_OK) return rc;
@@ -560,10 +542,6 @@ extern "C" int lo_expert_rows_block_int8(const int8_t *xq, const float *xs, cons
   g2.n_rows_per_expert = H; g2.K = I; g2.n_tiles = (int)(H / 128);
   g2.sorted_ids = L.sorted_ids; g2.numel_valid = T;
   g2.chunks = L.chunks; g2.num_chunks = L.header + 1;
-  if (wide) {
-    g2.chunks = L.chunks_wide; g2.num_chunks = L.header + 2;
-    g2.max_chunk_rows = (int)(T < CHUNK_ROWS_WIDE ? T : CHUNK_ROWS_WIDE);
-  }
   g2.C = static_cast<__nv_bfloat16 *>(out);      // top_k = 1: the sorted id is the row itself
   g2.topk_weights = row_weight;
   g2.weight_mode = row_weight ? LO_WEIGHT_BF16_PRODUCT : LO_WEIGHT_NONE;

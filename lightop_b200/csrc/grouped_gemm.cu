@@ -62,49 +62,65 @@ namespace {
 
 constexpr int TILE_N = 128;      // weight rows per accumulator (MMA M)
 constexpr int TILE_K = 128;      // int8 elements (= bytes) per K block
-constexpr int T_MAX = 128;       // tokens per chunk unless the caller asks for the wide block-scaled chunks
-constexpr int T_WIDE = 160;      // widest single-matrix block-scaled chunk: sums + two partial buffers = 3 x 160 columns
+constexpr int T_MAX = 128;       // default bound of the rows of a chunk
+constexpr int T_WIDE = 160;      // widest block-scaled chunk: three partial buffers of 160 columns fill tensor memory
 constexpr int NUM_THREADS = 640;
-constexpr int SCALE_THREADS = 64;
 constexpr int FIRST_EPI_WARP = 4;
 constexpr int EPI_WARPS = 16;
 constexpr int W_TILE_BYTES = TILE_N * TILE_K;   // 16 KiB
+constexpr int OUT_ROW_BYTES = TILE_N * 2;       // one token's 128 outputs as bf16 in the staging tile
 constexpr uint32_t TMEM_COLS = 512;
+constexpr int ND = 16;                          // completion ring, see Smem::done
+constexpr int SMEM_LIMIT = 227 * 1024;          // dynamic shared memory a CTA can be given on this part
 
 // A_ROWS is the largest chunk (token count) the instantiation accepts: with few tokens per call no
-// expert can receive more than that many rows, the activation tile of a stage shrinks and more
-// stages fit into shared memory (more weight bytes in flight per SM).
+// expert can receive more than that many rows, the activation tiles shrink and more weight tiles fit
+// into shared memory (more weight bytes in flight per SM).
 template <int MODE, int A_ROWS> struct Cfg {
-  static constexpr int NUM_W = MODE == GEMM_GATE_UP ? 2 : 1;   // gate tile + up tile
-  static constexpr int STAGE_BYTES = NUM_W * W_TILE_BYTES + A_ROWS * TILE_K;
-  static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 10 ? 10 : (200 * 1024) / STAGE_BYTES;
+  // gate_up: an item is two passes over K on the same chunk, first the gate tile, then the up tile
+  static constexpr int PHASES = MODE == GEMM_GATE_UP ? 2 : 1;
+  static constexpr int A_TILE_BYTES = A_ROWS * TILE_K;
+  // Two rings.  Activation tiles come from L2 (the chunk's rows are read by every output tile of the expert): a
+  // slot is refilled only after the MMAs that read it have completed, so the ring has to cover the load latency
+  // plus the MMA queue, four K blocks at least.  Weight tiles come from HBM and get the shared memory that is left.
+  static constexpr int NA_FIT = (64 * 1024) / A_TILE_BYTES;
+  static constexpr int NA = NA_FIT < 4 ? 4 : (NA_FIT > 10 ? 10 : NA_FIT);
+  // staging tile of the epilogue: [A_ROWS][128] bf16 (gate_up keeps the gate values there during the up pass)
+  static constexpr int STAGING_BYTES = MODE == GEMM_CHANNEL ? 0 : A_ROWS * OUT_ROW_BYTES;
+  static constexpr int FIXED_BYTES = 14 * 1024;   // scale tables, maxima, barriers, alignment slack (checked below)
+  static constexpr int NW_FIT = (SMEM_LIMIT - FIXED_BYTES - STAGING_BYTES - NA * A_TILE_BYTES) / W_TILE_BYTES;
+  static constexpr int NW = NW_FIT > 12 ? 12 : NW_FIT;
   // tensor memory is cut into partial buffers of A_ROWS columns, one int32 accumulator each (at most 8 are used):
   // the partial of one 128-wide K block in the block-scaled modes (the fp32 running sums live in the registers of
   // the promotion warps), the accumulator of a whole item in the per-channel mode
   static constexpr int NBUF = (int)TMEM_COLS / A_ROWS > 8 ? 8 : (int)TMEM_COLS / A_ROWS;
   // Ring of scale-product tables.  A slot written for K-block step i was last read at step
-  // i - SC_SLOTS; the producer of step i has seen the MMAs of step i - STAGES complete, which were
-  // issued after the promotion of step i - STAGES - NBUF finished, so STAGES + NBUF slots suffice.
-  static constexpr int SC_SLOTS = MODE == GEMM_CHANNEL ? 1 : STAGES + NBUF;
+  // i - SC_SLOTS; the producer of step i has seen the MMAs of step i - NW complete, which were
+  // issued after the promotion of step i - NW - NBUF finished, so NW + NBUF slots suffice.
+  static constexpr int SC_SLOTS = MODE == GEMM_CHANNEL ? 1 : NW + NBUF;
 };
 
-
 template <int MODE, int A_ROWS> struct Smem {
-  static constexpr int STAGES = Cfg<MODE, A_ROWS>::STAGES;
-  static constexpr int NUM_W = Cfg<MODE, A_ROWS>::NUM_W;
-  static constexpr int NBUF = Cfg<MODE, A_ROWS>::NBUF;
+  using C = Cfg<MODE, A_ROWS>;
   // operand tiles first: each is a multiple of 1024 bytes, base is 1024-aligned
-  uint8_t w[STAGES][NUM_W][W_TILE_BYTES];
-  uint8_t a[STAGES][A_ROWS * TILE_K];
-  static constexpr int SC_SLOTS = Cfg<MODE, A_ROWS>::SC_SLOTS;
-  float sc[SC_SLOTS][NUM_W][A_ROWS];       // token scale x weight-block scale, ring indexed by the K-block counter
+  uint8_t w[C::NW][W_TILE_BYTES];
+  uint8_t a[C::NA][C::A_TILE_BYTES];
+  // epilogue staging, row = token (column of the chunk), 256 bytes per row
+  uint8_t staging[C::STAGING_BYTES > 0 ? C::STAGING_BYTES : 16];
+  float sc[C::SC_SLOTS][A_ROWS];           // token scale x weight-block scale, ring indexed by the K-block counter
   // gate_up epilogue: |act| maxima per (item parity, lane quarter, token); a stub in the other modes
   uint32_t amax[MODE == GEMM_GATE_UP ? 2 : 1][4][MODE == GEMM_GATE_UP ? A_ROWS : 1];
-  uint64_t full[STAGES];
-  uint64_t empty[STAGES];
-  uint64_t tmem_full[NBUF];
-  uint64_t tmem_empty[NBUF];
+  uint64_t full_w[C::NW];
+  uint64_t full_a[C::NA];
+  // done[u % ND]: the MMAs of K-block step u have completed.  One tcgen05.commit per step serves everybody who
+  // waits for that event: the producers (a weight slot is free NW steps later, an activation slot NA steps later),
+  // the scale warp, and in the block-scaled modes the promotion warps (the partial of step u is in its buffer).
+  // ND exceeds every ring depth, so a waiter cannot be overtaken by the barrier's next phase.
+  uint64_t done[ND];
+  uint64_t tmem_full[C::NBUF];             // per-channel mode: the accumulator of an item is complete
+  uint64_t tmem_empty[C::NBUF];
   uint64_t esync[4];                       // rendezvous of the 128 epilogue threads of a column group
+  uint64_t isync;                          // rendezvous of all promotion warps, once per item
   uint32_t tmem_base;
   volatile int abort_flag;
 };
@@ -141,13 +157,18 @@ constexpr long long WAIT_LIMIT_CYCLES = 3000000000ll;
 
 // Bounded wait.  Returns false when the CTA is aborting (this waiter timed out or another one
 // did); `code` identifies the waiter in the status word.  The clock is only consulted every
-// 256 failed polls, so a wait that completes quickly costs nothing but the polls.
+// 256 failed polls, so a wait that completes quickly costs nothing but the polls.  A waiter sleeps
+// `sleep_ns` between two polls: a polling warp is always eligible, and the scheduler it shares with
+// four others was observed to give it most of the issue slots (a promotion warp's dozen loop
+// instructions between two K blocks took several hundred cycles).  Waiters far off the critical path
+// (producers that run stages ahead, promotion warps without columns in a narrow chunk) sleep longer.
 template <class S>
-__device__ __forceinline__ bool mbar_wait(S &sm, uint64_t *bar, uint32_t parity, int32_t *status, int code) {
+__device__ __forceinline__ bool mbar_wait(S &sm, uint64_t *bar, uint32_t parity, int32_t *status, int code, uint32_t sleep_ns = 32u) {
   if (mbar_try_wait(bar, parity)) return true;
   long long t0 = 0;
   uint32_t spins = 0;
   while (true) {
+    __nanosleep(sleep_ns);
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 255u) == 0u) {
       if (sm.abort_flag) return false;
@@ -175,11 +196,12 @@ __device__ __forceinline__ bool mbar_try_wait_addr(uint32_t bar, uint32_t parity
   return ok != 0;
 }
 template <class S>
-__device__ __forceinline__ bool mbar_wait_addr(S &sm, uint32_t bar, uint32_t parity, int32_t *status, int code) {
+__device__ __forceinline__ bool mbar_wait_addr(S &sm, uint32_t bar, uint32_t parity, int32_t *status, int code, uint32_t sleep_ns = 32u) {
   if (mbar_try_wait_addr(bar, parity)) return true;
   long long t0 = 0;
   uint32_t spins = 0;
   while (true) {
+    __nanosleep(sleep_ns);
     if (mbar_try_wait_addr(bar, parity)) return true;
     if ((++spins & 255u) == 0u) {
       if (sm.abort_flag) return false;
@@ -192,6 +214,18 @@ __device__ __forceinline__ bool mbar_wait_addr(S &sm, uint32_t bar, uint32_t par
       }
     }
   }
+}
+// One non-blocking look at a barrier: has the phase of this parity completed?
+__device__ __forceinline__ bool mbar_test_addr(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
 }
 __device__ __forceinline__ void mbar_arrive_addr(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -276,6 +310,19 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr)
       : "memory");
 }
+// 32 consecutive tensor-memory columns of this thread's lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // Packed fp32 pair arithmetic (two IEEE round-to-nearest operations per instruction).
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
@@ -296,7 +343,7 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
 // The 128-long int8 dot is below 2^21 in magnitude, so the conversion is exact; one rounding per K block.
 // `sc_addr` is the shared-memory address of the N scale products.
 template <int N>
-__device__ __forceinline__ void promote(const uint32_t (&raw)[N], float *acc, uint32_t sc_addr) {
+__device__ __forceinline__ void promote(const uint32_t *raw, float *acc, uint32_t sc_addr) {
 #pragma unroll
   for (int j4 = 0; j4 < N / 4; ++j4) {
     uint64_t sc01, sc23;               // scale products of four tokens
@@ -345,10 +392,12 @@ template <int MODE, int A_ROWS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ AMaps a_maps, const KParams p) {
   using SM = Smem<MODE, A_ROWS>;
-  constexpr int SC_SLOTS = SM::SC_SLOTS;
-  constexpr int STAGES = SM::STAGES;
-  constexpr int NUM_W = SM::NUM_W;
-  constexpr int NBUF = SM::NBUF;
+  using CF = Cfg<MODE, A_ROWS>;
+  constexpr int SC_SLOTS = CF::SC_SLOTS;
+  constexpr int NW = CF::NW;
+  constexpr int NA = CF::NA;
+  constexpr int NBUF = CF::NBUF;
+  constexpr int PHASES = CF::PHASES;
   extern __shared__ uint8_t smem_raw[];
   SM &sm = *reinterpret_cast<SM *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -360,16 +409,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
 
   // ------------------------------ set-up -----------------------------------
   if (tid == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      // TMA thread (arrive.expect_tx) + one arrive per scale warp (per-channel mode has no scale tables)
-      mbar_init(&sm.full[s], MODE == GEMM_CHANNEL ? 1 : 1 + SCALE_THREADS / 32);
-      mbar_init(&sm.empty[s], 1);                        // tcgen05.commit of the MMA thread
+    for (int s = 0; s < NW; ++s) {
+      // weight producer (arrive.expect_tx) + the scale warp (per-channel mode has no scale tables)
+      mbar_init(&sm.full_w[s], MODE == GEMM_CHANNEL ? 1 : 2);
     }
+    for (int s = 0; s < NA; ++s) mbar_init(&sm.full_a[s], 1);
+    for (int s = 0; s < ND; ++s) mbar_init(&sm.done[s], 1);   // tcgen05.commit of the MMA thread
     for (int b = 0; b < NBUF; ++b) {
       mbar_init(&sm.tmem_full[b], 1);
       mbar_init(&sm.tmem_empty[b], EPI_WARPS);
     }
     for (int b = 0; b < 4; ++b) mbar_init(&sm.esync[b], 128);
+    mbar_init(&sm.isync, EPI_WARPS);
     sm.abort_flag = 0;
     fence_barrier_init();
   }
@@ -402,104 +453,131 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
 
   if (warp < FIRST_EPI_WARP) {
     if (warp == 0) {
-      // ============ TMA producer: weight tiles + the chunk's token rows ============
+      // ============ weight producer: one 128 x 128 tile per K block (gate_up: gate pass, then up pass) ============
       if (lane == 0) {
         const uint64_t pol_stream = policy_evict_first();
         const uint64_t pol_keep = policy_evict_normal();
-        const uint64_t pol_a = policy_evict_last();
         uint32_t it = 0;
+        int s = 0;
         bool ok = true;
         for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
           const Chunk ch = p.chunks[item / p.n_tiles];
           const int nt = (int)(item % p.n_tiles);
+          if (ch.expert < 0) continue;
+          // weight tiles are streamed (evict-first) unless another chunk of the same expert is about to read
+          // them again: those stay in L2 under the normal policy
+          const uint64_t pol_w = ch.pad ? pol_keep : pol_stream;
+          for (int ph = 0; ph < PHASES && ok; ++ph) {
+            const int32_t row_g = (int32_t)(ch.expert * p.n_rows_per_expert + (int64_t)(ph * p.n_tiles + nt) * TILE_N);
+            for (int kb = 0; kb < KB; ++kb, ++it) {
+              // slot s was read by step it - NW
+              if (it >= (uint32_t)NW && !mbar_wait(sm, &sm.done[(it - NW) % ND], ((it - NW) / ND) & 1u, p.status, 1, 128u)) { ok = false; break; }
+              mbar_arrive_expect_tx(&sm.full_w[s], W_TILE_BYTES);
+              tma_load_2d(sm.w[s], &w_map, kb * TILE_K, row_g, &sm.full_w[s], pol_w);
+              s = s + 1 == NW ? 0 : s + 1;
+            }
+          }
+        }
+      } else if (lane == 16) {
+      // ============ activation producer (a second lane of the same warp, on its own path): the chunk's token
+      // rows of every K block.  Token rows are read from an expert-sorted copy of the activations, so a chunk is
+      // a run of consecutive rows and one tiled load fetches it (a second one for the rows beyond 128).
+        const uint64_t pol_a = policy_evict_last();
+        uint32_t it = 0;
+        int s = 0;
+        bool ok = true;
+        for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+          const Chunk ch = p.chunks[item / p.n_tiles];
           if (ch.expert < 0) continue;
           const int T = (ch.rows + 15) & ~15;
           const int T0 = T > 128 ? 128 : T;                  // first box; the rest (if any) goes into a second one
           const int mi = a_map_index(T0);
           const int mi2 = T > 128 ? a_map_index(T - 128) : -1;
           const uint32_t a_bytes = (16u << mi) * TILE_K + (mi2 >= 0 ? (16u << mi2) * TILE_K : 0u);
-          const int32_t row_g = (int32_t)(ch.expert * p.n_rows_per_expert + (int64_t)nt * TILE_N);
-          // weight tiles are streamed (evict-first) unless another chunk of the same expert is about to read
-          // them again: those stay in L2 under the normal policy
-          const uint64_t pol_w = ch.pad ? pol_keep : pol_stream;
-          for (int kb = 0; kb < KB; ++kb, ++it) {
-            const int s = it % STAGES;
-            const uint32_t ph = (it / STAGES) & 1u;
-            if (!mbar_wait(sm, &sm.empty[s], ph ^ 1u, p.status, 1)) { ok = false; break; }
-            mbar_arrive_expect_tx(&sm.full[s], NUM_W * W_TILE_BYTES + a_bytes);
-            tma_load_2d(sm.w[s][0], &w_map, kb * TILE_K, row_g, &sm.full[s], pol_w);
-            if (NUM_W == 2)
-              tma_load_2d(sm.w[s][NUM_W - 1], &w_map, kb * TILE_K, row_g + p.n_tiles * TILE_N, &sm.full[s], pol_w);
-            tma_load_2d(sm.a[s], &a_maps.m[mi], kb * TILE_K, ch.row0, &sm.full[s], pol_a);
-            if constexpr (A_ROWS > 128) {
-              if (mi2 >= 0)
-                tma_load_2d(sm.a[s] + 128 * TILE_K, &a_maps.m[mi2], kb * TILE_K, ch.row0 + 128, &sm.full[s], pol_a);
+          for (int ph = 0; ph < PHASES && ok; ++ph) {
+            for (int kb = 0; kb < KB; ++kb, ++it) {
+              if (it >= (uint32_t)NA && !mbar_wait(sm, &sm.done[(it - NA) % ND], ((it - NA) / ND) & 1u, p.status, 6, 128u)) { ok = false; break; }
+              mbar_arrive_expect_tx(&sm.full_a[s], a_bytes);
+              tma_load_2d(sm.a[s], &a_maps.m[mi], kb * TILE_K, ch.row0, &sm.full_a[s], pol_a);
+              if constexpr (A_ROWS > 128) {
+                if (mi2 >= 0)
+                  tma_load_2d(sm.a[s] + 128 * TILE_K, &a_maps.m[mi2], kb * TILE_K, ch.row0 + 128, &sm.full_a[s], pol_a);
+              }
+              s = s + 1 == NA ? 0 : s + 1;
             }
           }
         }
       }
-    } else if (warp == 1) {
-      // ============================ MMA issuer ===============================
-      if (lane == 0) {
-        uint32_t it = 0, ab = 0;
-        bool ok = true;
-        for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-          const Chunk ch = p.chunks[item / p.n_tiles];
-          if (ch.expert < 0) continue;
-          const uint32_t T = (uint32_t)((ch.rows + 15) & ~15);
-          const uint32_t idesc = make_idesc(T);
-          if constexpr (MODE == GEMM_CHANNEL) {
-            // one int32 accumulator per item, summed over every K block; the scales come in the epilogue
-            const uint32_t b = ab % NBUF;
-            const uint32_t aph = (ab / NBUF) & 1u;
-            ++ab;
-            if (!mbar_wait(sm, &sm.tmem_empty[b], aph ^ 1u, p.status, 2)) { ok = false; break; }
+    } else if (warp == 1 || warp == 3) {
+      // ============================ MMA issuers ===============================
+      // Lane 0 issues; lanes 0, 1 and 2 each poll one of the step's three barriers (weights landed, activations
+      // landed, partial buffer free) in the same instruction.  One commit per step.  A step of this role is a chain
+      // of a hundred dependent scalar instructions and barrier round trips, about a thousand cycles however little
+      // the tensor core has to do, which is more than the 16 KB of weights of a step take to arrive: in the
+      // block-scaled modes two warps share the steps (even ones here, odd ones there; the partials of different
+      // steps are independent and a commit tracks the MMAs of its own thread).  Per-channel mode accumulates an
+      // item's steps into one buffer, in order, so warp 1 issues them all.
+      constexpr int NISS = MODE == GEMM_CHANNEL ? 1 : 2;
+      const uint32_t which = warp == 1 ? 0u : 1u;
+      uint32_t it = 0;
+      uint32_t sw = 0, par_w = 0, sa = 0, par_a = 0, b = 0, par_b = 0;   // ring positions and their phase parities
+      const uint32_t full_w0 = smem_u32(&sm.full_w[0]), full_a0 = smem_u32(&sm.full_a[0]);
+      const uint32_t tempty0 = smem_u32(&sm.tmem_empty[0]);
+      bool ok = true;
+      for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+        const Chunk ch = p.chunks[item / p.n_tiles];
+        if (ch.expert < 0) continue;
+        const uint32_t T = (uint32_t)((ch.rows + 15) & ~15);
+        const uint32_t idesc = make_idesc(T);
+        const int steps = PHASES * KB;
+        for (int u = 0; u < steps; ++u, ++it) {
+          if (NISS == 1 ? which != 0u : (it & 1u) != which) {
+            // the other issuer's step: keep the ring positions in step
+            sw = sw + 1 == (uint32_t)NW ? 0u : sw + 1;
+            par_w ^= sw == 0u ? 1u : 0u;
+            sa = sa + 1 == (uint32_t)NA ? 0u : sa + 1;
+            par_a ^= sa == 0u ? 1u : 0u;
+            b = b + 1 == (uint32_t)NBUF ? 0u : b + 1;
+            par_b ^= b == 0u ? 1u : 0u;
+            continue;
+          }
+          // per-channel mode: one int32 accumulator per item, summed over every K block; the buffer is waited for
+          // once, at the item's first step
+          const bool need_buf = MODE != GEMM_CHANNEL || u == 0;
+          const uint32_t bar = lane == 0 ? full_w0 + 8u * sw : (lane == 1 ? full_a0 + 8u * sa : tempty0 + 8u * b);
+          const uint32_t par = lane == 0 ? par_w : (lane == 1 ? par_a : par_b ^ 1u);
+          bool mine = true;
+          if (lane < 2 || (lane == 2 && need_buf)) mine = mbar_wait_addr(sm, bar, par, p.status, 3 + lane, 20u);
+          if (!__all_sync(0xffffffffu, mine)) { ok = false; break; }
+          if (lane == 0) {
             tc_fence_after();
+            const uint64_t bdesc = make_smem_desc(smem_u32(sm.a[sa]));
+            const uint64_t adesc = make_smem_desc(smem_u32(sm.w[sw]));
             const uint32_t d = tmem_base + b * (uint32_t)A_ROWS;
-            for (int kb = 0; kb < KB; ++kb, ++it) {
-              const int s = it % STAGES;
-              const uint32_t ph = (it / STAGES) & 1u;
-              if (!mbar_wait(sm, &sm.full[s], ph, p.status, 3)) { ok = false; break; }
-              tc_fence_after();
-              const uint64_t bdesc = make_smem_desc(smem_u32(sm.a[s]));
-              const uint64_t adesc = make_smem_desc(smem_u32(sm.w[s][0]));
 #pragma unroll
-              for (int k4 = 0; k4 < TILE_K / 32; ++k4)
-                umma_i8(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, (kb | k4) != 0 ? 1u : 0u);
-              umma_commit(&sm.empty[s]);
-            }
-            if (ok) umma_commit(&sm.tmem_full[b]);
-          } else {
-            for (int kb = 0; kb < KB; ++kb, ++it) {
-              const int s = it % STAGES;
-              const uint32_t ph = (it / STAGES) & 1u;
-              if (!mbar_wait(sm, &sm.full[s], ph, p.status, 3)) { ok = false; break; }
-              const uint64_t bdesc = make_smem_desc(smem_u32(sm.a[s]));
-#pragma unroll
-              for (int w = 0; w < NUM_W; ++w, ++ab) {
-                const uint32_t b = ab % NBUF;
-                const uint32_t aph = (ab / NBUF) & 1u;
-                if (!mbar_wait(sm, &sm.tmem_empty[b], aph ^ 1u, p.status, 2)) { ok = false; break; }
-                tc_fence_after();
-                const uint64_t adesc = make_smem_desc(smem_u32(sm.w[s][w]));
-                const uint32_t d = tmem_base + b * (uint32_t)A_ROWS;
-#pragma unroll
-                for (int k4 = 0; k4 < TILE_K / 32; ++k4)
-                  umma_i8(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc, k4 != 0 ? 1u : 0u);
-                umma_commit(&sm.tmem_full[b]);
-              }
-              if (!ok) break;
-              umma_commit(&sm.empty[s]);
-            }
+            for (int k4 = 0; k4 < TILE_K / 32; ++k4)
+              umma_i8(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc,
+                      (MODE == GEMM_CHANNEL ? (u | k4) : k4) != 0 ? 1u : 0u);
+            umma_commit(&sm.done[it % ND]);
+            if (MODE == GEMM_CHANNEL && u == steps - 1) umma_commit(&sm.tmem_full[b]);
+          }
+          __syncwarp();
+          sw = sw + 1 == (uint32_t)NW ? 0u : sw + 1;
+          par_w ^= sw == 0u ? 1u : 0u;
+          sa = sa + 1 == (uint32_t)NA ? 0u : sa + 1;
+          par_a ^= sa == 0u ? 1u : 0u;
+          if (MODE != GEMM_CHANNEL || u == steps - 1) {
+            b = b + 1 == (uint32_t)NBUF ? 0u : b + 1;
+            par_b ^= b == 0u ? 1u : 0u;
           }
         }
       }
     } else if (MODE != GEMM_CHANNEL) {
-      // ========================= scale producers (2 warps) ====================
-      // Thread g owns tokens g, g + 64 (and g + 128) of the chunk.  Token scales and weight-block scales are
+      // ========================= scale producer (warp 2) ====================
+      // Thread g owns tokens g, g + 32, ... of the chunk.  Token scales and weight-block scales are
       // read four K blocks at a time and one group ahead, so the loop never waits on memory.
-      const int g = tid - 64;            // 0..63
-      constexpr int NU = (A_ROWS + SCALE_THREADS - 1) / SCALE_THREADS < 2 ? 2 : (A_ROWS + SCALE_THREADS - 1) / SCALE_THREADS;
+      const int g = lane;
+      constexpr int NU = (A_ROWS + 31) / 32;
       uint32_t it = 0;
       bool ok = true;
       const bool vec4 = (KB & 3) == 0;
@@ -513,87 +591,77 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         bool live[NU];
 #pragma unroll
         for (int u = 0; u < NU; ++u) {
-          const int t = g + u * SCALE_THREADS;
+          const int t = g + u * 32;
           live[u] = t < ch.rows;
           as_ptr[u] = p.a_scale + (int64_t)(ch.row0 + (live[u] ? t : 0)) * KB;
         }
-        const float *bs_ptr[NUM_W];
-#pragma unroll
-        for (int w = 0; w < NUM_W; ++w)
-          bs_ptr[w] = p.b_scale + ((int64_t)ch.expert * nblk + nt + (int64_t)w * p.n_tiles) * KB;
-        float4 cur_a[NU], nxt_a[NU], cur_b[NUM_W], nxt_b[NUM_W];
-        const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (vec4) {
-#pragma unroll
-          for (int u = 0; u < NU; ++u) nxt_a[u] = live[u] ? __ldg(reinterpret_cast<const float4 *>(as_ptr[u])) : zero4;
-#pragma unroll
-          for (int w = 0; w < NUM_W; ++w) nxt_b[w] = __ldg(reinterpret_cast<const float4 *>(bs_ptr[w]));
-        }
-        for (int kb = 0; kb < KB; ++kb, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1u;
-          float as_now[NU], bs_now[NUM_W];
+        for (int ph = 0; ph < PHASES && ok; ++ph) {
+          const float *bs_ptr = p.b_scale + ((int64_t)ch.expert * nblk + nt + (int64_t)ph * p.n_tiles) * KB;
+          float4 cur_a[NU], nxt_a[NU], cur_b, nxt_b;
+          const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
           if (vec4) {
-            if ((kb & 3) == 0) {
 #pragma unroll
-              for (int u = 0; u < NU; ++u) {
-                cur_a[u] = nxt_a[u];
-                if (kb + 4 < KB && live[u]) nxt_a[u] = __ldg(reinterpret_cast<const float4 *>(as_ptr[u] + kb + 4));
-              }
-#pragma unroll
-              for (int w = 0; w < NUM_W; ++w) {
-                cur_b[w] = nxt_b[w];
-                if (kb + 4 < KB) nxt_b[w] = __ldg(reinterpret_cast<const float4 *>(bs_ptr[w] + kb + 4));
-              }
-            }
-            const int sel = kb & 3;
-#pragma unroll
-            for (int u = 0; u < NU; ++u)
-              as_now[u] = sel == 0 ? cur_a[u].x : (sel == 1 ? cur_a[u].y : (sel == 2 ? cur_a[u].z : cur_a[u].w));
-#pragma unroll
-            for (int w = 0; w < NUM_W; ++w)
-              bs_now[w] = sel == 0 ? cur_b[w].x : (sel == 1 ? cur_b[w].y : (sel == 2 ? cur_b[w].z : cur_b[w].w));
-          } else {
-#pragma unroll
-            for (int u = 0; u < NU; ++u) as_now[u] = live[u] ? __ldg(as_ptr[u] + kb) : 0.f;
-#pragma unroll
-            for (int w = 0; w < NUM_W; ++w) bs_now[w] = __ldg(bs_ptr[w] + kb);
+            for (int u = 0; u < NU; ++u) nxt_a[u] = live[u] ? __ldg(reinterpret_cast<const float4 *>(as_ptr[u])) : zero4;
+            nxt_b = __ldg(reinterpret_cast<const float4 *>(bs_ptr));
           }
-          // the slot of this step is free once the stage is (see SC_SLOTS)
-          if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.empty[s], ph ^ 1u, p.status, 4))) { ok = false; break; }
-          const int slot = it % SC_SLOTS;
+          for (int kb = 0; kb < KB; ++kb, ++it) {
+            const int s = it % NW;
+            float as_now[NU], bs_now;
+            if (vec4) {
+              if ((kb & 3) == 0) {
 #pragma unroll
-          for (int u = 0; u < NU; ++u) {
-            const int t = g + u * SCALE_THREADS;
-            if (t < T) {
+                for (int u = 0; u < NU; ++u) {
+                  cur_a[u] = nxt_a[u];
+                  if (kb + 4 < KB && live[u]) nxt_a[u] = __ldg(reinterpret_cast<const float4 *>(as_ptr[u] + kb + 4));
+                }
+                cur_b = nxt_b;
+                if (kb + 4 < KB) nxt_b = __ldg(reinterpret_cast<const float4 *>(bs_ptr + kb + 4));
+              }
+              const int sel = kb & 3;
 #pragma unroll
-              for (int w = 0; w < NUM_W; ++w) sm.sc[slot][w][t] = __fmul_rn(as_now[u], bs_now[w]);
+              for (int u = 0; u < NU; ++u)
+                as_now[u] = sel == 0 ? cur_a[u].x : (sel == 1 ? cur_a[u].y : (sel == 2 ? cur_a[u].z : cur_a[u].w));
+              bs_now = sel == 0 ? cur_b.x : (sel == 1 ? cur_b.y : (sel == 2 ? cur_b.z : cur_b.w));
+            } else {
+#pragma unroll
+              for (int u = 0; u < NU; ++u) as_now[u] = live[u] ? __ldg(as_ptr[u] + kb) : 0.f;
+              bs_now = __ldg(bs_ptr + kb);
             }
+            // the slot of this step is free once the weight stage is (see SC_SLOTS)
+            if (it >= (uint32_t)NW &&
+                !__all_sync(0xffffffffu, mbar_wait(sm, &sm.done[(it - NW) % ND], ((it - NW) / ND) & 1u, p.status, 4, 128u))) { ok = false; break; }
+            const int slot = it % SC_SLOTS;
+#pragma unroll
+            for (int u = 0; u < NU; ++u) {
+              const int t = g + u * 32;
+              if (t < T) sm.sc[slot][t] = __fmul_rn(as_now[u], bs_now);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.full_w[s]);
           }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&sm.full[s]);
         }
       }
     }
   } else {
     // ====================== promotion + epilogue (16 warps) ====================
-    const int pw = warp - FIRST_EPI_WARP;   // 0..15; every group of four consecutive warps covers the four lane quarters
+    const int pw = warp - FIRST_EPI_WARP;   // 0..15
     const int q = warp & 3;              // lane quarter of tensor memory this warp may access
     const int cg = pw >> 2;              // column group: which share of the chunk's tokens
     const uint32_t lane_off = (uint32_t)(q * 32) << 16;
-    uint32_t ab = 0, eph = 0, item_par = 0;
-    uint32_t sc_slot = 0, buf = 0, buf_ph = 0;   // block-scaled modes: ring positions of the K loop
+    const int n_local = q * 32 + lane;
+    uint32_t ab = 0, eph = 0, iph = 0, item_par = 0;
+    uint32_t sc_slot = 0, buf = 0, step = 0;     // block-scaled modes: ring positions of the K loop, K-block step count
+    bool ready = false;                          // the coming step's barrier was already seen complete
     bool ok = true;
     for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
       const Chunk ch = p.chunks[item / p.n_tiles];
       const int nt = (int)(item % p.n_tiles);
-      const int n_local = q * 32 + lane;
       if (ch.expert < 0) {
         // block of a non-local expert: its output rows are zero
         if (MODE != GEMM_GATE_UP) {
           for (int t = cg; t < ch.rows; t += 4) {
             const int32_t sid = p.sorted_ids ? p.sorted_ids[ch.row0 + t] : ch.row0 + t;
-            if (sid >= 0 && sid < p.numel_valid)
+            if (sid >= 0 && sid < p.numel_valid && (int64_t)nt * TILE_N + n_local < p.n_store)
               p.C[(int64_t)(p.out_by_position ? ch.row0 + t : sid) * p.n_store + (int64_t)nt * TILE_N + n_local] =
                   __float2bfloat16_rn(0.f);
           }
@@ -686,94 +754,149 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         }
       } else {
         // ---------------- block-scaled modes: promotion once per K block, sums in registers ----------------
-        // This warp owns the columns [col_begin, col_begin + 16 * my_p) of its 32 lanes, for the gate and the up
-        // tile alike.  Their fp32 running sums stay in registers over the whole K loop (NP pieces of 16 columns at
-        // most; the piece loop is unrolled and a piece beyond the chunk's width is skipped), so tensor memory holds
-        // nothing but partial buffers and a K block costs one tensor-memory load per piece.
+        // This warp owns the columns [col_begin, col_begin + 16 * my_p) of its 32 lanes.  Their fp32 running sums
+        // stay in registers over the whole K loop (NP pieces of 16 columns at most; the piece loop is unrolled and
+        // a piece beyond the chunk's width is skipped), so tensor memory holds nothing but partial buffers and a
+        // K block costs one tensor-memory load per piece.
         constexpr int NP = (A_ROWS / 16 + 3) / 4;
-        float acc[NUM_W][NP][16];
-#pragma unroll
-        for (int w = 0; w < NUM_W; ++w)
-#pragma unroll
-          for (int pc = 0; pc < NP; ++pc)
-#pragma unroll
-            for (int j = 0; j < 16; ++j) acc[w][pc][j] = 0.f;
+        float acc[NP][16];
         // Addresses of this item, formed once: the loops below only add constants to them.  Ring positions
         // (scale slot, partial buffer and its phase) are carried as counters instead of being divided out of
         // the step numbers.
         const uint32_t part0 = tmem_base + lane_off + (uint32_t)col_begin;
-        const uint32_t sc0 = smem_u32(&sm.sc[0][0][0]) + (uint32_t)col_begin * 4u;
-        const uint32_t full0 = smem_u32(&sm.tmem_full[0]), empty0 = smem_u32(&sm.tmem_empty[0]);
+        const uint32_t sc0 = smem_u32(&sm.sc[0][0]) + (uint32_t)col_begin * 4u;
+        const uint32_t done0 = smem_u32(&sm.done[0]), empty0 = smem_u32(&sm.tmem_empty[0]);
+        const uint32_t wait_ns = my_p > 0 ? 32u : 256u;   // a warp without columns only has to keep step
+        // this thread's column of the staging tile: row = token, 2 bytes per output channel.  Plain loads and
+        // stores (no volatile asm), so that the compiler can overlap the sixteen tokens of a piece; the barrier
+        // operations between the phases are compiler barriers as well.
+        __nv_bfloat16 *const stg_mine = reinterpret_cast<__nv_bfloat16 *>(&sm.staging[0]) + col_begin * TILE_N + n_local;
 #pragma unroll 1
-        for (int kb = 0; kb < KB; ++kb) {
-          const uint32_t sc_step = sc0 + sc_slot * (uint32_t)(NUM_W * A_ROWS * 4);
-          sc_slot = sc_slot + 1 == (uint32_t)SC_SLOTS ? 0u : sc_slot + 1;
+        for (int ph = 0; ph < PHASES; ++ph) {
 #pragma unroll
-          for (int w = 0; w < NUM_W; ++w) {
-            const uint32_t b = buf, aph = buf_ph;
+          for (int pc = 0; pc < NP; ++pc)
+#pragma unroll
+            for (int j = 0; j < 16; ++j) acc[pc][j] = 0.f;
+#pragma unroll 1
+          for (int kb = 0; kb < KB; ++kb) {
+            const uint32_t sc_step = sc0 + sc_slot * (uint32_t)(A_ROWS * 4);
+            sc_slot = sc_slot + 1 == (uint32_t)SC_SLOTS ? 0u : sc_slot + 1;
+            const uint32_t b = buf;
             buf = buf + 1 == (uint32_t)NBUF ? 0u : buf + 1;
-            buf_ph ^= buf == 0u ? 1u : 0u;
-            // The scale products of this step were written to shared memory before the stage's full
+            const uint32_t dn = step & (uint32_t)(ND - 1), dph = (step >> 4) & 1u;
+            ++step;
+            // The scale products of this step were written to shared memory before the weight stage's full
             // barrier completed, which the MMA thread observed before it issued the MMAs whose
             // completion this wait observes.  Warp-uniform outcome: the accesses below are warp-collective.
-            if (!__all_sync(0xffffffffu, mbar_wait_addr(sm, full0 + 8u * b, aph, p.status, 5))) { ok = false; break; }
+            if (!ready && !__all_sync(0xffffffffu, mbar_wait_addr(sm, done0 + 8u * dn, dph, p.status, 5, wait_ns))) { ok = false; break; }
             tc_fence_after();
+            // an early look at the next step's barrier: the answer arrives while this step's columns are promoted
+            // (a barrier round trip takes more than a hundred cycles even when the phase has long completed)
+            const bool next_done = mbar_test_addr(done0 + 8u * (step & (uint32_t)(ND - 1)), (step >> 4) & 1u);
             const uint32_t part = part0 + b * (uint32_t)A_ROWS;
+            if (NP == 2 && my_p >= 2) {
+              // two pieces in one load (a load stalls the warp for its whole round trip, whatever its width;
+              // with three pieces of sums per thread the registers do not allow it)
+              uint32_t raw[32];
+              tmem_ld32(part, raw);
+              tmem_ld_wait();
+              promote<16>(&raw[0], &acc[0][0], sc_step);
+              promote<16>(&raw[16], &acc[NP > 1 ? 1 : 0][0], sc_step + 64u);
 #pragma unroll
-            for (int pc = 0; pc < NP; ++pc) {
-              if (pc < my_p) {
-                uint32_t raw[16];
-                tmem_ld16(part + pc * 16, raw);
-                tmem_ld_wait();
-                promote<16>(raw, &acc[w][pc][0], sc_step + (uint32_t)(w * A_ROWS * 4 + pc * 64));
+              for (int pc = 2; pc < NP; ++pc) {
+                if (pc < my_p) {
+                  uint32_t r16[16];
+                  tmem_ld16(part + pc * 16, r16);
+                  tmem_ld_wait();
+                  promote<16>(r16, &acc[pc][0], sc_step + (uint32_t)(pc * 64));
+                }
+              }
+            } else {
+#pragma unroll
+              for (int pc = 0; pc < NP; ++pc) {
+                if (pc < my_p) {
+                  uint32_t r16[16];
+                  tmem_ld16(part + pc * 16, r16);
+                  tmem_ld_wait();
+                  promote<16>(r16, &acc[pc][0], sc_step + (uint32_t)(pc * 64));
+                }
               }
             }
+            ready = __all_sync(0xffffffffu, next_done);
             // every load of the partial has completed: hand the buffer back to the MMA warp
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_addr(empty0 + 8u * b);
           }
           if (!ok) break;
+          if (MODE == GEMM_GATE_UP && ph == 0) {
+            // End of the gate pass: bf16(gate) goes to this thread's column of the staging tile and is read back by
+            // the same thread after the up pass.  The rows may still be in use by the row stores of the previous
+            // item's epilogue, by any warp (the split of the rows over the column groups follows the chunk's
+            // width): all promotion warps meet first.
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.isync);
+            if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.isync, iph, p.status, 8))) { ok = false; break; }
+            iph ^= 1u;
+#pragma unroll
+            for (int pc = 0; pc < NP; ++pc) {
+              if (pc < my_p) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                  float gte = acc[pc][j];
+                  if (p.weight_mode == LO_WEIGHT_FP32)
+                    gte *= __shfl_sync(0xffffffffu, NPF > 1 && (pc >> 1) ? wgt_r[NPF - 1] : wgt_r[0], (pc & 1) * 16 + j);
+                  stg_mine[(pc * 16 + j) * TILE_N] = __float2bfloat16_rn(gte);
+                }
+              }
+            }
+          }
         }
         if (!ok) break;
 
         // ------------------------------ epilogue -------------------------------
         // One rolled loop over the warp's pieces: the body always works on piece 0 of the register sums and the
         // remaining pieces move down one place afterwards (registers cannot be indexed by a loop counter, and an
-        // epilogue unrolled over the pieces would be fetched cold once per item).
+        // epilogue unrolled over the pieces would be fetched cold once per item).  Outputs go through the staging
+        // tile so that global memory sees whole rows: a thread holds one output channel of 16 tokens, a row of the
+        // output is 128 channels of one token.
         if constexpr (MODE == GEMM_GATE_UP) {
           const int64_t I = (int64_t)p.n_tiles * TILE_N;
           uint32_t(*amax_tab)[A_ROWS] = sm.amax[item_par];
 #pragma unroll 1
           for (int pc = 0; pc < my_p; ++pc) {
-            float *gv = &acc[0][0][0], *uv = &acc[NUM_W - 1][0][0];
-            // Pass A: act = bf16(bf16(silu(bf16(gate))) * bf16(up)) in place of the gate sums; maximum of |act|
+            float *av = &acc[0][0];
+            const __nv_bfloat16 *gs = stg_mine + pc * 16 * TILE_N;
+            // Pass A: act = bf16(bf16(silu(bf16(gate))) * bf16(up)) in place of the up sums; maximum of |act|
             // over this warp's 32 output columns, lane j keeps the one of token j.
+            float gte[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) gte[j] = __bfloat162float(gs[j * TILE_N]);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float up = av[j];
+              if (p.weight_mode == LO_WEIGHT_FP32)
+                up *= __shfl_sync(0xffffffffu, NPF > 1 && (pc >> 1) ? wgt_r[NPF - 1] : wgt_r[0], (pc & 1) * 16 + j);
+              up = bf16_round(up);
+              const float sl = bf16_round(__fdiv_rn(gte[j], 1.0f + expf(-gte[j])));
+              av[j] = bf16_round(sl * up);
+            }
             uint32_t own = 0u;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              float gte = gv[j], up = uv[j];
-              if (p.weight_mode == LO_WEIGHT_FP32) {
-                const float wgt = __shfl_sync(0xffffffffu, NPF > 1 && (pc >> 1) ? wgt_r[NPF - 1] : wgt_r[0], (pc & 1) * 16 + j);
-                gte *= wgt;
-                up *= wgt;
-              }
-              gte = bf16_round(gte);
-              up = bf16_round(up);
-              const float sl = bf16_round(__fdiv_rn(gte, 1.0f + expf(-gte)));
-              const float a = bf16_round(sl * up);
-              gv[j] = a;
-              const uint32_t m = __reduce_max_sync(0xffffffffu, __float_as_uint(a) & 0x7fffffffu);
+              const uint32_t m = __reduce_max_sync(0xffffffffu, __float_as_uint(av[j]) & 0x7fffffffu);
               if (j == lane) own = m;
             }
             if (lane < 16) amax_tab[q][col_begin + pc * 16 + lane] = own;
             // the four warps of this column group exchange their maxima (the table alternates between two
-            // copies from item to item; the pieces of one item use different entries)
+            // copies from item to item; the pieces of one item use different entries); every gate value of the
+            // piece has been read when they have met
             mbar_arrive(&sm.esync[cg]);
             if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.esync[cg], eph, p.status, 9))) { ok = false; break; }
             eph ^= 1u;
             // Pass B: lane j (< 16) forms the group scale of token j of the piece, amax / 127; every thread then
-            // quantises its column of the 16 tokens: q = trunc(clamp(act / scale)).
+            // quantises its column of the 16 tokens, q = trunc(clamp(act / scale)), into byte n of the token's
+            // staging row.
             float scale_r = 1.f;
             const int t_own = col_begin + pc * 16 + (lane & 15);
             {
@@ -781,49 +904,80 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
               scale_r = __fdiv_rn(fmaxf(__uint_as_float(m), p.act_eps), 127.0f);
               if (q == 0 && lane < 16 && t_own < ch.rows) p.act_s[((int64_t)ch.row0 + t_own) * p.n_tiles + nt] = scale_r;
             }
+            int8_t *qs = reinterpret_cast<int8_t *>(&sm.staging[0]) + (col_begin + pc * 16) * OUT_ROW_BYTES + n_local;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              const int t = col_begin + pc * 16 + j;
               const float scale = __shfl_sync(0xffffffffu, scale_r, j);
-              if (t < ch.rows) {
-                float r = __fdiv_rn(gv[j], scale);
-                r = fminf(fmaxf(r, -128.0f), 127.0f);
-                p.act_q[((int64_t)ch.row0 + t) * I + (int64_t)nt * TILE_N + n_local] = (int8_t)__float2int_rz(r);
-              }
+              float r = __fdiv_rn(av[j], scale);
+              r = fminf(fmaxf(r, -128.0f), 127.0f);
+              qs[j * OUT_ROW_BYTES] = (int8_t)__float2int_rz(r);
             }
-#pragma unroll
-            for (int w = 0; w < NUM_W; ++w)
-#pragma unroll
-              for (int pp = 0; pp + 1 < NP; ++pp)
-#pragma unroll
-                for (int j = 0; j < 16; ++j) acc[w][pp][j] = acc[w][pp + 1][j];
-          }
-          if (!ok) break;
-          item_par ^= 1u;
-        } else {
-#pragma unroll 1
-          for (int pc = 0; pc < my_p; ++pc) {
-            const float *av = &acc[0][0][0];
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const int32_t sid = __shfl_sync(0xffffffffu, NPF > 1 && (pc >> 1) ? sid_r[NPF - 1] : sid_r[0], (pc & 1) * 16 + j);
-              const float wgt = __shfl_sync(0xffffffffu, NPF > 1 && (pc >> 1) ? wgt_r[NPF - 1] : wgt_r[0], (pc & 1) * 16 + j);
-              if (sid >= 0) {
-                float v = av[j];
-                if (p.weight_mode == LO_WEIGHT_FP32) {
-                  v = v * wgt;
-                } else if (p.weight_mode == LO_WEIGHT_BF16_PRODUCT) {
-                  v = bf16_round(v) * bf16_round(wgt);
-                }
-                if ((int64_t)nt * TILE_N + n_local < p.n_store)
-                  p.C[(int64_t)sid * p.n_store + (int64_t)nt * TILE_N + n_local] = __float2bfloat16_rn(v);
+            mbar_arrive(&sm.esync[cg]);
+            if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.esync[cg], eph, p.status, 10))) { ok = false; break; }
+            eph ^= 1u;
+            // rows out: this warp takes tokens 4q .. 4q+3 of the piece, eight lanes x 16 bytes per row
+            {
+              const int t = col_begin + pc * 16 + 4 * q + (lane >> 3);
+              if (t < ch.rows) {
+                const uint4 v = *reinterpret_cast<const uint4 *>(&sm.staging[t * OUT_ROW_BYTES + (lane & 7) * 16]);
+                *reinterpret_cast<uint4 *>(p.act_q + ((int64_t)ch.row0 + t) * I + (int64_t)nt * TILE_N + (lane & 7) * 16) = v;
               }
             }
 #pragma unroll
             for (int pp = 0; pp + 1 < NP; ++pp)
 #pragma unroll
-              for (int j = 0; j < 16; ++j) acc[0][pp][j] = acc[0][pp + 1][j];
+              for (int j = 0; j < 16; ++j) acc[pp][j] = acc[pp + 1][j];
           }
+          if (!ok) break;
+          item_par ^= 1u;
+        } else {
+          // the staging rows may still be read by the row stores of the previous item, by any warp (the split of
+          // the rows over the column groups follows the chunk's width): all promotion warps meet first
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sm.isync);
+          if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.isync, iph, p.status, 8))) { ok = false; break; }
+          iph ^= 1u;
+          const bool vec_ok = (p.n_store & 7) == 0;
+#pragma unroll 1
+          for (int pc = 0; pc < my_p; ++pc) {
+            const float *av = &acc[0][0];
+            __nv_bfloat16 *os = stg_mine + pc * 16 * TILE_N;
+            const int32_t sid_u = NPF > 1 && (pc >> 1) ? sid_r[NPF - 1] : sid_r[0];
+            const float wgt_u = NPF > 1 && (pc >> 1) ? wgt_r[NPF - 1] : wgt_r[0];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float v = av[j];
+              if (p.weight_mode != LO_WEIGHT_NONE) {
+                const float wgt = __shfl_sync(0xffffffffu, wgt_u, (pc & 1) * 16 + j);
+                v = p.weight_mode == LO_WEIGHT_FP32 ? v * wgt : bf16_round(v) * bf16_round(wgt);
+              }
+              os[j * TILE_N] = __float2bfloat16_rn(v);
+            }
+            mbar_arrive(&sm.esync[cg]);
+            if (!__all_sync(0xffffffffu, mbar_wait(sm, &sm.esync[cg], eph, p.status, 9))) { ok = false; break; }
+            eph ^= 1u;
+            // rows out: this warp takes tokens 4q .. 4q+3 of the piece, two rows per step, sixteen lanes x 16 bytes per row
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              const int tp = 4 * q + 2 * i + (lane >> 4);                       // token of the piece
+              const int32_t sid = __shfl_sync(0xffffffffu, sid_u, (pc & 1) * 16 + tp);
+              const int64_t n0 = (int64_t)nt * TILE_N + (lane & 15) * 8;
+              if (sid >= 0 && n0 < p.n_store) {
+                const uint8_t *src = &sm.staging[(col_begin + pc * 16 + tp) * OUT_ROW_BYTES + (lane & 15) * 16];
+                __nv_bfloat16 *dst = p.C + (int64_t)sid * p.n_store + n0;
+                if (vec_ok) {
+                  *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(src);
+                } else {
+                  for (int e = 0; e < 8 && n0 + e < p.n_store; ++e) dst[e] = reinterpret_cast<const __nv_bfloat16 *>(src)[e];
+                }
+              }
+            }
+#pragma unroll
+            for (int pp = 0; pp + 1 < NP; ++pp)
+#pragma unroll
+              for (int j = 0; j < 16; ++j) acc[pp][j] = acc[pp + 1][j];
+          }
+          if (!ok) break;
         }
       }
     }
@@ -889,6 +1043,10 @@ int make_tile_map(CUtensorMap *map, const int8_t *base, int64_t rows, int64_t K,
 template <int MODE, int A_ROWS>
 int launch_mode(const GemmArgs &a, cudaStream_t stream) {
   using SM = Smem<MODE, A_ROWS>;
+  static_assert(sizeof(SM) + 1024 <= SMEM_LIMIT, "shared-memory layout exceeds what a CTA can be given");
+  static_assert(ND == 16, "the promotion warps take the completion-ring phase from bit 4 of the step count");
+  static_assert(Cfg<MODE, A_ROWS>::NW >= 4, "too few weight stages");
+  static_assert(Cfg<MODE, A_ROWS>::NW < ND && Cfg<MODE, A_ROWS>::NA < ND && Cfg<MODE, A_ROWS>::NBUF < ND, "completion ring too short");
   const size_t smem_bytes = sizeof(SM) + 1024;
   // the attribute belongs to the (kernel, device) pair: set it once per device this thread launches on
   static thread_local uint64_t configured_devices = 0;
@@ -936,11 +1094,11 @@ int launch_grouped_gemm(GemmMode mode, const GemmArgs &a, cudaStream_t stream) {
   const int cap = a.max_chunk_rows <= 0 ? T_MAX : a.max_chunk_rows;
   if (mode == GEMM_GATE_UP) {
     LO_REQUIRE(a.n_rows_per_expert == 2 * (int64_t)a.n_tiles * TILE_N, "grouped gemm: gate_up needs N = 2*I");
-    // two sets of running sums and two partial buffers of `cap` columns each: 128 is the widest that fits
-    LO_REQUIRE(cap <= T_MAX, "grouped gemm: gate_up chunks hold at most 128 rows");
+    LO_REQUIRE(cap <= T_WIDE, "grouped gemm: block-scaled chunks hold at most 160 rows");
     if (cap <= 32) return launch_mode<GEMM_GATE_UP, 32>(a, stream);
     if (cap <= 64) return launch_mode<GEMM_GATE_UP, 64>(a, stream);
-    return launch_mode<GEMM_GATE_UP, 128>(a, stream);
+    if (cap <= 128) return launch_mode<GEMM_GATE_UP, 128>(a, stream);
+    return launch_mode<GEMM_GATE_UP, T_WIDE>(a, stream);
   }
   LO_REQUIRE((int64_t)a.n_tiles * TILE_N >= a.n_rows_per_expert && (int64_t)(a.n_tiles - 1) * TILE_N < a.n_rows_per_expert,
              "grouped gemm: tile count mismatch");
@@ -951,7 +1109,7 @@ int launch_grouped_gemm(GemmMode mode, const GemmArgs &a, cudaStream_t stream) {
     if (cap <= 128) return launch_mode<GEMM_CHANNEL, 128>(a, stream);
     return launch_mode<GEMM_CHANNEL, 256>(a, stream);
   }
-  LO_REQUIRE(cap <= T_WIDE, "grouped gemm: block-scaled single-matrix chunks hold at most 160 rows");
+  LO_REQUIRE(cap <= T_WIDE, "grouped gemm: block-scaled chunks hold at most 160 rows");
   if (cap <= 32) return launch_mode<GEMM_SINGLE, 32>(a, stream);
   if (cap <= 64) return launch_mode<GEMM_SINGLE, 64>(a, stream);
   if (cap <= 128) return launch_mode<GEMM_SINGLE, 128>(a, stream);

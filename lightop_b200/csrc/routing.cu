@@ -479,73 +479,6 @@ __global__ void chunks_from_blocks_kernel(const int32_t *__restrict__ expert_ids
 }
 
 
-// Second chunk table with another chunk size, derived from the table the align kernel wrote (whose `pad` field
-// counts the chunks of the same expert that follow, so the head chunk of an expert finds the tail directly).
-// One CTA; the new chunks keep the expert order (block-wide exclusive scan of the new chunk counts, 1024 table
-// entries per round).
-__global__ void __launch_bounds__(1024) rechunk_kernel(const Chunk *__restrict__ in, const int32_t *__restrict__ n_in,
-                                                       int chunk_max, Chunk *__restrict__ out,
-                                                       int32_t *__restrict__ n_out, int64_t capacity) {
-  __shared__ int32_t warp_tot[32];
-  __shared__ int32_t round_total;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int n = *n_in;
-  int carry = 0;
-  for (int base = 0; base < n; base += 1024) {
-    const int i = base + tid;
-    int c = 0, per = 0, emit = 0;
-    Chunk head{};
-    if (i < n) {
-      head = in[i];
-      const bool is_head = i == 0 || in[i - 1].pad == 0;
-      if (is_head) {
-        const int t = i + head.pad < n ? i + head.pad : n - 1;
-        const Chunk tail = in[t];
-        c = tail.row0 + tail.rows - head.row0;
-        if (c > 0) {
-          const int nch = (c + chunk_max - 1) / chunk_max;
-          per = (((c + nch - 1) / nch) + 15) / 16 * 16;
-          emit = (c + per - 1) / per;
-        }
-      }
-    }
-    int a = emit;
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-      const int t = __shfl_up_sync(0xffffffffu, a, off);
-      if (lane >= off) a += t;
-    }
-    if (lane == 31) warp_tot[warp] = a;
-    __syncthreads();
-    if (warp == 0) {
-      int t = warp_tot[lane];
-      const int own = t;
-#pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        const int u = __shfl_up_sync(0xffffffffu, t, off);
-        if (lane >= off) t += u;
-      }
-      warp_tot[lane] = t - own;
-      if (lane == 31) round_total = t;
-    }
-    __syncthreads();
-    int ci = carry + warp_tot[warp] + a - emit;
-    for (int k = 0, r = 0; k < emit; ++k, r += per, ++ci) {
-      if (ci < capacity) {
-        Chunk ch;
-        ch.expert = head.expert;
-        ch.row0 = head.row0 + r;
-        ch.rows = c - r < per ? c - r : per;
-        ch.pad = emit - 1 - k;
-        out[ci] = ch;
-      }
-    }
-    carry += round_total;
-    __syncthreads();
-  }
-  if (tid == 0) *n_out = carry < capacity ? carry : (int32_t)capacity;
-}
-
 }  // namespace
 
 int launch_align(const void *topk_ids, int ids_dtype, int64_t numel, int num_experts, int block_size,
@@ -660,12 +593,3 @@ extern "C" int lo_moe_align_block_size(const void *topk_ids, int ids_dtype, int6
                           sorted_capacity, expert_ids, expert_ids_capacity, num_tokens_post_pad, nullptr, nullptr,
                           0, nullptr, 128, static_cast<cudaStream_t>(stream));
 }
-
-namespace lo {
-int launch_rechunk(const Chunk *chunks, const int32_t *num_chunks, int chunk_max, Chunk *out, int32_t *num_out,
-                   int64_t capacity, cudaStream_t stream) {
-  rechunk_kernel<<<1, 1024, 0, stream>>>(chunks, num_chunks, chunk_max, out, num_out, capacity);
-  LO_LAUNCH_OK("rechunk_kernel");
-  return LO_OK;
-}
-}  // namespace lo
