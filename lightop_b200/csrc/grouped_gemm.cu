@@ -358,6 +358,20 @@ __device__ __forceinline__ void promote(const uint32_t *raw, float *acc, uint32_
 }
 
 __device__ __forceinline__ float bf16_round(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+// Reciprocal refined by one Newton step, and the quotient a / b from it with the remainder folded back in
+// (q = a*y, then q + (a - b*q)*y): the IEEE round-to-nearest quotient for operands whose quotient and reciprocal
+// are normal numbers, which holds for every division of the epilogues (denominators in [1, 1e38] or a group
+// scale of at least 1e-10 / 127).  Inline, so the sixteen divisions of a piece overlap; the library division is
+// a subroutine call each, and two of them per output made the epilogue a fifth of the kernel's time.
+__device__ __forceinline__ float rcp_refined(float b) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(b));
+  return __fmaf_rn(__fmaf_rn(-b, y, 1.0f), y, y);
+}
+__device__ __forceinline__ float div_by(float a, float b, float y) {
+  const float q = __fmul_rn(a, y);
+  return __fmaf_rn(__fmaf_rn(-b, q, a), y, q);
+}
 
 struct KParams {
   const float *a_scale;     // [positions, KB]
@@ -878,7 +892,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
               if (p.weight_mode == LO_WEIGHT_FP32)
                 up *= __shfl_sync(0xffffffffu, NPF > 1 && (pc >> 1) ? wgt_r[NPF - 1] : wgt_r[0], (pc & 1) * 16 + j);
               up = bf16_round(up);
-              const float sl = bf16_round(__fdiv_rn(gte[j], 1.0f + expf(-gte[j])));
+              // 1 + exp(-gate) capped below the fp32 maximum: the quotient is then zero instead of an invalid
+              // operation in the refinement (the exact quotient would be -0 or a number below 1e-36)
+              const float den = fminf(1.0f + expf(-gte[j]), 1e38f);
+              const float sl = bf16_round(div_by(gte[j], den, rcp_refined(den)));
               av[j] = bf16_round(sl * up);
             }
             uint32_t own = 0u;
@@ -897,18 +914,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
             // Pass B: lane j (< 16) forms the group scale of token j of the piece, amax / 127; every thread then
             // quantises its column of the 16 tokens, q = trunc(clamp(act / scale)), into byte n of the token's
             // staging row.
-            float scale_r = 1.f;
+            float scale_r = 1.f, rcp_r = 1.f;
             const int t_own = col_begin + pc * 16 + (lane & 15);
             {
               const uint32_t m = max(max(amax_tab[0][t_own], amax_tab[1][t_own]), max(amax_tab[2][t_own], amax_tab[3][t_own]));
               scale_r = __fdiv_rn(fmaxf(__uint_as_float(m), p.act_eps), 127.0f);
+              rcp_r = rcp_refined(scale_r);
               if (q == 0 && lane < 16 && t_own < ch.rows) p.act_s[((int64_t)ch.row0 + t_own) * p.n_tiles + nt] = scale_r;
             }
             int8_t *qs = reinterpret_cast<int8_t *>(&sm.staging[0]) + (col_begin + pc * 16) * OUT_ROW_BYTES + n_local;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const float scale = __shfl_sync(0xffffffffu, scale_r, j);
-              float r = __fdiv_rn(av[j], scale);
+              float r = div_by(av[j], scale, __shfl_sync(0xffffffffu, rcp_r, j));
               r = fminf(fmaxf(r, -128.0f), 127.0f);
               qs[j * OUT_ROW_BYTES] = (int8_t)__float2int_rz(r);
             }
@@ -947,10 +965,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               float v = av[j];
-              if (p.weight_mode != LO_WEIGHT_NONE) {
-                const float wgt = __shfl_sync(0xffffffffu, wgt_u, (pc & 1) * 16 + j);
-                v = p.weight_mode == LO_WEIGHT_FP32 ? v * wgt : bf16_round(v) * bf16_round(wgt);
-              }
+              if (p.weight_mode == LO_WEIGHT_FP32) v *= __shfl_sync(0xffffffffu, wgt_u, (pc & 1) * 16 + j);
               os[j * TILE_N] = __float2bfloat16_rn(v);
             }
             mbar_arrive(&sm.esync[cg]);
@@ -961,14 +976,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
             for (int i = 0; i < 2; ++i) {
               const int tp = 4 * q + 2 * i + (lane >> 4);                       // token of the piece
               const int32_t sid = __shfl_sync(0xffffffffu, sid_u, (pc & 1) * 16 + tp);
+              // bf16-product order: bf16(sum) * bf16(w), rounded once more: one packed multiply per two outputs
+              const __nv_bfloat162 w2 = __float2bfloat162_rn(__shfl_sync(0xffffffffu, wgt_u, (pc & 1) * 16 + tp));
               const int64_t n0 = (int64_t)nt * TILE_N + (lane & 15) * 8;
               if (sid >= 0 && n0 < p.n_store) {
                 const uint8_t *src = &sm.staging[(col_begin + pc * 16 + tp) * OUT_ROW_BYTES + (lane & 15) * 16];
                 __nv_bfloat16 *dst = p.C + (int64_t)sid * p.n_store + n0;
+                uint4 v = *reinterpret_cast<const uint4 *>(src);
+                if (p.weight_mode == LO_WEIGHT_BF16_PRODUCT) {
+                  __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&v);
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) h[e] = __hmul2(h[e], w2);
+                }
                 if (vec_ok) {
-                  *reinterpret_cast<uint4 *>(dst) = *reinterpret_cast<const uint4 *>(src);
+                  *reinterpret_cast<uint4 *>(dst) = v;
                 } else {
-                  for (int e = 0; e < 8 && n0 + e < p.n_store; ++e) dst[e] = reinterpret_cast<const __nv_bfloat16 *>(src)[e];
+                  for (int e = 0; e < 8 && n0 + e < p.n_store; ++e) dst[e] = reinterpret_cast<const __nv_bfloat16 *>(&v)[e];
                 }
               }
             }
