@@ -64,9 +64,8 @@ constexpr int TILE_N = 128;      // weight rows per accumulator (MMA M)
 constexpr int TILE_K = 128;      // int8 elements (= bytes) per K block
 constexpr int T_MAX = 128;       // default bound of the rows of a chunk
 constexpr int T_WIDE = 160;      // widest block-scaled chunk: three partial buffers of 160 columns fill tensor memory
-constexpr int NUM_THREADS = 640;
 constexpr int FIRST_EPI_WARP = 4;
-constexpr int EPI_WARPS = 16;
+constexpr int MAX_NCG = 5;
 constexpr int W_TILE_BYTES = TILE_N * TILE_K;   // 16 KiB
 constexpr int OUT_ROW_BYTES = TILE_N * 2;       // one token's 128 outputs as bf16 in the staging tile
 constexpr uint32_t TMEM_COLS = 512;
@@ -79,6 +78,13 @@ constexpr int SMEM_LIMIT = 227 * 1024;          // dynamic shared memory a CTA c
 template <int MODE, int A_ROWS> struct Cfg {
   // gate_up: an item is two passes over K on the same chunk, first the gate tile, then the up tile
   static constexpr int PHASES = MODE == GEMM_GATE_UP ? 2 : 1;
+  // Column groups: the chunk's tokens are dealt, in pieces of 16, to this many sets of four promotion warps (one
+  // warp per lane quarter of tensor memory).  Five groups keep a group at two pieces for chunks of up to 160
+  // tokens (the group with the most pieces paces the K loop); the CTA then has 24 warps and 80 registers per
+  // thread.  Narrow chunks use four groups: more warps would only add idle ones that have to keep step.
+  static constexpr int NCG = A_ROWS > 64 ? 5 : 4;
+  static constexpr int EPI_WARPS = 4 * NCG;
+  static constexpr int NUM_THREADS = (FIRST_EPI_WARP + EPI_WARPS) * 32;
   static constexpr int A_TILE_BYTES = A_ROWS * TILE_K;
   // Two rings.  Activation tiles come from L2 (the chunk's rows are read by every output tile of the expert): a
   // slot is refilled only after the MMAs that read it have completed, so the ring has to cover the load latency
@@ -119,7 +125,7 @@ template <int MODE, int A_ROWS> struct Smem {
   uint64_t done[ND];
   uint64_t tmem_full[C::NBUF];             // per-channel mode: the accumulator of an item is complete
   uint64_t tmem_empty[C::NBUF];
-  uint64_t esync[4];                       // rendezvous of the 128 epilogue threads of a column group
+  uint64_t esync[MAX_NCG];                 // rendezvous of the 128 epilogue threads of a column group
   uint64_t isync;                          // rendezvous of all promotion warps, once per item
   uint32_t tmem_base;
   volatile int abort_flag;
@@ -310,19 +316,6 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "r"(taddr)
       : "memory");
 }
-// 32 consecutive tensor-memory columns of this thread's lane.
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 // Packed fp32 pair arithmetic (two IEEE round-to-nearest operations per instruction).
 __device__ __forceinline__ uint64_t pack2(float lo, float hi) {
@@ -403,7 +396,7 @@ struct AMaps {
 __device__ __forceinline__ int a_map_index(int T) { return T <= 16 ? 0 : (T <= 32 ? 1 : (T <= 64 ? 2 : 3)); }
 
 template <int MODE, int A_ROWS>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__((Cfg<MODE, A_ROWS>::NUM_THREADS), 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_constant__ AMaps a_maps, const KParams p) {
   using SM = Smem<MODE, A_ROWS>;
   using CF = Cfg<MODE, A_ROWS>;
@@ -412,6 +405,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
   constexpr int NA = CF::NA;
   constexpr int NBUF = CF::NBUF;
   constexpr int PHASES = CF::PHASES;
+  constexpr int NCG = CF::NCG;
+  constexpr int EPI_WARPS = CF::EPI_WARPS;
   extern __shared__ uint8_t smem_raw[];
   SM &sm = *reinterpret_cast<SM *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -433,7 +428,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       mbar_init(&sm.tmem_full[b], 1);
       mbar_init(&sm.tmem_empty[b], EPI_WARPS);
     }
-    for (int b = 0; b < 4; ++b) mbar_init(&sm.esync[b], 128);
+    for (int b = 0; b < NCG; ++b) mbar_init(&sm.esync[b], 128);
     mbar_init(&sm.isync, EPI_WARPS);
     sm.abort_flag = 0;
     fence_barrier_init();
@@ -588,70 +583,57 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       }
     } else if (MODE != GEMM_CHANNEL) {
       // ========================= scale producer (warp 2) ====================
-      // Thread g owns tokens g, g + 32, ... of the chunk.  Token scales and weight-block scales are
-      // read four K blocks at a time and one group ahead, so the loop never waits on memory.
+      // Thread g owns tokens g, g + 32, ... of the chunk.  The scales of a K block are fetched two steps before
+      // they are used (they come from L2: the chunk's scale rows are read by every output tile of the expert), one
+      // value per token and step, which keeps this role to a few registers per token.
       const int g = lane;
       constexpr int NU = (A_ROWS + 31) / 32;
       uint32_t it = 0;
+      int s = 0, slot = 0;
       bool ok = true;
-      const bool vec4 = (KB & 3) == 0;
       const int64_t nblk = (p.n_rows_per_expert + TILE_N - 1) / TILE_N;
       for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
         const Chunk ch = p.chunks[item / p.n_tiles];
         const int nt = (int)(item % p.n_tiles);
         if (ch.expert < 0) continue;
         const int T = (ch.rows + 15) & ~15;
-        const float *as_ptr[NU];
-        bool live[NU];
+        const float *as_base = p.a_scale + (int64_t)ch.row0 * KB;
+        uint32_t as_off[NU];          // offset of the token's scale row; a token beyond the chunk reads row 0
 #pragma unroll
-        for (int u = 0; u < NU; ++u) {
-          const int t = g + u * 32;
-          live[u] = t < ch.rows;
-          as_ptr[u] = p.a_scale + (int64_t)(ch.row0 + (live[u] ? t : 0)) * KB;
-        }
+        for (int u = 0; u < NU; ++u) as_off[u] = (uint32_t)((g + u * 32 < ch.rows ? g + u * 32 : 0) * KB);
         for (int ph = 0; ph < PHASES && ok; ++ph) {
           const float *bs_ptr = p.b_scale + ((int64_t)ch.expert * nblk + nt + (int64_t)ph * p.n_tiles) * KB;
-          float4 cur_a[NU], nxt_a[NU], cur_b, nxt_b;
-          const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
-          if (vec4) {
+          float a0[NU], a1[NU], b0, b1;     // scales of this step and of the next one
 #pragma unroll
-            for (int u = 0; u < NU; ++u) nxt_a[u] = live[u] ? __ldg(reinterpret_cast<const float4 *>(as_ptr[u])) : zero4;
-            nxt_b = __ldg(reinterpret_cast<const float4 *>(bs_ptr));
+          for (int u = 0; u < NU; ++u) {
+            a0[u] = __ldg(as_base + as_off[u]);
+            a1[u] = KB > 1 ? __ldg(as_base + as_off[u] + 1) : 0.f;
           }
+          b0 = __ldg(bs_ptr);
+          b1 = KB > 1 ? __ldg(bs_ptr + 1) : 0.f;
           for (int kb = 0; kb < KB; ++kb, ++it) {
-            const int s = it % NW;
-            float as_now[NU], bs_now;
-            if (vec4) {
-              if ((kb & 3) == 0) {
+            float as_now[NU];
+            const float bs_now = b0;
+            b0 = b1;
+            if (kb + 2 < KB) b1 = __ldg(bs_ptr + kb + 2);
 #pragma unroll
-                for (int u = 0; u < NU; ++u) {
-                  cur_a[u] = nxt_a[u];
-                  if (kb + 4 < KB && live[u]) nxt_a[u] = __ldg(reinterpret_cast<const float4 *>(as_ptr[u] + kb + 4));
-                }
-                cur_b = nxt_b;
-                if (kb + 4 < KB) nxt_b = __ldg(reinterpret_cast<const float4 *>(bs_ptr + kb + 4));
-              }
-              const int sel = kb & 3;
-#pragma unroll
-              for (int u = 0; u < NU; ++u)
-                as_now[u] = sel == 0 ? cur_a[u].x : (sel == 1 ? cur_a[u].y : (sel == 2 ? cur_a[u].z : cur_a[u].w));
-              bs_now = sel == 0 ? cur_b.x : (sel == 1 ? cur_b.y : (sel == 2 ? cur_b.z : cur_b.w));
-            } else {
-#pragma unroll
-              for (int u = 0; u < NU; ++u) as_now[u] = live[u] ? __ldg(as_ptr[u] + kb) : 0.f;
-              bs_now = __ldg(bs_ptr + kb);
+            for (int u = 0; u < NU; ++u) {
+              as_now[u] = a0[u];
+              a0[u] = a1[u];
+              if (kb + 2 < KB) a1[u] = __ldg(as_base + as_off[u] + kb + 2);
             }
             // the slot of this step is free once the weight stage is (see SC_SLOTS)
             if (it >= (uint32_t)NW &&
                 !__all_sync(0xffffffffu, mbar_wait(sm, &sm.done[(it - NW) % ND], ((it - NW) / ND) & 1u, p.status, 4, 128u))) { ok = false; break; }
-            const int slot = it % SC_SLOTS;
 #pragma unroll
             for (int u = 0; u < NU; ++u) {
               const int t = g + u * 32;
-              if (t < T) sm.sc[slot][t] = __fmul_rn(as_now[u], bs_now);
+              if (t < T) sm.sc[slot][t] = t < ch.rows ? __fmul_rn(as_now[u], bs_now) : 0.f;
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.full_w[s]);
+            s = s + 1 == NW ? 0 : s + 1;
+            slot = slot + 1 == SC_SLOTS ? 0 : slot + 1;
           }
         }
       }
@@ -673,7 +655,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       if (ch.expert < 0) {
         // block of a non-local expert: its output rows are zero
         if (MODE != GEMM_GATE_UP) {
-          for (int t = cg; t < ch.rows; t += 4) {
+          for (int t = cg; t < ch.rows; t += NCG) {
             const int32_t sid = p.sorted_ids ? p.sorted_ids[ch.row0 + t] : ch.row0 + t;
             if (sid >= 0 && sid < p.numel_valid && (int64_t)nt * TILE_N + n_local < p.n_store)
               p.C[(int64_t)(p.out_by_position ? ch.row0 + t : sid) * p.n_store + (int64_t)nt * TILE_N + n_local] =
@@ -682,18 +664,18 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         }
         continue;
       }
-      // The chunk's T columns (a multiple of 16) are dealt to the four column groups in pieces of 16,
-      // as evenly as that allows; a group owns at most two pieces (32 tokens) of a chunk of up to 128 tokens,
-      // three of a chunk of up to 160, four of a chunk of up to 256.
+      // The chunk's T columns (a multiple of 16) are dealt to the column groups in pieces of 16, as evenly as
+      // that allows; a group owns at most two pieces (32 tokens) of a chunk of up to 160 tokens, four of a chunk
+      // of up to 256.
       const int T = (ch.rows + 15) & ~15;
       const int n_pieces = T >> 4;
-      const int my_p = n_pieces / 4 + (cg < (n_pieces & 3) ? 1 : 0);
-      const int col_begin = (cg * (n_pieces / 4) + min(cg, n_pieces & 3)) * 16;
+      const int my_p = n_pieces / NCG + (cg < n_pieces % NCG ? 1 : 0);
+      const int col_begin = (cg * (n_pieces / NCG) + min(cg, n_pieces % NCG)) * 16;
 
       // Row id and routed weight of token col_begin + 32 * u + lane, fetched now so that the latency is
       // hidden behind the K loop; broadcast by shuffle in the epilogue: piece pc of the group is in
       // register set pc / 2, lanes 16 * (pc & 1) .. + 15.
-      constexpr int NPF = A_ROWS > 128 ? 2 : 1;
+      constexpr int NPF = ((A_ROWS / 16 + NCG - 1) / NCG + 1) / 2;   // sets of 32 tokens that cover a group's pieces
       int32_t sid_r[NPF];
       float wgt_r[NPF];
 #pragma unroll
@@ -772,7 +754,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         // stay in registers over the whole K loop (NP pieces of 16 columns at most; the piece loop is unrolled and
         // a piece beyond the chunk's width is skipped), so tensor memory holds nothing but partial buffers and a
         // K block costs one tensor-memory load per piece.
-        constexpr int NP = (A_ROWS / 16 + 3) / 4;
+        constexpr int NP = (A_ROWS / 16 + NCG - 1) / NCG;
         float acc[NP][16];
         // Addresses of this item, formed once: the loops below only add constants to them.  Ring positions
         // (scale slot, partial buffer and its phase) are carried as counters instead of being divided out of
@@ -808,32 +790,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
             // (a barrier round trip takes more than a hundred cycles even when the phase has long completed)
             const bool next_done = mbar_test_addr(done0 + 8u * (step & (uint32_t)(ND - 1)), (step >> 4) & 1u);
             const uint32_t part = part0 + b * (uint32_t)A_ROWS;
-            if (NP == 2 && my_p >= 2) {
-              // two pieces in one load (a load stalls the warp for its whole round trip, whatever its width;
-              // with three pieces of sums per thread the registers do not allow it)
-              uint32_t raw[32];
-              tmem_ld32(part, raw);
-              tmem_ld_wait();
-              promote<16>(&raw[0], &acc[0][0], sc_step);
-              promote<16>(&raw[16], &acc[NP > 1 ? 1 : 0][0], sc_step + 64u);
 #pragma unroll
-              for (int pc = 2; pc < NP; ++pc) {
-                if (pc < my_p) {
-                  uint32_t r16[16];
-                  tmem_ld16(part + pc * 16, r16);
-                  tmem_ld_wait();
-                  promote<16>(r16, &acc[pc][0], sc_step + (uint32_t)(pc * 64));
-                }
-              }
-            } else {
-#pragma unroll
-              for (int pc = 0; pc < NP; ++pc) {
-                if (pc < my_p) {
-                  uint32_t r16[16];
-                  tmem_ld16(part + pc * 16, r16);
-                  tmem_ld_wait();
-                  promote<16>(r16, &acc[pc][0], sc_step + (uint32_t)(pc * 64));
-                }
+            for (int pc = 0; pc < NP; ++pc) {
+              if (pc < my_p) {
+                uint32_t r16[16];
+                tmem_ld16(part + pc * 16, r16);
+                tmem_ld_wait();
+                promote<16>(r16, &acc[pc][0], sc_step + (uint32_t)(pc * 64));
               }
             }
             ready = __all_sync(0xffffffffu, next_done);
@@ -1096,7 +1059,7 @@ int launch_mode(const GemmArgs &a, cudaStream_t stream) {
   p.out_by_position = a.out_by_position;
   const int grid = sm_count();
   if (grid <= 0) return fail(LO_ERR_CUDA, "no CUDA device");
-  LO_CUDA_OK(launch_dependent(grouped_gemm_kernel<MODE, A_ROWS>, dim3(grid), dim3(NUM_THREADS), smem_bytes, stream, wmap,
+  LO_CUDA_OK(launch_dependent(grouped_gemm_kernel<MODE, A_ROWS>, dim3(grid), dim3(Cfg<MODE, A_ROWS>::NUM_THREADS), smem_bytes, stream, wmap,
                               amaps, p));
   return LO_OK;
 }
