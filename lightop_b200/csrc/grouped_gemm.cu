@@ -519,66 +519,61 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       }
     } else if (warp == 1 || warp == 3) {
       // ============================ MMA issuers ===============================
-      // Lane 0 issues; lanes 0, 1 and 2 each poll one of the step's three barriers (weights landed, activations
-      // landed, partial buffer free) in the same instruction.  One commit per step.  A step of this role is a chain
-      // of a hundred dependent scalar instructions and barrier round trips, about a thousand cycles however little
-      // the tensor core has to do, which is more than the 16 KB of weights of a step take to arrive: in the
-      // block-scaled modes two warps share the steps (even ones here, odd ones there; the partials of different
-      // steps are independent and a commit tracks the MMAs of its own thread).  Per-channel mode accumulates an
-      // item's steps into one buffer, in order, so warp 1 issues them all.
-      constexpr int NISS = MODE == GEMM_CHANNEL ? 1 : 2;
+      // A step of this role is a chain of dependent scalar instructions and barrier round trips (a barrier poll
+      // takes more than a hundred cycles even when the phase has long completed), which costs more time than the
+      // 16 KB of weights of a step take to arrive however little the tensor core has to do.  So: lane 0 issues,
+      // lanes 0, 1 and 2 each own one of the step's three barriers (weights landed, activations landed, partial
+      // buffer free) with its ring position and poll it in the same instruction; one commit per step; and in the
+      // block-scaled modes two warps share the steps (even ones here, odd ones there: the partials of different
+      // steps are independent, a commit tracks the MMAs of its own thread, and the ring positions of a warp simply
+      // advance by two).  Per-channel mode accumulates an item's steps into one buffer, in order: warp 1 issues
+      // them all and the buffer ring advances once per item.
+      constexpr uint32_t NISS = MODE == GEMM_CHANNEL ? 1u : 2u;
       const uint32_t which = warp == 1 ? 0u : 1u;
-      uint32_t it = 0;
-      uint32_t sw = 0, par_w = 0, sa = 0, par_a = 0, b = 0, par_b = 0;   // ring positions and their phase parities
-      const uint32_t full_w0 = smem_u32(&sm.full_w[0]), full_a0 = smem_u32(&sm.full_a[0]);
-      const uint32_t tempty0 = smem_u32(&sm.tmem_empty[0]);
-      bool ok = true;
-      for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
-        const Chunk ch = p.chunks[item / p.n_tiles];
-        if (ch.expert < 0) continue;
-        const uint32_t T = (uint32_t)((ch.rows + 15) & ~15);
-        const uint32_t idesc = make_idesc(T);
-        const int steps = PHASES * KB;
-        for (int u = 0; u < steps; ++u, ++it) {
-          if (NISS == 1 ? which != 0u : (it & 1u) != which) {
-            // the other issuer's step: keep the ring positions in step
-            sw = sw + 1 == (uint32_t)NW ? 0u : sw + 1;
-            par_w ^= sw == 0u ? 1u : 0u;
-            sa = sa + 1 == (uint32_t)NA ? 0u : sa + 1;
-            par_a ^= sa == 0u ? 1u : 0u;
-            b = b + 1 == (uint32_t)NBUF ? 0u : b + 1;
-            par_b ^= b == 0u ? 1u : 0u;
-            continue;
-          }
-          // per-channel mode: one int32 accumulator per item, summed over every K block; the buffer is waited for
-          // once, at the item's first step
-          const bool need_buf = MODE != GEMM_CHANNEL || u == 0;
-          const uint32_t bar = lane == 0 ? full_w0 + 8u * sw : (lane == 1 ? full_a0 + 8u * sa : tempty0 + 8u * b);
-          const uint32_t par = lane == 0 ? par_w : (lane == 1 ? par_a : par_b ^ 1u);
-          bool mine = true;
-          if (lane < 2 || (lane == 2 && need_buf)) mine = mbar_wait_addr(sm, bar, par, p.status, 3 + lane, 20u);
-          if (!__all_sync(0xffffffffu, mine)) { ok = false; break; }
-          if (lane == 0) {
-            tc_fence_after();
-            const uint64_t bdesc = make_smem_desc(smem_u32(sm.a[sa]));
-            const uint64_t adesc = make_smem_desc(smem_u32(sm.w[sw]));
-            const uint32_t d = tmem_base + b * (uint32_t)A_ROWS;
+      if (which < NISS) {
+        const uint32_t my_n = lane == 0 ? (uint32_t)NW : (lane == 1 ? (uint32_t)NA : (uint32_t)NBUF);
+        const uint32_t my_base = lane == 0 ? smem_u32(&sm.full_w[0]) : (lane == 1 ? smem_u32(&sm.full_a[0]) : smem_u32(&sm.tmem_empty[0]));
+        // ring position and phase parity of this lane's barrier at this warp's next step (global step index `it`);
+        // a fresh "buffer free" barrier is waited for with the opposite parity
+        uint32_t my_slot = which % my_n;
+        uint32_t my_par = ((which / my_n) & 1u) ^ (lane == 2 ? 1u : 0u);
+        uint32_t it = which, it_base = 0;
+        const uint64_t desc_w0 = make_smem_desc(smem_u32(sm.w[0])), desc_a0 = make_smem_desc(smem_u32(sm.a[0]));
+        bool ok = true;
+        for (int64_t item = blockIdx.x; item < num_items && ok; item += gridDim.x) {
+          const Chunk ch = p.chunks[item / p.n_tiles];
+          if (ch.expert < 0) continue;
+          const uint32_t idesc = make_idesc((uint32_t)((ch.rows + 15) & ~15));
+          const uint32_t steps = (uint32_t)(PHASES * KB);
+          for (uint32_t u = it - it_base; u < steps; u += NISS, it += NISS) {
+            // per-channel mode: the accumulator buffer is waited for at the item's first step only
+            const bool poll = lane < 2 || (lane == 2 && (MODE != GEMM_CHANNEL || u == 0));
+            const bool mine = poll ? mbar_wait_addr(sm, my_base + 8u * my_slot, my_par, p.status, 3 + lane, 20u) : true;
+            if (!__all_sync(0xffffffffu, mine)) { ok = false; break; }
+            const uint32_t sw = __shfl_sync(0xffffffffu, my_slot, 0);
+            const uint32_t sa = __shfl_sync(0xffffffffu, my_slot, 1);
+            const uint32_t b = __shfl_sync(0xffffffffu, my_slot, 2);
+            if (lane == 0) {
+              tc_fence_after();
+              // descriptor start addresses are in 16-byte units
+              const uint64_t adesc = desc_w0 + (uint64_t)(sw * (W_TILE_BYTES >> 4));
+              const uint64_t bdesc = desc_a0 + (uint64_t)(sa * (uint32_t)(CF::A_TILE_BYTES >> 4));
+              const uint32_t d = tmem_base + b * (uint32_t)A_ROWS;
 #pragma unroll
-            for (int k4 = 0; k4 < TILE_K / 32; ++k4)
-              umma_i8(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc,
-                      (MODE == GEMM_CHANNEL ? (u | k4) : k4) != 0 ? 1u : 0u);
-            umma_commit(&sm.done[it % ND]);
-            if (MODE == GEMM_CHANNEL && u == steps - 1) umma_commit(&sm.tmem_full[b]);
+              for (int k4 = 0; k4 < TILE_K / 32; ++k4)
+                umma_i8(d, adesc + (uint64_t)(k4 * 2), bdesc + (uint64_t)(k4 * 2), idesc,
+                        (MODE == GEMM_CHANNEL ? (u | (uint32_t)k4) : (uint32_t)k4) != 0u ? 1u : 0u);
+              umma_commit(&sm.done[it & (uint32_t)(ND - 1)]);
+              if (MODE == GEMM_CHANNEL && u == steps - 1) umma_commit(&sm.tmem_full[b]);
+            }
+            __syncwarp();
+            // per-channel mode: the buffer ring (lane 2) advances once per item
+            if (MODE != GEMM_CHANNEL || lane != 2 || u == steps - 1) {
+              my_slot += (MODE == GEMM_CHANNEL && lane == 2) ? 1u : NISS;
+              if (my_slot >= my_n) { my_slot -= my_n; my_par ^= 1u; }
+            }
           }
-          __syncwarp();
-          sw = sw + 1 == (uint32_t)NW ? 0u : sw + 1;
-          par_w ^= sw == 0u ? 1u : 0u;
-          sa = sa + 1 == (uint32_t)NA ? 0u : sa + 1;
-          par_a ^= sa == 0u ? 1u : 0u;
-          if (MODE != GEMM_CHANNEL || u == steps - 1) {
-            b = b + 1 == (uint32_t)NBUF ? 0u : b + 1;
-            par_b ^= b == 0u ? 1u : 0u;
-          }
+          it_base += steps;
         }
       }
     } else if (MODE != GEMM_CHANNEL) {
