@@ -48,16 +48,31 @@ __global__ void __launch_bounds__(128, 1) k(int iters, int n, int chains, long l
   if (threadIdx.x < 32) { asm volatile("tcgen05.fence::after_thread_sync;"); asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tb)); }
 }
 int main() {
+  // MMA-only loop on every SM: the ceiling of the tensor pipe for kind::i8 (and kind::f8f6f4) at M=128, K=32 and
+  // N = 16..256, with one or two independent accumulator chains.  Prints one line per case and, last, one JSON
+  // line with the all-SM rates timed with CUDA events (bench.py reads it).
   long long *d; cudaMalloc(&d, 148 * 8); long long h[148];
   cudaFuncSetAttribute(k<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 70 * 1024);
   cudaFuncSetAttribute(k<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 70 * 1024);
+  int sms = 0; cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, 0);
+  if (sms <= 0 || sms > 148) sms = 148;
+  cudaEvent_t e0, e1; cudaEventCreate(&e0); cudaEventCreate(&e1);
   int ns[] = {16, 32, 64, 128, 256};
+  double pops_i8_128 = 0, pops_i8_256 = 0;
   for (int kind = 0; kind < 2; ++kind) for (int ch = 1; ch <= 2; ++ch) for (int ni = 0; ni < 5; ++ni) {
     int n = ns[ni]; if (n * ch > 512) continue; int iters = 2000;
-    if (kind == 0) k<0><<<148, 128, 70 * 1024>>>(iters, n, ch, d); else k<1><<<148, 128, 70 * 1024>>>(iters, n, ch, d);
+    if (kind == 0) k<0><<<sms, 128, 70 * 1024>>>(200, n, ch, d); else k<1><<<sms, 128, 70 * 1024>>>(200, n, ch, d);   // warm-up
+    cudaEventRecord(e0);
+    if (kind == 0) k<0><<<sms, 128, 70 * 1024>>>(iters, n, ch, d); else k<1><<<sms, 128, 70 * 1024>>>(iters, n, ch, d);
+    cudaEventRecord(e1);
     cudaError_t e = cudaDeviceSynchronize(); cudaMemcpy(h, d, 148 * 8, cudaMemcpyDeviceToHost);
+    float ms = 0; cudaEventElapsedTime(&ms, e0, e1);
     double cyc = (double)h[0] / (iters * ch * 4);
-    printf("%s chains=%d N=%3d: %.1f cycles per M128xN%dxK32 MMA -> %.0f MAC/clk/SM, all-SM %.2f POPS @1.965GHz  (%s)\n", kind ? "f8f6f4" : "i8    ", ch, n, cyc, n, 128.0 * n * 32 / cyc, 2 * 128.0 * n * 32 / cyc * 148 * 1.965e9 / 1e15, cudaGetErrorString(e));
+    double pops = 2.0 * 128 * n * 32 * (double)iters * ch * 4 * sms / (ms * 1e-3) / 1e15;
+    if (kind == 0 && n == 128 && pops > pops_i8_128) pops_i8_128 = pops;
+    if (kind == 0 && n == 256 && pops > pops_i8_256) pops_i8_256 = pops;
+    printf("%s chains=%d N=%3d: %.1f cycles per M128xN%dxK32 MMA -> %.0f MAC/clk/SM, all-SM %.2f POPS by CUDA events  (%s)\n", kind ? "f8f6f4" : "i8    ", ch, n, cyc, n, 128.0 * n * 32 / cyc, pops, cudaGetErrorString(e));
   }
+  printf("{\"int8_pops_n128\": %.4f, \"int8_pops_n256\": %.4f, \"sms\": %d}\n", pops_i8_128, pops_i8_256, sms);
   return 0;
 }

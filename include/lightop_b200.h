@@ -47,6 +47,8 @@ const char *lo_last_error(void);
 /* Number of SMs of the current device (grid sizing is done inside the library;
  * exported for the benchmark's reporting). */
 int lo_sm_count(void);
+/* Kernels this library has launched since it was loaded (all threads, all devices). */
+long long lo_launch_count(void);
 
 /*
  * Softmax over experts + top-k selection (+ optional renormalisation).
@@ -177,7 +179,8 @@ int lo_fused_moe_block_int8(const void *x, const int8_t *w1, const int8_t *w2,
  * array of LO_NOALLOC_SCRATCH_BYTES inside the library image, reserved on every GPU that loads the
  * library until the process exits.  Limit: lo_fused_moe_workspace_bytes(M, E_local, global_num_experts,
  * topk, H, I) must not exceed LO_NOALLOC_SCRATCH_BYTES (64 MiB: the DeepSeek-V3 shape with top_k 8 and
- * 256 experts fits up to 64 tokens per call); larger shapes are rejected with LO_ERR_INVALID_ARGUMENT.
+ * 256 experts fits up to 402 tokens per call; lo_fused_moe_workspace_bytes gives the need of any shape); larger
+ * shapes are rejected with LO_ERR_INVALID_ARGUMENT.
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
  * current); make that first call outside any stream capture.  The function calls no cudaMalloc / cudaFree
  * and no allocating library.  All calls on a device share the one array and leave their intermediates
@@ -209,6 +212,17 @@ int lo_expert_rows_block_int8(const int8_t *xq, const float *xs, const int32_t *
                               const float *w1_scale, const float *w2_scale, int64_t T, int E_local,
                               int64_t H, int64_t I, void *out, void *workspace, size_t workspace_bytes,
                               int32_t *status, void *stream);
+
+/*
+ * The same on records as lo_ep_dispatch_pack writes them (packed [T, lo_ep_dispatch_row_bytes(H)] u8, as received
+ * from the other ranks): expert id and routed weight are read from the records, rows and scales are gathered from
+ * them into expert order.  workspace: lo_expert_rows_packed_workspace_bytes(T, E_local, H, I) bytes.  No counterpart
+ * in the reference (see lo_expert_rows_block_int8).
+ */
+size_t lo_expert_rows_packed_workspace_bytes(int64_t T, int E_local, int64_t H, int64_t I);
+int lo_expert_rows_block_int8_packed(const uint8_t *packed, int64_t T, const int8_t *w1, const int8_t *w2,
+                                     const float *w1_scale, const float *w2_scale, int E_local, int64_t H, int64_t I,
+                                     void *out, void *workspace, size_t workspace_bytes, int32_t *status, void *stream);
 
 /*
  * Dense block-INT8 linear: C[m, n] = sum_kb (A_q[m, kb] . B_q[n, kb]) * a_s[m, kb] * b_s[n/128, kb], bf16 out.
@@ -397,6 +411,23 @@ int lo_ep_scatter(const int8_t *aq, const float *aq_scale, int scale_cols,
                   const int32_t *expert_num_tokens, int8_t *aq_out, float *aq_scale_out,
                   int32_t *m_indices, int32_t *inv_perm, int64_t T, int k, int64_t H, int64_t rows,
                   int local_num_experts, int alignment, void *stream);
+
+/*
+ * Dispatch payload of expert parallelism across ranks: one record per routed (token, slot), records grouped by
+ * destination rank in stable order, so that ONE all-to-all carries everything the expert side needs.
+ * Record (lo_ep_dispatch_row_bytes(H) bytes, a multiple of 16): int8 row [H] | group scales f32 [H/128] |
+ * i32 expert id on the destination rank | f32 routed weight | padding.
+ * aq [T,H] int8, aq_scale [T,H/128] f32, topk_ids [T,k] (LO_I32/LO_I64), topk_weights f32 [T,k],
+ * rank_of_expert i32 [global experts]; packed [T*k, record] u8, dest_rank i32 [T*k] (rank of every record),
+ * inv_perm i32 [T,k] (record of every slot), counts i32 [world] (records per destination rank, on the device).
+ * The reference has no counterpart: its expert-parallel kernels (csrc/kernels/deepgemm_moe_permute.cu:1080-1188)
+ * permute rows on one device and leave the exchange to the serving framework.
+ */
+int64_t lo_ep_dispatch_row_bytes(int64_t H);
+int lo_ep_dispatch_pack(const int8_t *aq, const float *aq_scale, const void *topk_ids, int ids_dtype,
+                        const float *topk_weights, const int32_t *rank_of_expert, int64_t T, int k, int64_t H,
+                        int experts_per_rank, int world, uint8_t *packed, int32_t *dest_rank, int32_t *inv_perm,
+                        int32_t *counts, void *stream);
 
 /*
  * Per-row expert id of the aligned contiguous layout.

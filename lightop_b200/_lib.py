@@ -30,6 +30,7 @@ PROTOTYPES = {
     "lo_version": (c_int, []),
     "lo_last_error": (c_char_p, []),
     "lo_sm_count": (c_int, []),
+    "lo_launch_count": (ctypes.c_longlong, []),
     "lo_topk_softmax": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_int, c_void_p, c_void_p, c_int,
                                 c_void_p, c_void_p]),
     "lo_moe_align_block_size": (c_int, [c_void_p, c_int, c_int64, c_int, c_int, c_void_p, c_int, c_void_p,
@@ -50,6 +51,12 @@ PROTOTYPES = {
     "lo_fused_moe_block_int8_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                                 c_int, c_void_p, c_int, c_int64, c_int, c_int, c_int64, c_int64,
                                                 c_void_p, c_void_p, c_void_p, c_int, c_float, c_void_p, c_void_p]),
+    "lo_ep_dispatch_row_bytes": (c_int64, [c_int64]),
+    "lo_ep_dispatch_pack": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_int64,
+                                    c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "lo_expert_rows_packed_workspace_bytes": (c_size_t, [c_int64, c_int, c_int64, c_int64]),
+    "lo_expert_rows_block_int8_packed": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                                 c_int64, c_int64, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
     "lo_expert_rows_block_int8": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                           c_void_p, c_int64, c_int, c_int64, c_int64, c_void_p, c_void_p, c_size_t,
                                           c_void_p, c_void_p]),

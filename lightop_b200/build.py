@@ -58,9 +58,10 @@ def build(force: bool = False, verbose: bool = False) -> str:
 
 
 def build_tools(force: bool = False) -> str:
-    """Compile the stand-alone MMA-peak micro-benchmark (not part of the library)."""
-    src = os.path.join(CSRC, "bench_mma_peak.cu")
-    exe = os.path.join(CSRC, "bench_mma_peak")
+    """Compile the stand-alone MMA-peak micro-benchmark next to bench.py, which runs it for the INT8 tensor peak."""
+    root = os.path.dirname(HERE)
+    src = os.path.join(root, "bench_mma_peak.cu")
+    exe = os.path.join(root, "bench_mma_peak")
     if force or not os.path.exists(exe) or os.path.getmtime(src) > os.path.getmtime(exe):
         res = subprocess.run([_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-o", exe, src],
                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)

@@ -5,6 +5,7 @@
 namespace lo {
 
 static thread_local char g_err[512] = "";
+std::atomic<long long> g_launch_count{0};
 
 void set_error(const char *fmt, ...) {
   va_list ap;
@@ -31,3 +32,4 @@ int sm_count() {
 extern "C" int lo_version(void) { return 1; }
 extern "C" const char *lo_last_error(void) { return lo::g_err; }
 extern "C" int lo_sm_count(void) { return lo::sm_count(); }
+extern "C" long long lo_launch_count(void) { return lo::g_launch_count.load(std::memory_order_relaxed); }

@@ -7,6 +7,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdarg>
+#include <atomic>
 #include "../../include/lightop_b200.h"
 
 namespace lo {
@@ -38,10 +39,14 @@ inline int fail(int code, const char *fmt, ...) {
 
 #define LO_LAUNCH_OK(what)                                                            \
   do {                                                                                \
+    ::lo::g_launch_count.fetch_add(1, std::memory_order_relaxed);                     \
     cudaError_t e__ = cudaGetLastError();                                             \
     if (e__ != cudaSuccess)                                                           \
       return ::lo::fail(LO_ERR_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e__)); \
   } while (0)
+
+// Kernels launched by this library since it was loaded (lo_launch_count): every launch site counts itself.
+extern std::atomic<long long> g_launch_count;
 
 inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 inline int64_t round_up(int64_t a, int64_t b) { return ceil_div(a, b) * b; }
@@ -87,10 +92,16 @@ int launch_silu_mul_token_quant(const void *in, int64_t rows, int64_t d, const i
                                 int64_t group_rows = 0, const int32_t *group_counts = nullptr);
 
 // Copy int8 rows and their scales into sorted-position order: row(pos) = sorted_ids[pos] / top_k.
-// scales_per_row = 0 means K / 128 (block scales); 1 is the per-token format.  reduce.cu
+// scales_per_row = 0 means K / 128 (block scales); 1 is the per-token format.  a_stride = 0 means K bytes between
+// source rows; with a_scale == nullptr the scales of a row follow it inside its a_stride-byte record.  reduce.cu
 int launch_permute_rows(const int8_t *A, const float *a_scale, int64_t rows_a, int64_t K, const int32_t *sorted_ids,
                         int64_t sorted_capacity, const int32_t *num_tokens_post_pad, int64_t numel_valid, int top_k,
-                        int8_t *A_sorted, float *a_scale_sorted, cudaStream_t stream, int64_t scales_per_row = 0);
+                        int8_t *A_sorted, float *a_scale_sorted, cudaStream_t stream, int64_t scales_per_row = 0,
+                        int64_t a_stride = 0);
+
+// Expert id and routed weight of packed dispatch records (lo_ep_dispatch_pack) into contiguous arrays.  reduce.cu
+int launch_ep_unpack_meta(const uint8_t *packed, int64_t rows, int64_t stride, int64_t meta_off, int32_t *row_expert,
+                          float *row_weight, cudaStream_t stream);
 
 // Chunk table from an existing (expert_ids, num_tokens_post_pad) pair, see routing.cu.
 int launch_chunks_from_blocks(const int32_t *expert_ids, const int32_t *num_tokens_post_pad,
@@ -153,6 +164,7 @@ inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 bl
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  g_launch_count.fetch_add(1, std::memory_order_relaxed);
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
@@ -173,8 +185,10 @@ __device__ __forceinline__ unsigned peers_of(int e, int nbits) {
 }
 #endif
 
+// Top-k sum of the fused layers.  A slot is skipped under the alignment kernel's rule: its id lies outside
+// [0, num_experts) or (with an expert_map) maps outside [0, num_local); such rows were never written.  reduce.cu
 int launch_moe_sum_masked(const __nv_bfloat16 *in, __nv_bfloat16 *out, const __nv_bfloat16 *bias,
                           int64_t M, int topk, int64_t H, float factor, const void *topk_ids,
-                          int ids_dtype, const int32_t *expert_map, cudaStream_t stream);
+                          int ids_dtype, const int32_t *expert_map, int num_experts, int num_local, cudaStream_t stream);
 
 }  // namespace lo

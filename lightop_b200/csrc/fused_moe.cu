@@ -202,7 +202,7 @@ extern "C" int lo_fused_moe_block_int8(const void *x, const int8_t *w1, const in
   prof_mark(4, st);
   rc = launch_moe_sum_masked(static_cast<const __nv_bfloat16 *>(cache3), static_cast<__nv_bfloat16 *>(out),
                              static_cast<const __nv_bfloat16 *>(shared_output), M, topk, H, routed_scaling_factor,
-                             topk_ids, ids_dtype, expert_map, st);
+                             topk_ids, ids_dtype, expert_map, align_E, E_local, st);
   prof_mark(5, st);
   if (g_prof.enabled && g_prof.created) g_prof.recorded = true;
   return rc;
@@ -490,7 +490,7 @@ extern "C" int lo_fused_moe_channel_int8(const void *x, int x_dtype, const int8_
   prof_mark(4, st);
   rc = launch_moe_sum_masked(static_cast<const __nv_bfloat16 *>(cache3), static_cast<__nv_bfloat16 *>(out),
                              static_cast<const __nv_bfloat16 *>(shared_output), M, topk, H, routed_scaling_factor,
-                             topk_ids, ids_dtype, expert_map, st);
+                             topk_ids, ids_dtype, expert_map, align_E, E_local, st);
   prof_mark(5, st);
   if (g_prof.enabled && g_prof.created) g_prof.recorded = true;
   return rc;
@@ -500,15 +500,16 @@ extern "C" int lo_fused_moe_channel_int8(const void *x, int x_dtype, const int8_
 // Expert side of expert parallelism: rows arrive already quantised (int8 + group scales), each with
 // the local expert that has to process it and, optionally, its routed weight.
 // ---------------------------------------------------------------------------
-extern "C" int lo_expert_rows_block_int8(const int8_t *xq, const float *xs, const int32_t *row_expert,
-                                         const float *row_weight, const int8_t *w1, const int8_t *w2,
-                                         const float *w1_scale, const float *w2_scale, int64_t T, int E_local,
-                                         int64_t H, int64_t I, void *out, void *workspace, size_t workspace_bytes,
-                                         int32_t *status, void *stream) {
-  using namespace lo;
+namespace lo {
+namespace {
+// xs == nullptr: the rows are records of `x_stride` bytes, int8 row first, its group scales right behind it
+int expert_rows_impl(const int8_t *xq, const float *xs, int64_t x_stride, const int32_t *row_expert,
+                     const float *row_weight, const int8_t *w1, const int8_t *w2, const float *w1_scale,
+                     const float *w2_scale, int64_t T, int E_local, int64_t H, int64_t I, void *out, void *workspace,
+                     size_t workspace_bytes, int32_t *status, void *stream) {
   LO_REQUIRE(T >= 0 && E_local >= 1 && E_local <= 1024, "expert rows: bad shape");
   if (T == 0) return LO_OK;
-  LO_REQUIRE(xq && xs && row_expert && w1 && w2 && w1_scale && w2_scale && out && workspace, "expert rows: null pointer");
+  LO_REQUIRE(xq && row_expert && w1 && w2 && w1_scale && w2_scale && out && workspace, "expert rows: null pointer");
   LO_REQUIRE(H % 128 == 0 && I % 128 == 0, "expert rows: hidden and intermediate sizes must be multiples of 128");
   LO_REQUIRE(T < (1LL << 30), "expert rows: too many rows");
   LO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & (ALIGN_BYTES - 1)) == 0, "expert rows: workspace must be 256-byte aligned");
@@ -522,7 +523,7 @@ extern "C" int lo_expert_rows_block_int8(const int8_t *xq, const float *xs, cons
                         nullptr, 0, L.header, L.chunks, L.header + 1, L.chunk_cap, nullptr, chunk_max, st);
   if (rc != LO_OK) return rc;
   // 2. rows and scales into sorted order
-  rc = launch_permute_rows(xq, xs, T, H, L.sorted_ids, L.sorted_cap, L.header, T, 1, L.xq, L.xs, st);
+  rc = launch_permute_rows(xq, xs, T, H, L.sorted_ids, L.sorted_cap, L.header, T, 1, L.xq, L.xs, st, 0, x_stride);
   if (rc != LO_OK) return rc;
   GemmArgs g1{};
   g1.A = L.xq; g1.a_scale = L.xs; g1.rows_a = L.sorted_cap; g1.max_chunk_rows = (int)(T < chunk_max ? T : chunk_max);
@@ -547,6 +548,47 @@ extern "C" int lo_expert_rows_block_int8(const int8_t *xq, const float *xs, cons
   g2.weight_mode = row_weight ? LO_WEIGHT_BF16_PRODUCT : LO_WEIGHT_NONE;
   g2.status = status;
   return launch_grouped_gemm(GEMM_SINGLE, g2, st);
+}
+}  // namespace
+}  // namespace lo
+
+extern "C" int lo_expert_rows_block_int8(const int8_t *xq, const float *xs, const int32_t *row_expert,
+                                         const float *row_weight, const int8_t *w1, const int8_t *w2,
+                                         const float *w1_scale, const float *w2_scale, int64_t T, int E_local,
+                                         int64_t H, int64_t I, void *out, void *workspace, size_t workspace_bytes,
+                                         int32_t *status, void *stream) {
+  LO_REQUIRE(xs != nullptr || T == 0, "expert rows: null pointer");
+  return lo::expert_rows_impl(xq, xs, 0, row_expert, row_weight, w1, w2, w1_scale, w2_scale, T, E_local, H, I, out,
+                              workspace, workspace_bytes, status, stream);
+}
+
+extern "C" size_t lo_expert_rows_packed_workspace_bytes(int64_t T, int E_local, int64_t H, int64_t I) {
+  using namespace lo;
+  return carve_fused(nullptr, T, E_local, 1, H, I).bytes + 2 * (size_t)round_up(T * 4, ALIGN_BYTES);
+}
+
+extern "C" int lo_expert_rows_block_int8_packed(const uint8_t *packed, int64_t T, const int8_t *w1, const int8_t *w2,
+                                                const float *w1_scale, const float *w2_scale, int E_local, int64_t H,
+                                                int64_t I, void *out, void *workspace, size_t workspace_bytes,
+                                                int32_t *status, void *stream) {
+  using namespace lo;
+  LO_REQUIRE(T >= 0 && E_local >= 1 && H % 128 == 0 && I % 128 == 0, "expert rows (packed): bad shape");
+  if (T == 0) return LO_OK;
+  LO_REQUIRE(packed && workspace, "expert rows (packed): null pointer");
+  LO_REQUIRE((reinterpret_cast<uintptr_t>(packed) & 15) == 0, "expert rows (packed): records must be 16-byte aligned");
+  LO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & (ALIGN_BYTES - 1)) == 0, "expert rows (packed): workspace must be 256-byte aligned");
+  const size_t fused_bytes = carve_fused(nullptr, T, E_local, 1, H, I).bytes;
+  const size_t meta_bytes = (size_t)round_up(T * 4, ALIGN_BYTES);
+  LO_REQUIRE(workspace_bytes >= fused_bytes + 2 * meta_bytes, "expert rows (packed): workspace of %zu bytes, %zu needed",
+             workspace_bytes, fused_bytes + 2 * meta_bytes);
+  uint8_t *ws = static_cast<uint8_t *>(workspace);
+  int32_t *row_expert = reinterpret_cast<int32_t *>(ws + fused_bytes);
+  float *row_weight = reinterpret_cast<float *>(ws + fused_bytes + meta_bytes);
+  const int64_t stride = lo_ep_dispatch_row_bytes(H);
+  int rc = launch_ep_unpack_meta(packed, T, stride, H + 4 * (H / 128), row_expert, row_weight, static_cast<cudaStream_t>(stream));
+  if (rc != LO_OK) return rc;
+  return expert_rows_impl(reinterpret_cast<const int8_t *>(packed), nullptr, stride, row_expert, row_weight, w1, w2, w1_scale,
+                          w2_scale, T, E_local, H, I, out, workspace, fused_bytes, status, stream);
 }
 
 // ---------------------------------------------------------------------------

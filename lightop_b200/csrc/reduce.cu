@@ -64,7 +64,8 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(const T *__restrict__ in, 
                                                       const T *__restrict__ bias, int64_t M, int topk, int64_t H8,
                                                       float factor, const uint8_t *__restrict__ mask,
                                                       const int32_t *__restrict__ num_local_tokens,
-                                                      const IdT *__restrict__ ids, const int32_t *__restrict__ expert_map) {
+                                                      const IdT *__restrict__ ids, const int32_t *__restrict__ expert_map,
+                                                      int num_experts, int num_local) {
   using V = Vec8<T>;
   const int64_t t = blockIdx.y;
   dependency_wait();            // the rows come from the kernel before this one
@@ -75,8 +76,14 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(const T *__restrict__ in, 
     for (int j = 0; j < topk; ++j) {
       if (mask && !mask[t * topk + j]) continue;
       if (ids) {
+        // the rule of the alignment kernel (load_expert): an id outside [0, num_experts), or one that maps
+        // outside the local experts, was dropped there and its row was never written
         const long long e = (long long)ids[t * topk + j];
-        if (e < 0 || (expert_map && expert_map[e] < 0)) continue;
+        if (e < 0 || e >= num_experts) continue;
+        if (expert_map) {
+          const int m = expert_map[e];
+          if (m < 0 || m >= num_local) continue;
+        }
       }
       float f[8];
       in_v[(int64_t)j * H8 + c].to_float(f);
@@ -101,12 +108,12 @@ __global__ void __launch_bounds__(256) moe_sum_kernel(const T *__restrict__ in, 
 template <typename T, typename IdT>
 int launch_sum(const void *in, void *out, const void *bias, int64_t M, int topk, int64_t H, float factor,
                const uint8_t *mask, const int32_t *nlt, const void *ids, const int32_t *expert_map,
-               cudaStream_t st) {
+               cudaStream_t st, int num_experts = 0x7fffffff, int num_local = 0x7fffffff) {
   const int64_t H8 = H / 8;
   dim3 grid((unsigned)(ceil_div(H8, 256) > 65535 ? 65535 : ceil_div(H8, 256)), (unsigned)M);
   LO_CUDA_OK(launch_dependent(moe_sum_kernel<T, IdT>, grid, dim3(256), 0, st, static_cast<const T *>(in),
                               static_cast<T *>(out), static_cast<const T *>(bias), M, topk, H8, factor, mask, nlt,
-                              static_cast<const IdT *>(ids), expert_map));
+                              static_cast<const IdT *>(ids), expert_map, num_experts, num_local));
   return LO_OK;
 }
 
@@ -135,7 +142,7 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(const IdT *__restrict__ i
                                                        const int32_t *__restrict__ expert_map,
                                                        const int32_t *__restrict__ counts_in, int local_E,
                                                        int alignment, int32_t *__restrict__ m_indices, int64_t rows,
-                                                       int32_t *__restrict__ inv_perm) {
+                                                       int32_t *__restrict__ inv_perm, int32_t *__restrict__ counts_out) {
   namespace cg = cooperative_groups;
   cg::cluster_group cluster = cg::this_cluster();
   const int C = (int)cluster.num_blocks();      // 1 for a plain launch
@@ -186,6 +193,7 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(const IdT *__restrict__ i
     }
     cnt[e] = counts_in ? counts_in[e] : total;
     before[e] = lower;
+    if (counts_out != nullptr && r == 0) counts_out[e] = total;
   }
   __syncthreads();
   if (tid == 0) {
@@ -220,7 +228,8 @@ __global__ void __launch_bounds__(1024) ep_plan_kernel(const IdT *__restrict__ i
 
 template <typename IdT>
 int launch_ep_plan(const void *ids, int64_t numel, const int32_t *expert_map, const int32_t *counts_in, int local_E,
-                   int alignment, int32_t *m_indices, int64_t rows, int32_t *inv_perm, cudaStream_t st) {
+                   int alignment, int32_t *m_indices, int64_t rows, int32_t *inv_perm, cudaStream_t st,
+                   int32_t *counts_out = nullptr) {
   const size_t smem = sizeof(int32_t) * (36 * (size_t)local_E + 1);
   LO_CUDA_OK(cudaFuncSetAttribute(ep_plan_kernel<IdT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const IdT *idp = static_cast<const IdT *>(ids);
@@ -237,11 +246,12 @@ int launch_ep_plan(const void *ids, int64_t numel, const int32_t *expert_map, co
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    g_launch_count.fetch_add(1, std::memory_order_relaxed);
     LO_CUDA_OK(cudaLaunchKernelEx(&cfg, ep_plan_kernel<IdT>, idp, numel, expert_map, counts_in, local_E, alignment,
-                                  m_indices, rows, inv_perm));
+                                  m_indices, rows, inv_perm, counts_out));
     return LO_OK;
   }
-  ep_plan_kernel<IdT><<<1, 1024, smem, st>>>(idp, numel, expert_map, counts_in, local_E, alignment, m_indices, rows, inv_perm);
+  ep_plan_kernel<IdT><<<1, 1024, smem, st>>>(idp, numel, expert_map, counts_in, local_E, alignment, m_indices, rows, inv_perm, counts_out);
   LO_LAUNCH_OK("ep_plan_kernel");
   return LO_OK;
 }
@@ -261,6 +271,44 @@ __global__ void __launch_bounds__(128) ep_copy_rows_kernel(const int8_t *__restr
   for (int c = threadIdx.x; c < scale_cols; c += blockDim.x) as_out[(int64_t)dst * scale_cols + c] = as[t * scale_cols + c];
 }
 
+// Dispatch payload of expert parallelism, one CTA per (token, slot): the token's int8 row, its group scales, the
+// slot's expert id on the destination rank and its routed weight, as ONE record of `stride` bytes at row
+// inv_perm[token, slot] of the send buffer (rows grouped by destination rank), so that a step needs a single
+// all-to-all for everything the expert side wants.
+template <typename IdT>
+__global__ void __launch_bounds__(128) ep_pack_rows_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as,
+                                                           const IdT *__restrict__ ids, const float *__restrict__ w,
+                                                           const int32_t *__restrict__ inv_perm, uint8_t *__restrict__ out,
+                                                           int k, int64_t H, int G, int64_t stride, int experts_per_rank,
+                                                           int64_t rows) {
+  const int64_t flat = blockIdx.x;
+  const int32_t dst = inv_perm[flat];
+  if (dst < 0 || dst >= rows) return;
+  const int64_t t = flat / k;
+  uint8_t *rec = out + (int64_t)dst * stride;
+  const uint4 *src = reinterpret_cast<const uint4 *>(aq + t * H);
+  uint4 *d = reinterpret_cast<uint4 *>(rec);
+  for (int64_t c = threadIdx.x; c < H / 16; c += blockDim.x) d[c] = src[c];
+  float *sc = reinterpret_cast<float *>(rec + H);
+  for (int c = threadIdx.x; c < G; c += blockDim.x) sc[c] = as[t * G + c];
+  if (threadIdx.x == 0) {
+    reinterpret_cast<int32_t *>(rec + H + 4 * (int64_t)G)[0] = (int32_t)((long long)ids[flat] % experts_per_rank);
+    reinterpret_cast<float *>(rec + H + 4 * (int64_t)G)[1] = w[flat];
+  }
+}
+
+// Expert id and routed weight of every received record into contiguous arrays (the alignment kernel wants the ids
+// as one array).
+__global__ void __launch_bounds__(256) ep_unpack_meta_kernel(const uint8_t *__restrict__ packed, int64_t rows, int64_t stride,
+                                                             int64_t meta_off, int32_t *__restrict__ row_expert,
+                                                             float *__restrict__ row_weight) {
+  const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  const uint8_t *rec = packed + r * stride + meta_off;
+  row_expert[r] = reinterpret_cast<const int32_t *>(rec)[0];
+  row_weight[r] = reinterpret_cast<const float *>(rec)[1];
+}
+
 template <typename IdT>
 __global__ void __launch_bounds__(256) ep_gather_kernel(const __nv_bfloat16 *__restrict__ a, const IdT *__restrict__ ids,
                                                         const float *__restrict__ w, const int32_t *__restrict__ inv_perm,
@@ -271,10 +319,11 @@ __global__ void __launch_bounds__(256) ep_gather_kernel(const __nv_bfloat16 *__r
   for (int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; c < H8; c += (int64_t)gridDim.x * blockDim.x) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int j = 0; j < k; ++j) {
-      const long long e = (long long)ids[t * k + j];
-      if (e < 0 || (expert_map && expert_map[e] < 0)) continue;
+      // a slot that the scatter dropped has no row (and its id may lie outside the map): look at that first
       const int32_t r = inv_perm[t * k + j];
       if (r < 0) continue;
+      const long long e = (long long)ids[t * k + j];
+      if (e < 0 || (expert_map && expert_map[e] < 0)) continue;
       const float wj = w[t * k + j];
       float f[8];
       reinterpret_cast<const V *>(a)[(int64_t)r * H8 + c].to_float(f);
@@ -293,41 +342,55 @@ __global__ void __launch_bounds__(128) permute_rows_kernel(const int8_t *__restr
                                                            const int32_t *__restrict__ num_tokens_post_pad,
                                                            int64_t numel_valid, int top_k, int64_t kb,
                                                            int8_t *__restrict__ A_sorted,
-                                                           float *__restrict__ a_scale_sorted) {
+                                                           float *__restrict__ a_scale_sorted, int64_t a_stride) {
   const int64_t pos = blockIdx.x;
   if (pos >= *num_tokens_post_pad) return;
   const int32_t sid = sorted_ids[pos];
   if (sid < 0 || sid >= numel_valid) return;
   const int64_t row = sid / top_k;
   if (row >= rows_a) return;
-  const uint4 *src = reinterpret_cast<const uint4 *>(A + row * K);
+  // a_stride: bytes between two source rows (K for a plain matrix); without a scale array the scales follow the
+  // row inside its record
+  const uint4 *src = reinterpret_cast<const uint4 *>(A + row * a_stride);
+  const float *src_s = a_scale ? a_scale + row * kb : reinterpret_cast<const float *>(A + row * a_stride + K);
   uint4 *dst = reinterpret_cast<uint4 *>(A_sorted + pos * K);
   for (int64_t c = threadIdx.x; c < K / 16; c += blockDim.x) dst[c] = src[c];
-  for (int64_t c = threadIdx.x; c < kb; c += blockDim.x) a_scale_sorted[pos * kb + c] = a_scale[row * kb + c];
+  for (int64_t c = threadIdx.x; c < kb; c += blockDim.x) a_scale_sorted[pos * kb + c] = src_s[c];
 }
 
 }  // namespace
 
 int launch_permute_rows(const int8_t *A, const float *a_scale, int64_t rows_a, int64_t K, const int32_t *sorted_ids,
                         int64_t sorted_capacity, const int32_t *num_tokens_post_pad, int64_t numel_valid, int top_k,
-                        int8_t *A_sorted, float *a_scale_sorted, cudaStream_t stream, int64_t scales_per_row) {
+                        int8_t *A_sorted, float *a_scale_sorted, cudaStream_t stream, int64_t scales_per_row,
+                        int64_t a_stride) {
   if (sorted_capacity <= 0) return LO_OK;
   LO_REQUIRE(sorted_capacity <= 0x7fffffffLL, "permute rows: too many positions");
   permute_rows_kernel<<<(unsigned)sorted_capacity, 128, 0, stream>>>(A, a_scale, rows_a, K, sorted_ids, num_tokens_post_pad,
                                                                      numel_valid, top_k,
                                                                      scales_per_row > 0 ? scales_per_row : K / 128, A_sorted,
-                                                                     a_scale_sorted);
+                                                                     a_scale_sorted, a_stride > 0 ? a_stride : K);
   LO_LAUNCH_OK("permute_rows_kernel");
+  return LO_OK;
+}
+
+int launch_ep_unpack_meta(const uint8_t *packed, int64_t rows, int64_t stride, int64_t meta_off, int32_t *row_expert,
+                          float *row_weight, cudaStream_t stream) {
+  if (rows <= 0) return LO_OK;
+  ep_unpack_meta_kernel<<<(unsigned)ceil_div(rows, 256), 256, 0, stream>>>(packed, rows, stride, meta_off, row_expert, row_weight);
+  LO_LAUNCH_OK("ep_unpack_meta_kernel");
   return LO_OK;
 }
 
 int launch_moe_sum_masked(const __nv_bfloat16 *in, __nv_bfloat16 *out, const __nv_bfloat16 *bias, int64_t M,
                           int topk, int64_t H, float factor, const void *topk_ids, int ids_dtype,
-                          const int32_t *expert_map, cudaStream_t stream) {
+                          const int32_t *expert_map, int num_experts, int num_local, cudaStream_t stream) {
   if (M == 0) return LO_OK;
   if (ids_dtype == LO_I64)
-    return launch_sum<__nv_bfloat16, int64_t>(in, out, bias, M, topk, H, factor, nullptr, nullptr, topk_ids, expert_map, stream);
-  return launch_sum<__nv_bfloat16, int32_t>(in, out, bias, M, topk, H, factor, nullptr, nullptr, topk_ids, expert_map, stream);
+    return launch_sum<__nv_bfloat16, int64_t>(in, out, bias, M, topk, H, factor, nullptr, nullptr, topk_ids, expert_map, stream,
+                                              num_experts, num_local);
+  return launch_sum<__nv_bfloat16, int32_t>(in, out, bias, M, topk, H, factor, nullptr, nullptr, topk_ids, expert_map, stream,
+                                            num_experts, num_local);
 }
 
 }  // namespace lo
@@ -385,6 +448,39 @@ extern "C" int lo_ep_scatter(const int8_t *aq, const float *aq_scale, int scale_
     ep_copy_rows_kernel<<<(unsigned)(T * k), 128, 0, st>>>(aq, aq_scale, scale_cols, inv_perm, aq_out, aq_scale_out, k, H, rows);
     LO_LAUNCH_OK("ep_copy_rows_kernel");
   }
+  return LO_OK;
+}
+
+extern "C" int64_t lo_ep_dispatch_row_bytes(int64_t H) { return lo::round_up(H + 4 * (H / 128) + 8, 16); }
+
+extern "C" int lo_ep_dispatch_pack(const int8_t *aq, const float *aq_scale, const void *topk_ids, int ids_dtype,
+                                   const float *topk_weights, const int32_t *rank_of_expert, int64_t T, int k, int64_t H,
+                                   int experts_per_rank, int world, uint8_t *packed, int32_t *dest_rank,
+                                   int32_t *inv_perm, int32_t *counts, void *stream) {
+  using namespace lo;
+  LO_REQUIRE(world >= 1 && world <= 1024 && experts_per_rank >= 1, "ep_dispatch_pack: bad sharding");
+  LO_REQUIRE(k >= 1 && T >= 0 && H % 128 == 0, "ep_dispatch_pack: bad shape");
+  LO_REQUIRE(aq && aq_scale && topk_ids && topk_weights && rank_of_expert && packed && dest_rank && inv_perm && counts,
+             "ep_dispatch_pack: null pointer");
+  LO_REQUIRE(T * k <= 0x7fffffffLL, "ep_dispatch_pack: too many (token, slot) pairs");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t rows = T * k;
+  int rc;
+  if (ids_dtype == LO_I64)
+    rc = launch_ep_plan<int64_t>(topk_ids, rows, rank_of_expert, nullptr, world, 1, dest_rank, rows, inv_perm, st, counts);
+  else if (ids_dtype == LO_I32)
+    rc = launch_ep_plan<int32_t>(topk_ids, rows, rank_of_expert, nullptr, world, 1, dest_rank, rows, inv_perm, st, counts);
+  else
+    return fail(LO_ERR_UNSUPPORTED, "ep_dispatch_pack: unsupported id dtype code %d", ids_dtype);
+  if (rc != LO_OK || rows == 0) return rc;
+  const int64_t stride = lo_ep_dispatch_row_bytes(H);
+  if (ids_dtype == LO_I64)
+    ep_pack_rows_kernel<int64_t><<<(unsigned)rows, 128, 0, st>>>(aq, aq_scale, static_cast<const int64_t *>(topk_ids), topk_weights,
+                                                                 inv_perm, packed, k, H, (int)(H / 128), stride, experts_per_rank, rows);
+  else
+    ep_pack_rows_kernel<int32_t><<<(unsigned)rows, 128, 0, st>>>(aq, aq_scale, static_cast<const int32_t *>(topk_ids), topk_weights,
+                                                                 inv_perm, packed, k, H, (int)(H / 128), stride, experts_per_rank, rows);
+  LO_LAUNCH_OK("ep_pack_rows_kernel");
   return LO_OK;
 }
 

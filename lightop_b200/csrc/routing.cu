@@ -512,6 +512,7 @@ int launch_align(const void *topk_ids, int ids_dtype, int64_t numel, int num_exp
     if (ids_dtype == LO_I32) {
       if (csmem > 48 * 1024)
         LO_CUDA_OK(cudaFuncSetAttribute(align_cluster_kernel<int32_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csmem));
+      g_launch_count.fetch_add(1, std::memory_order_relaxed);
       LO_CUDA_OK(cudaLaunchKernelEx(&cfg, align_cluster_kernel<int32_t>, static_cast<const int32_t *>(topk_ids), numel,
                                     num_experts, block_size, expert_map, map_mode, sorted_ids, sorted_capacity, expert_ids,
                                     expert_ids_capacity, num_tokens_post_pad, chunks, num_chunks, chunk_capacity, inv_pos,
@@ -519,6 +520,7 @@ int launch_align(const void *topk_ids, int ids_dtype, int64_t numel, int num_exp
     } else {
       if (csmem > 48 * 1024)
         LO_CUDA_OK(cudaFuncSetAttribute(align_cluster_kernel<int64_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csmem));
+      g_launch_count.fetch_add(1, std::memory_order_relaxed);
       LO_CUDA_OK(cudaLaunchKernelEx(&cfg, align_cluster_kernel<int64_t>, static_cast<const int64_t *>(topk_ids), numel,
                                     num_experts, block_size, expert_map, map_mode, sorted_ids, sorted_capacity, expert_ids,
                                     expert_ids_capacity, num_tokens_post_pad, chunks, num_chunks, chunk_capacity, inv_pos,
@@ -527,21 +529,18 @@ int launch_align(const void *topk_ids, int ids_dtype, int64_t numel, int num_exp
     return LO_OK;
   }
   if (ids_dtype == LO_I32) {
-    static thread_local size_t set32 = 0;
-    if (smem > 48 * 1024 && smem > set32) {
+    // the opt-in belongs to the (kernel, device) pair: set whenever a launch needs it, whichever device is current
+    if (smem > 48 * 1024) {
       e = cudaFuncSetAttribute(align_kernel<int32_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return fail(LO_ERR_CUDA, "moe_align: smem opt-in failed: %s", cudaGetErrorString(e));
-      set32 = smem;
     }
     align_kernel<int32_t><<<1, ALIGN_WARPS * 32, smem, stream>>>(
         static_cast<const int32_t *>(topk_ids), numel, num_experts, block_size, expert_map, map_mode, sorted_ids,
         sorted_capacity, expert_ids, expert_ids_capacity, num_tokens_post_pad, chunks, num_chunks, chunk_capacity, inv_pos, chunk_max);
   } else if (ids_dtype == LO_I64) {
-    static thread_local size_t set64 = 0;
-    if (smem > 48 * 1024 && smem > set64) {
+    if (smem > 48 * 1024) {
       e = cudaFuncSetAttribute(align_kernel<int64_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       if (e != cudaSuccess) return fail(LO_ERR_CUDA, "moe_align: smem opt-in failed: %s", cudaGetErrorString(e));
-      set64 = smem;
     }
     align_kernel<int64_t><<<1, ALIGN_WARPS * 32, smem, stream>>>(
         static_cast<const int64_t *>(topk_ids), numel, num_experts, block_size, expert_map, map_mode, sorted_ids,

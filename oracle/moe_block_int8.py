@@ -143,8 +143,12 @@ def moe_sum(inp: torch.Tensor, factor: float = 1.0, bias: Optional[torch.Tensor]
 def fused_moe_block_int8(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
                          w1_s: torch.Tensor, w2_s: torch.Tensor,
                          topk_weight: torch.Tensor, topk_ids: torch.Tensor,
-                         block_shape=(128, 128), return_intermediates: bool = False):
+                         block_shape=(128, 128), return_intermediates: bool = False,
+                         quant_fn=None, matmul_fn=None):
     """The composed block-INT8 MoE layer.
+
+    ``quant_fn`` / ``matmul_fn`` replace this module's group quantisation and block matmul by functions of the
+    same signatures (the benchmark's CPU arm passes the reference's own two functions when a checkout is found).
 
     The reference holds only a commented-out call of this function
     (test/moe_w8a8/benchmark_moe_int8.py:225-234); it is composed here exactly
@@ -157,7 +161,9 @@ def fused_moe_block_int8(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
     B, D = x.shape
     topk = topk_ids.shape[1]
     group = block_shape[1]
-    a_q, a_s = group_quant_int8(x, group)
+    quant = quant_fn or group_quant_int8
+    matmul = matmul_fn or block_int8_matmul
+    a_q, a_s = quant(x, group)
     a_q = a_q.view(B, -1, D).repeat(1, topk, 1).reshape(-1, D)
     a_s = a_s.view(B, 1, -1).repeat(1, topk, 1).reshape(B * topk, -1)
     H = w2.shape[1]
@@ -170,14 +176,14 @@ def fused_moe_block_int8(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor,
     for e in range(w1.shape[0]):
         mask = flat_ids == e
         if mask.sum():
-            inter = block_int8_matmul(a_q[mask], w1[e], a_s[mask], w1_s[e], block_shape, x.dtype)
+            inter = matmul(a_q[mask], w1[e], a_s[mask], w1_s[e], list(block_shape), x.dtype)
             d = inter.shape[-1] // 2
             act = F.silu(inter[..., :d]) * inter[..., d:]
-            act_q, act_s = group_quant_int8(act.contiguous(), group)
+            act_q, act_s = quant(act.contiguous(), group)
             if return_intermediates:
                 act_q_all[mask] = act_q
                 act_s_all[mask] = act_s
-            out[mask] = block_int8_matmul(act_q, w2[e], act_s, w2_s[e], block_shape, x.dtype)
+            out[mask] = matmul(act_q, w2[e], act_s, w2_s[e], list(block_shape), x.dtype)
     y = (out.view(B, -1, H) * flat_w.view(B, -1, 1).to(out.dtype)).sum(dim=1)
     if return_intermediates:
         return y, dict(a_q=a_q.view(B, topk, D)[:, 0].contiguous(), a_s=a_s.view(B, topk, -1)[:, 0].contiguous(),

@@ -7,8 +7,8 @@ keeps only the requested ``FunctionDef`` nodes and executes them in a
 namespace holding ``torch``, ``F`` and ``math`` (the reference's CI uses the
 same trick, test/ci_tests/test_w8a8_small_m_config.py:63-76).
 
-A reference checkout is looked for in ``$LIGHTOP_REF`` and in the build environment's default location.
-It exists only where the fixtures are generated; tests that need it skip when
+A reference checkout is looked for in ``$LIGHTOP_REF`` and then in ``baseline/_ref`` under the
+repository root.  It exists only where the fixtures are generated; tests that need it skip when
 it is absent.
 """
 from __future__ import annotations
@@ -20,7 +20,8 @@ from typing import Dict, Iterable, Optional
 
 
 def reference_root() -> Optional[str]:
-    for cand in (os.environ.get("LIGHTOP_REF"), os.path.join(os.sep, "root", "reference")):
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for cand in (os.environ.get("LIGHTOP_REF"), os.path.join(repo, "baseline", "_ref")):
         if cand and os.path.isdir(os.path.join(cand, "test", "moe_w8a8")):
             return cand
     return None

@@ -100,3 +100,22 @@ def test_api_names_present():
     assert hasattr(lightop_b200.quant, "per_token_group_quant_int8")
     assert hasattr(lightop_b200.quant, "per_token_quant_int8")
     assert hasattr(lightop_b200.activation, "fuse_silu_mul_quant")
+
+
+def test_noalloc_size_check_boundary_without_a_gpu():
+    """The scratch-free entry point refuses a shape by its workspace need before anything else happens: at the
+    DeepSeek-V3 shape 402 tokens fit its 64 MiB array and 403 do not (the size check needs no device)."""
+    from lightop_b200 import _lib
+    lib = _lib.load()
+    args = dict(E=256, k=8, H=7168, I=2048)
+    assert lib.lo_fused_moe_workspace_bytes(402, args["E"], args["E"], args["k"], args["H"], args["I"]) <= 64 << 20
+    assert lib.lo_fused_moe_workspace_bytes(403, args["E"], args["E"], args["k"], args["H"], args["I"]) > 64 << 20
+
+    def call(M):
+        st = lib.lo_fused_moe_block_int8_noalloc(0, 0, 0, 0, 0, 0, 0, _lib.LO_I32, 0, args["E"], M, args["E"], args["k"],
+                                                 args["H"], args["I"], 0, 0, 0, 0, 1.0, 0, 0)
+        return st, lib.lo_last_error()
+    st, msg = call(403)
+    assert st == 1 and b"built-in array" in msg
+    st, msg = call(402)           # passes the size check; what stops it afterwards is the missing device or the null pointers
+    assert st != 0 and b"built-in array" not in msg

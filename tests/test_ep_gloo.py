@@ -23,14 +23,25 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _pack_torch(xq, xs, topk_ids, rank_of_expert, world, rows):
+def _pack_torch(xq, xs, topk_ids, topk_weights, rank_of_expert, experts_per_rank, world):
+    """Torch model of lo_ep_dispatch_pack: one record per routed (token, slot), grouped by destination rank."""
+    from lightop_b200.ep import record_layout
     T, k = topk_ids.shape
+    H = xq.shape[1]
+    stride, off_s, off_m = record_layout(H)
     dest = rank_of_expert.long()[topk_ids.long()].reshape(-1)
-    order = torch.sort(dest, stable=True)[1]               # packed row -> flat (token, slot)
+    order = torch.sort(dest, stable=True)[1]               # record -> flat (token, slot)
     inv = torch.empty(T * k, dtype=torch.int32)
     inv[order] = torch.arange(T * k, dtype=torch.int32)
     tok = order // k
-    return xq[tok].contiguous(), xs[tok].contiguous(), inv.view(T, k)
+    packed = torch.zeros(T * k, stride, dtype=torch.uint8)
+    packed[:, :H] = xq[tok].view(torch.uint8)
+    packed[:, off_s:off_m] = xs[tok].contiguous().view(torch.uint8).reshape(T * k, -1)
+    e_local = (topk_ids.reshape(-1)[order].long() % experts_per_rank).to(torch.int32)
+    packed[:, off_m:off_m + 4] = e_local.view(torch.uint8).reshape(-1, 4)
+    packed[:, off_m + 4:off_m + 8] = topk_weights.reshape(-1)[order].float().contiguous().view(torch.uint8).reshape(-1, 4)
+    counts = torch.bincount(dest, minlength=world).to(torch.int32)
+    return packed, inv.view(T, k), counts
 
 
 def _combine_torch(rows_back, topk_ids, inv):
@@ -39,8 +50,14 @@ def _combine_torch(rows_back, topk_ids, inv):
 
 
 def _make_expert_fn(w1, w2, w1_s, w2_s):
-    def fn(rq, rs, r_expert, r_weight):
+    def fn(packed):
+        from lightop_b200.ep import record_layout
         H = w2.shape[1]
+        stride, off_s, off_m = record_layout(H)
+        rq = packed[:, :H].contiguous().view(torch.int8)
+        rs = packed[:, off_s:off_m].contiguous().view(torch.float32)
+        r_expert = packed[:, off_m:off_m + 4].contiguous().view(torch.int32).reshape(-1)
+        r_weight = packed[:, off_m + 4:off_m + 8].contiguous().view(torch.float32).reshape(-1)
         out = torch.zeros(rq.shape[0], H, dtype=torch.bfloat16)
         for e in range(w1.shape[0]):
             m = r_expert == e
@@ -76,12 +93,10 @@ def _worker(rank, world, port, q, mode):
             except ValueError as e:
                 q.put((rank, "ValueError"))
             return
-        # "pipelined": three micro-batches of 7..9 tokens, so the asynchronous dispatch / combine schedule runs
-        mb_kw = dict(micro_batches=3, micro_batch_min_tokens=7) if mode == "pipelined" else {}
         layer = ExpertParallelMoE(w1[sl], w2[sl], w1_s[sl], w2_s[sl], E,
                                   quant_fn=lambda t: O.group_quant_int8(t.contiguous(), 128), pack_fn=_pack_torch,
                                   expert_fn=_make_expert_fn(w1[sl], w2[sl], w1_s[sl], w2_s[sl]),
-                                  combine_fn=_combine_torch, **mb_kw)
+                                  combine_fn=_combine_torch)
         y = layer.forward(x, w, ids)
         y_ref = O.fused_moe_block_int8(x, w1, w2, w1_s, w2_s, w, ids)
         send, recv = layer.last_counts
@@ -109,13 +124,6 @@ def test_ep_two_ranks_match_single_process_oracle():
     assert [r[1] for r in res] == [True, True], res
     assert all(r[2] for r in res)
     # what rank 0 sends to rank 1 is what rank 1 receives from rank 0
-    assert res[0][3][1] == res[1][4][0] and res[1][3][0] == res[0][4][1]
-
-
-def test_ep_micro_batched_schedule_gives_the_same_bits():
-    res = _run("pipelined")
-    assert [r[1] for r in res] == [True, True], res
-    assert all(r[2] for r in res)
     assert res[0][3][1] == res[1][4][0] and res[1][3][0] == res[0][4][1]
 
 

@@ -303,16 +303,16 @@ def test_expert_rows_entry_point_and_ep_driver_world1(lo):
     try:
         layer = ExpertParallelMoE(w1.to(DEV), w2.to(DEV), w1_s.to(DEV), w2_s.to(DEV), E)
         y = layer.forward(x.to(DEV), w.to(DEV), ids.to(DEV))
-        # the micro-batched schedule (asynchronous exchanges overlapping the expert kernels): same bits
-        piped = ExpertParallelMoE(w1.to(DEV), w2.to(DEV), w1_s.to(DEV), w2_s.to(DEV), E, micro_batches=3,
-                                  micro_batch_min_tokens=16)
-        y3 = piped.forward(x.to(DEV), w.to(DEV), ids.to(DEV))
+        layer.profile = True
+        y3 = layer.forward(x.to(DEV), w.to(DEV), ids.to(DEV))
+        stages = layer.stage_ms()
         torch.cuda.synchronize()
         lo.check_device_status()
     finally:
         dist.destroy_process_group()
     assert torch.equal(y, base)
     assert torch.equal(y3, base)
+    assert set(stages) == {"quantise", "pack", "counts", "dispatch", "experts", "combine", "gather"}
     assert_out_close(y, O.fused_moe_block_int8(x, w1, w2, w1_s, w2_s, w, ids), "ep world 1")
 
 
