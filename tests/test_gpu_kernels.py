@@ -37,6 +37,19 @@ def test_group_quant_golden(lo, small, golden_dir):
     assert torch.equal(q.cpu(), gold["xq"]) and torch.equal(s.cpu(), gold["xs"])
 
 
+def test_quantisers_match_the_reference_triton_kernels(lo, golden_dir):
+    """Both quantisation kernels against the outputs of the reference's own Triton kernels
+    (layers/gemm/int8_utils.py:21-71, 74-193; vectors produced by tests/golden/make_triton_golden.py): bit-equal."""
+    cases = torch.load(os.path.join(golden_dir, "triton_quant_cases.pt"))
+    for name, c in cases.items():
+        g = torch.Generator().manual_seed(c["seed"])
+        x = (torch.randn(c["rows"], c["cols"], generator=g) * 3.0).to(getattr(torch, c["dtype"])).to(DEV)
+        q, s = lo.quant.per_token_group_quant_int8(x, 128)
+        assert torch.equal(q.cpu(), c["group_q"]) and torch.equal(s.cpu(), c["group_s"]), name
+        q, s = lo.quant.per_token_quant_int8(x)
+        assert torch.equal(q.cpu(), c["token_q"]) and torch.equal(s.cpu(), c["token_s"]), name
+
+
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
 @pytest.mark.parametrize("shape,group", [((1, 128), 128), ((7, 384), 128), ((33, 7168), 128), ((5, 3, 256), 64), ((9, 512), 256)])
 def test_group_quant_bit_exact(lo, dtype, shape, group):

@@ -120,3 +120,18 @@ def test_oracle_equals_reference_functions_on_fresh_inputs():
             a = O.align_block_size(ids, E, bs)
             b = align(ids.reshape(-1).long(), E, bs)
             assert all(torch.equal(u, v.cpu()) for u, v in zip(a, b))
+
+
+def test_quantisers_match_the_reference_triton_kernels(golden_dir):
+    """The two restated quantisers against the outputs of the reference's own Triton kernels
+    (layers/gemm/int8_utils.py:21-71, 74-193), run in Triton's interpreter by tests/golden/make_triton_golden.py."""
+    from oracle import moe_channel_int8 as OC
+    cases = torch.load(os.path.join(golden_dir, "triton_quant_cases.pt"))
+    assert len(cases) >= 6
+    for name, c in cases.items():
+        g = torch.Generator().manual_seed(c["seed"])
+        x = (torch.randn(c["rows"], c["cols"], generator=g) * 3.0).to(getattr(torch, c["dtype"]))
+        q, s = O.group_quant_int8(x, 128)
+        assert torch.equal(q, c["group_q"]) and torch.equal(s, c["group_s"]), name
+        q, s = OC.per_token_quant_int8(x)
+        assert torch.equal(q, c["token_q"]) and torch.equal(s, c["token_s"]), name
