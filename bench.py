@@ -548,16 +548,25 @@ def ep_parity_check(lightop_b200, synthetic, ExpertParallelMoE, dist, rank, worl
                                                      w1_scale=w1_s, w2_scale=w2_s)
     El = E // world
     sl = slice(rank * El, (rank + 1) * El)
-    layer = ExpertParallelMoE(w1[sl].contiguous(), w2[sl].contiguous(), w1_s[sl].contiguous(), w2_s[sl].contiguous(), E)
-    y = layer.forward(x, tw, ti)
-    torch.cuda.synchronize()
-    lightop_b200.check_device_status(dev)
-    equal = torch.tensor([1 if torch.equal(y, local) else 0], dtype=torch.int32, device=dev)
-    maxdiff = (y.float() - local.float()).abs().max().reshape(1)
-    dist.all_reduce(equal, op=dist.ReduceOp.MIN)
-    dist.all_reduce(maxdiff, op=dist.ReduceOp.MAX)
-    send, recv = layer.last_counts
-    return {"bit_equal": bool(equal.item() == 1), "ranks": world, "max_abs_diff": float(maxdiff.item()),
+    ok, worst, send = True, 0.0, None
+    per_transport = {}
+    for transport in ("peer", "collective"):
+        layer = ExpertParallelMoE(w1[sl].contiguous(), w2[sl].contiguous(), w1_s[sl].contiguous(), w2_s[sl].contiguous(), E,
+                                  transport=transport)
+        y = layer.forward(x, tw, ti)
+        y = layer.forward(x, tw, ti)         # a second step reuses the landing zones
+        torch.cuda.synchronize()
+        lightop_b200.check_device_status(dev)
+        equal = torch.tensor([1 if torch.equal(y, local) else 0], dtype=torch.int32, device=dev)
+        maxdiff = (y.float() - local.float()).abs().max().reshape(1)
+        dist.all_reduce(equal, op=dist.ReduceOp.MIN)
+        dist.all_reduce(maxdiff, op=dist.ReduceOp.MAX)
+        per_transport[transport] = bool(equal.item() == 1)
+        ok = ok and per_transport[transport]
+        worst = max(worst, float(maxdiff.item()))
+        send, recv = layer.last_counts
+        layer.close()
+    return {"bit_equal": ok, "ranks": world, "max_abs_diff": worst, "per_transport": per_transport,
             "case": {"E": E, "top_k": k, "M_per_rank": M, "hidden": H, "intermediate": I},
             "rows_sent_to_peers_rank0": sum(send) - send[rank],
             "against": "fused_experts_impl_int8 with all experts on the rank's own GPU, same tokens"}
@@ -633,6 +642,18 @@ def run_ep(args, rank: int, world: int, dev: torch.device):
             acc[kname] = acc.get(kname, 0.0) + v / 3
     layer.profile = False
     lightop_b200.check_device_status(dev)
+    # the same step with the exchange as NCCL all-to-all collectives, for comparison
+    other = ExpertParallelMoE(w1, w2, w1_s, w2_s, E, transport="collective" if layer.transport == "peer" else "peer")
+
+    def step_other():
+        lightop_b200.moe.topk_softmax(tw[0], ti[0], None, logits, True)
+        holder["y2"] = other.forward(x, tw[0], ti[0])
+    for _ in range(3):
+        step_other()
+    other_ms = timed(lambda n: cuda_time_ms(step_other, n, stream), 5) / 5
+    same_bits = torch.tensor([1 if torch.equal(holder["y"], holder["y2"]) else 0], dtype=torch.int32, device=dev)
+    dist.all_reduce(same_bits, op=dist.ReduceOp.MIN)
+    other.close()
 
     send_counts, recv_counts = layer.last_counts
     rows_recv = sum(recv_counts)
@@ -655,6 +676,12 @@ def run_ep(args, rank: int, world: int, dev: torch.device):
         "config": make_config(name, cfg, world),
         "ep": {"experts_per_rank": E_local, "rows_received_rank0": rows_recv, "rows_sent_to_peers_rank0": remote_rows,
                "dispatch_bytes_per_row": int(lib.lo_ep_dispatch_row_bytes(H)), "combine_bytes_per_row": 2 * H,
+               "transport": layer.transport,
+               "transport_how": ("records and result rows are stored into the destination rank's device memory by the "
+                                 "dispatch kernel and by the down GEMM's epilogue (plain stores over NVLink); per step one "
+                                 "all-gather of the counts and two one-word all-reduces as barriers")
+               if layer.transport == "peer" else "three all-to-all collectives per step (counts, records, result rows)",
+               "other_transport": {"name": other.transport, "ms_per_step": other_ms, "same_bits": bool(same_bits.item() == 1)},
                "collectives_per_step": 3},
         "ep_parity": parity,
         "stage_ms": acc, "comm_and_glue_frac_of_step": comm_glue / max(sum(acc.values()), 1e-9),

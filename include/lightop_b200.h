@@ -225,6 +225,20 @@ int lo_expert_rows_block_int8_packed(const uint8_t *packed, int64_t T, const int
                                      void *out, void *workspace, size_t workspace_bytes, int32_t *status, void *stream);
 
 /*
+ * The same, with every output row stored at an address of its own instead of into one matrix: the received records
+ * form `world` runs (source rank s sent records seg_first[s] .. seg_first[s + 1] - 1; seg_first has world + 1
+ * entries, device memory) and record r of run s is written, as H bf16, to seg_ret[s] + (r - seg_first[s]) * 2H
+ * (seg_ret: world device-side addresses in this process's address space, local memory or a mapping of a peer's
+ * buffer from lo_peer_open; 0 = drop the run).  The down GEMM's epilogue stores the rows with plain 16-byte
+ * stores, so the combine step of expert parallelism needs no collective, only a barrier after the kernel.
+ * workspace: lo_expert_rows_packed_workspace_bytes.  No counterpart in the reference.
+ */
+int lo_expert_rows_block_int8_packed_put(const uint8_t *packed, int64_t T, const int8_t *w1, const int8_t *w2,
+                                         const float *w1_scale, const float *w2_scale, int E_local, int64_t H,
+                                         int64_t I, const int32_t *seg_first, const int64_t *seg_ret, int world,
+                                         void *workspace, size_t workspace_bytes, int32_t *status, void *stream);
+
+/*
  * Dense block-INT8 linear: C[m, n] = sum_kb (A_q[m, kb] . B_q[n, kb]) * a_s[m, kb] * b_s[n/128, kb], bf16 out.
  * Replaces: the dense block-INT8 matmul of the reference -- matmul_block_int8 / apply_w8a8_block_int8_linear
  *           (python/lightop/_lmslim_native/layers/gemm/int8_utils.py:298-429) and gemm_w8a8_asm
@@ -428,6 +442,36 @@ int lo_ep_dispatch_pack(const int8_t *aq, const float *aq_scale, const void *top
                         const float *topk_weights, const int32_t *rank_of_expert, int64_t T, int k, int64_t H,
                         int experts_per_rank, int world, uint8_t *packed, int32_t *dest_rank, int32_t *inv_perm,
                         int32_t *counts, void *stream);
+
+/*
+ * The two halves of lo_ep_dispatch_pack for a dispatch without a collective.  lo_ep_dispatch_plan computes only the
+ * bookkeeping (dest_rank, inv_perm, counts as above).  Once the ranks have exchanged their counts,
+ * lo_ep_dispatch_put writes the record of every (token, slot) straight to its destination: seg_first[d] is the
+ * packed position of this rank's first record for rank d and seg_dst[d] the address where that record belongs in
+ * rank d's receive buffer (both device arrays of `world` entries; addresses in this process's address space, from
+ * lo_peer_open for the other ranks; 0 = send nothing to d).  Plain stores only.  No counterpart in the reference.
+ */
+int lo_ep_dispatch_plan(const void *topk_ids, int ids_dtype, const int32_t *rank_of_expert, int64_t T, int k,
+                        int world, int32_t *dest_rank, int32_t *inv_perm, int32_t *counts, void *stream);
+int lo_ep_dispatch_put(const int8_t *aq, const float *aq_scale, const void *topk_ids, int ids_dtype,
+                       const float *topk_weights, const int32_t *rank_of_expert, const int32_t *inv_perm,
+                       int64_t T, int k, int64_t H, int experts_per_rank, int world, const int32_t *seg_first,
+                       const int64_t *seg_dst, void *stream);
+
+/*
+ * Device buffers that other processes of the node may write (the landing zones of the two calls above).
+ * lo_peer_alloc: a device allocation of its own on the current device.  lo_peer_export: its inter-process handle
+ * (lo_peer_handle_bytes() bytes, to be sent to the other ranks by any means).  lo_peer_open: maps a handle received
+ * from another process into this one and enables peer access; the returned address is valid on the current device.
+ * lo_peer_close / lo_peer_free undo them (close every mapping before the owner frees).  A process must not open
+ * its own handle: it uses the pointer.  No counterpart in the reference.
+ */
+int lo_peer_alloc(size_t bytes, void **ptr);
+int lo_peer_free(void *ptr);
+int lo_peer_handle_bytes(void);
+int lo_peer_export(const void *ptr, uint8_t *handle);
+int lo_peer_open(const uint8_t *handle, void **ptr);
+int lo_peer_close(void *ptr);
 
 /*
  * Per-row expert id of the aligned contiguous layout.

@@ -54,6 +54,18 @@ PROTOTYPES = {
     "lo_ep_dispatch_row_bytes": (c_int64, [c_int64]),
     "lo_ep_dispatch_pack": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int64, c_int, c_int64,
                                     c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "lo_ep_dispatch_plan": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "lo_ep_dispatch_put": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int64, c_int,
+                                   c_int64, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "lo_expert_rows_block_int8_packed_put": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                                     c_int64, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_size_t,
+                                                     c_void_p, c_void_p]),
+    "lo_peer_alloc": (c_int, [c_size_t, c_void_p]),
+    "lo_peer_free": (c_int, [c_void_p]),
+    "lo_peer_handle_bytes": (c_int, []),
+    "lo_peer_export": (c_int, [c_void_p, c_void_p]),
+    "lo_peer_open": (c_int, [c_void_p, c_void_p]),
+    "lo_peer_close": (c_int, [c_void_p]),
     "lo_expert_rows_packed_workspace_bytes": (c_size_t, [c_int64, c_int, c_int64, c_int64]),
     "lo_expert_rows_block_int8_packed": (c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                                  c_int64, c_int64, c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),

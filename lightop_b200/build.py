@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "liblightop_b200.so")
-SOURCES = ["common.cu", "quant.cu", "routing.cu", "gate.cu", "reduce.cu", "grouped_gemm.cu", "fused_moe.cu", "grouped_layouts.cu"]
+SOURCES = ["common.cu", "quant.cu", "routing.cu", "gate.cu", "reduce.cu", "grouped_gemm.cu", "fused_moe.cu", "grouped_layouts.cu", "peer.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 

@@ -101,7 +101,9 @@ int launch_permute_rows(const int8_t *A, const float *a_scale, int64_t rows_a, i
 
 // Expert id and routed weight of packed dispatch records (lo_ep_dispatch_pack) into contiguous arrays.  reduce.cu
 int launch_ep_unpack_meta(const uint8_t *packed, int64_t rows, int64_t stride, int64_t meta_off, int32_t *row_expert,
-                          float *row_weight, cudaStream_t stream);
+                          float *row_weight, cudaStream_t stream, const int32_t *seg_first = nullptr,
+                          const int64_t *seg_ret = nullptr, int world = 0, int64_t ret_row_bytes = 0,
+                          int64_t *row_dst = nullptr);
 
 // Chunk table from an existing (expert_ids, num_tokens_post_pad) pair, see routing.cu.
 int launch_chunks_from_blocks(const int32_t *expert_ids, const int32_t *num_tokens_post_pad,
@@ -138,6 +140,9 @@ struct GemmArgs {
   float act_eps;            // eps of the fused re-quantisation, already rounded to bf16
   int32_t *status;          // device word, set non-zero on a wait that ran out (may be null)
   int out_by_position;      // bf16 output row = sorted position (ids still select validity and the routed weight)
+  // single (block-scaled) only: address of output row `sorted id`, one entry per id, instead of C + id * N.  The rows
+  // may lie in another GPU's memory (a peer mapping): the epilogue writes them with plain 16-byte stores.
+  const int64_t *row_dst;
 };
 
 int launch_grouped_gemm(GemmMode mode, const GemmArgs &args, cudaStream_t stream);

@@ -506,10 +506,10 @@ namespace {
 int expert_rows_impl(const int8_t *xq, const float *xs, int64_t x_stride, const int32_t *row_expert,
                      const float *row_weight, const int8_t *w1, const int8_t *w2, const float *w1_scale,
                      const float *w2_scale, int64_t T, int E_local, int64_t H, int64_t I, void *out, void *workspace,
-                     size_t workspace_bytes, int32_t *status, void *stream) {
+                     size_t workspace_bytes, int32_t *status, void *stream, const int64_t *row_dst = nullptr) {
   LO_REQUIRE(T >= 0 && E_local >= 1 && E_local <= 1024, "expert rows: bad shape");
   if (T == 0) return LO_OK;
-  LO_REQUIRE(xq && row_expert && w1 && w2 && w1_scale && w2_scale && out && workspace, "expert rows: null pointer");
+  LO_REQUIRE(xq && row_expert && w1 && w2 && w1_scale && w2_scale && (out || row_dst) && workspace, "expert rows: null pointer");
   LO_REQUIRE(H % 128 == 0 && I % 128 == 0, "expert rows: hidden and intermediate sizes must be multiples of 128");
   LO_REQUIRE(T < (1LL << 30), "expert rows: too many rows");
   LO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & (ALIGN_BYTES - 1)) == 0, "expert rows: workspace must be 256-byte aligned");
@@ -544,6 +544,7 @@ int expert_rows_impl(const int8_t *xq, const float *xs, int64_t x_stride, const 
   g2.sorted_ids = L.sorted_ids; g2.numel_valid = T;
   g2.chunks = L.chunks; g2.num_chunks = L.header + 1;
   g2.C = static_cast<__nv_bfloat16 *>(out);      // top_k = 1: the sorted id is the row itself
+  g2.row_dst = row_dst;                          // or: every row has an address of its own
   g2.topk_weights = row_weight;
   g2.weight_mode = row_weight ? LO_WEIGHT_BF16_PRODUCT : LO_WEIGHT_NONE;
   g2.status = status;
@@ -564,14 +565,16 @@ extern "C" int lo_expert_rows_block_int8(const int8_t *xq, const float *xs, cons
 
 extern "C" size_t lo_expert_rows_packed_workspace_bytes(int64_t T, int E_local, int64_t H, int64_t I) {
   using namespace lo;
-  return carve_fused(nullptr, T, E_local, 1, H, I).bytes + 2 * (size_t)round_up(T * 4, ALIGN_BYTES);
+  return carve_fused(nullptr, T, E_local, 1, H, I).bytes + 2 * (size_t)round_up(T * 4, ALIGN_BYTES) +
+         (size_t)round_up(T * 8, ALIGN_BYTES);
 }
 
-extern "C" int lo_expert_rows_block_int8_packed(const uint8_t *packed, int64_t T, const int8_t *w1, const int8_t *w2,
-                                                const float *w1_scale, const float *w2_scale, int E_local, int64_t H,
-                                                int64_t I, void *out, void *workspace, size_t workspace_bytes,
-                                                int32_t *status, void *stream) {
-  using namespace lo;
+namespace lo {
+namespace {
+int expert_rows_packed_impl(const uint8_t *packed, int64_t T, const int8_t *w1, const int8_t *w2, const float *w1_scale,
+                            const float *w2_scale, int E_local, int64_t H, int64_t I, void *out, const int32_t *seg_first,
+                            const int64_t *seg_ret, int world, void *workspace, size_t workspace_bytes, int32_t *status,
+                            void *stream) {
   LO_REQUIRE(T >= 0 && E_local >= 1 && H % 128 == 0 && I % 128 == 0, "expert rows (packed): bad shape");
   if (T == 0) return LO_OK;
   LO_REQUIRE(packed && workspace, "expert rows (packed): null pointer");
@@ -579,16 +582,41 @@ extern "C" int lo_expert_rows_block_int8_packed(const uint8_t *packed, int64_t T
   LO_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & (ALIGN_BYTES - 1)) == 0, "expert rows (packed): workspace must be 256-byte aligned");
   const size_t fused_bytes = carve_fused(nullptr, T, E_local, 1, H, I).bytes;
   const size_t meta_bytes = (size_t)round_up(T * 4, ALIGN_BYTES);
-  LO_REQUIRE(workspace_bytes >= fused_bytes + 2 * meta_bytes, "expert rows (packed): workspace of %zu bytes, %zu needed",
-             workspace_bytes, fused_bytes + 2 * meta_bytes);
+  const size_t table_bytes = (size_t)round_up(T * 8, ALIGN_BYTES);
+  LO_REQUIRE(workspace_bytes >= fused_bytes + 2 * meta_bytes + table_bytes,
+             "expert rows (packed): workspace of %zu bytes, %zu needed", workspace_bytes, fused_bytes + 2 * meta_bytes + table_bytes);
   uint8_t *ws = static_cast<uint8_t *>(workspace);
   int32_t *row_expert = reinterpret_cast<int32_t *>(ws + fused_bytes);
   float *row_weight = reinterpret_cast<float *>(ws + fused_bytes + meta_bytes);
+  int64_t *row_dst = seg_ret ? reinterpret_cast<int64_t *>(ws + fused_bytes + 2 * meta_bytes) : nullptr;
   const int64_t stride = lo_ep_dispatch_row_bytes(H);
-  int rc = launch_ep_unpack_meta(packed, T, stride, H + 4 * (H / 128), row_expert, row_weight, static_cast<cudaStream_t>(stream));
+  int rc = launch_ep_unpack_meta(packed, T, stride, H + 4 * (H / 128), row_expert, row_weight, static_cast<cudaStream_t>(stream),
+                                 seg_first, seg_ret, world, 2 * H, row_dst);
   if (rc != LO_OK) return rc;
   return expert_rows_impl(reinterpret_cast<const int8_t *>(packed), nullptr, stride, row_expert, row_weight, w1, w2, w1_scale,
-                          w2_scale, T, E_local, H, I, out, workspace, fused_bytes, status, stream);
+                          w2_scale, T, E_local, H, I, out, workspace, fused_bytes, status, stream, row_dst);
+}
+}  // namespace
+}  // namespace lo
+
+extern "C" int lo_expert_rows_block_int8_packed(const uint8_t *packed, int64_t T, const int8_t *w1, const int8_t *w2,
+                                                const float *w1_scale, const float *w2_scale, int E_local, int64_t H,
+                                                int64_t I, void *out, void *workspace, size_t workspace_bytes,
+                                                int32_t *status, void *stream) {
+  using namespace lo;
+  LO_REQUIRE(out != nullptr || T == 0, "expert rows (packed): null pointer");
+  return expert_rows_packed_impl(packed, T, w1, w2, w1_scale, w2_scale, E_local, H, I, out, nullptr, nullptr, 0, workspace,
+                                 workspace_bytes, status, stream);
+}
+
+extern "C" int lo_expert_rows_block_int8_packed_put(const uint8_t *packed, int64_t T, const int8_t *w1, const int8_t *w2,
+                                                    const float *w1_scale, const float *w2_scale, int E_local, int64_t H,
+                                                    int64_t I, const int32_t *seg_first, const int64_t *seg_ret, int world,
+                                                    void *workspace, size_t workspace_bytes, int32_t *status, void *stream) {
+  using namespace lo;
+  LO_REQUIRE(world >= 1 && world <= 1024 && (T == 0 || (seg_first && seg_ret)), "expert rows (put): bad return route");
+  return expert_rows_packed_impl(packed, T, w1, w2, w1_scale, w2_scale, E_local, H, I, nullptr, seg_first, seg_ret, world,
+                                 workspace, workspace_bytes, status, stream);
 }
 
 // ---------------------------------------------------------------------------

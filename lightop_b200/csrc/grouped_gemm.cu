@@ -1,51 +1,52 @@
 // Grouped block-INT8 GEMM for sm_100a: TMA-fed tcgen05 kind::i8 MMAs with int32
-// partial sums in tensor memory, promoted to fp32 once per 128-wide K block.
+// partial sums in tensor memory, promoted to fp32 register sums once per 128-wide K block.
 //
 // Orientation ("swap-AB").  The 128 rows of a weight tile are the M side of the
 // MMA and the tokens of one expert are its N side (N = tokens rounded up to 16,
-// at most 128; 160 for the single-matrix block-scaled mode).  A chunk of 1..128
+// at most 160 in the block-scaled modes, 256 per channel).  A chunk of 1..160
 // tokens therefore costs one pass over the weight tile with no padding to 128
 // rows, which is what a weight-streaming (HBM-bound) MoE needs, and the same
 // kernel serves prefill and decode sizes.  In tensor memory a lane is an output
 // column n and a column is a token.
 //
-// Work item = (chunk of expert-sorted rows, 128-row output tile).  Chunk widths: gate_up
-// <=128 (two sets of running sums + two partial buffers of 128 columns fill the 512
-// columns of tensor memory), single-matrix block-scaled <=160 (sums + two partials of
-// 160), per-channel <=256.  Items are ordered chunk-major so that CTAs running side by
-// side share the chunk's activation rows, and the chunks of one expert (adjacent
-// in the table) read the same weight tiles at about the same time: weight tiles
-// are loaded with an evict-first L2 policy unless the chunk table says that
+// Work item = (chunk of expert-sorted rows, 128-row output tile; for gate_up the gate tile and
+// the up tile of the same 128 output columns, run as two passes over K).  Items are ordered
+// chunk-major so that CTAs running side by side share the chunk's activation rows, and the
+// chunks of one expert (adjacent in the table) read the same weight tiles at about the same
+// time: weight tiles are loaded with an evict-first L2 policy unless the chunk table says that
 // another chunk of the expert follows.  Persistent CTAs take items round-robin.
 //
-// Warp roles in a CTA of 20 warps:
-//   warp 0      : TMA producer (one elected lane): weight tiles and the chunk's token rows.
-//                 Token rows are read from an expert-sorted copy of the activations, so a
-//                 chunk is a run of consecutive rows and one tiled TMA load fetches it.
-//   warp 1      : MMA issuer (one elected lane); owns the tensor-memory allocation
-//   warps 2-3   : scale producers: the token scales of the K block (prefetched four K
-//                 blocks ahead) times the weight-block scale(s) -> per-step table in
-//                 shared memory
-//   warps 4-19  : promotion / epilogue (gate_up: warps 4-11 promote the gate partials, warps 12-19 the up
-//                 partials; all sixteen share the epilogue).  The fp32 running sums live in tensor memory next to
-//                 the int32 partials: per K block a warp loads 16 columns of the partial and of
-//                 the running sum, converts exactly (2^23+2^22 offset trick), multiplies by the
-//                 scale product, adds (packed f32x2; mul and add kept separate: the rounding
-//                 sequence of the reference's torch model) and stores the sum back.  All loops
-//                 over columns are rolled, so the instruction footprint is one 16-column body
-//                 however many tokens a chunk has, and a thread needs few registers, which is
-//                 what lets 16 such warps (4 per scheduler) hide the tensor-memory latency.
-// Pipelines: STAGES shared-memory stages (full/empty mbarriers) between the producers and
-// the MMA warp; NBUF tensor-memory partial buffers (tmem_full / tmem_empty) between the MMA
-// warp and the promotion warps.  A buffer holds ONE accumulator: for gate_up the gate and the
-// up partial of a K block are separate half-steps, so the MMAs of one overlap the promotion
-// of the other even when only two buffers fit.
+// Warp roles in a CTA of 20 or 24 warps:
+//   warp 0      : two TMA producers on two lanes with their own control flow: lane 0 streams
+//                 the weight tiles (HBM) into ring w[], lane 16 the chunk's token rows (L2) into
+//                 ring a[].  Token rows are read from an expert-sorted copy of the activations,
+//                 so a chunk is a run of consecutive rows and one tiled TMA load fetches it.
+//   warps 1, 3  : MMA issuers, alternating K-block steps (warp 1 alone in the per-channel
+//                 mode).  Three lanes of an issuer each follow one barrier ring (weights,
+//                 activations, free partial buffer), poll in the same instruction and agree by
+//                 a vote; lane 0 then issues the four MMAs of the step and one commit to done[].
+//                 Warp 1 owns the tensor-memory allocation.
+//   warp 2      : scale producer: the token scales of the K block (fetched two steps ahead)
+//                 times the weight-block scale -> per-step table in shared memory
+//   warps 4..   : promotion / epilogue, four warps (one per lane quarter of tensor memory) per
+//                 column group; the chunk's tokens are dealt to the groups in pieces of 16.  A
+//                 thread keeps the fp32 running sums of its output column for its pieces in
+//                 registers: per K block it loads 16 int32 partials, converts and does one
+//                 fused multiply-add per value with the scale product (packed f32x2).
+// Pipelines: the two shared-memory rings (full_w / full_a, refilled when done[] says the MMAs
+// that read a slot have completed) and NBUF tensor-memory partial buffers (done[] as "full",
+// tmem_empty as "free") between the issuers and the promotion warps.
+//
+// Epilogues run out of the register sums through a staging tile in shared memory, so that the
+// global stores are whole rows: gate_up keeps bf16(gate) there during the up pass, then forms
+// SiLU(gate)*up, the 128-wide group maximum and the int8 row; down stages bf16 rows and applies
+// the routed weight on the way out.
 //
 // Per-channel mode (one scale per token and one per output channel instead of 128x128 blocks) uses
 // the same pipeline without the promotion: a tensor-memory buffer is the int32 accumulator of a whole
 // item, summed over every K block by the tensor core, and the promotion warps only run an epilogue
 // (int32 -> fp32, times token scale, times channel scale) while the MMAs of the next items fill the
-// other buffers.  The scale-producer warps idle in that mode.
+// other buffers.  The scale-producer warp idles in that mode.
 //
 // Every wait is bounded: after about a second a waiter records a timeout in the
 // status word, raises a CTA-wide abort flag, and all roles fall through to the
@@ -385,6 +386,7 @@ struct KParams {
   float act_eps;
   int32_t *status;
   int out_by_position;      // bf16 output row = sorted position instead of the sorted id
+  const int64_t *row_dst;   // single mode: address of the output row of every sorted id (null: C + id * n_store)
 };
 
 // Four tensor maps of the sorted activation matrix, box heights 16 / 32 / 64 / 128 rows.  A chunk of
@@ -649,7 +651,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       const int nt = (int)(item % p.n_tiles);
       if (ch.expert < 0) {
         // block of a non-local expert: its output rows are zero
-        if (MODE != GEMM_GATE_UP) {
+        if (MODE != GEMM_GATE_UP && p.C != nullptr) {
           for (int t = cg; t < ch.rows; t += NCG) {
             const int32_t sid = p.sorted_ids ? p.sorted_ids[ch.row0 + t] : ch.row0 + t;
             if (sid >= 0 && sid < p.numel_valid && (int64_t)nt * TILE_N + n_local < p.n_store)
@@ -673,10 +675,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
       constexpr int NPF = ((A_ROWS / 16 + NCG - 1) / NCG + 1) / 2;   // sets of 32 tokens that cover a group's pieces
       int32_t sid_r[NPF];
       float wgt_r[NPF];
+      // single mode: address of the row's first output column (0 = no row), so that the epilogue's row stores
+      // serve a table of row addresses (rows in a peer's memory) and the plain matrix alike
+      unsigned long long rowp_r[MODE == GEMM_SINGLE ? NPF : 1];
+      rowp_r[0] = 0ull;
 #pragma unroll
       for (int u = 0; u < NPF; ++u) {
         sid_r[u] = -1;
         wgt_r[u] = 0.f;
+        if (MODE == GEMM_SINGLE) rowp_r[MODE == GEMM_SINGLE ? u : 0] = 0ull;
         if (MODE != GEMM_GATE_UP || p.weight_mode != LO_WEIGHT_NONE) {
           const int t = col_begin + u * 32 + lane;
           if (u * 32 + lane < my_p * 16 && t < ch.rows) {
@@ -684,7 +691,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
             int32_t sid = p.sorted_ids ? p.sorted_ids[ch.row0 + t] : ch.row0 + t;
             if (sid < 0 || sid >= p.numel_valid) sid = -1;
             if (sid >= 0 && p.weight_mode != LO_WEIGHT_NONE) wgt_r[u] = p.topk_weights[sid];
+            if (MODE == GEMM_SINGLE && sid >= 0 && p.row_dst != nullptr)
+              rowp_r[MODE == GEMM_SINGLE ? u : 0] = (unsigned long long)p.row_dst[sid];
             if (sid >= 0 && p.out_by_position) sid = ch.row0 + t;
+            if (MODE == GEMM_SINGLE && sid >= 0 && p.row_dst == nullptr)
+              rowp_r[MODE == GEMM_SINGLE ? u : 0] = (unsigned long long)(p.C + (int64_t)sid * p.n_store);
             sid_r[u] = sid;
           }
         }
@@ -918,7 +929,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           for (int pc = 0; pc < my_p; ++pc) {
             const float *av = &acc[0][0];
             __nv_bfloat16 *os = stg_mine + pc * 16 * TILE_N;
-            const int32_t sid_u = NPF > 1 && (pc >> 1) ? sid_r[NPF - 1] : sid_r[0];
+            const unsigned long long rowp_u = NPF > 1 && (pc >> 1) ? rowp_r[NPF - 1] : rowp_r[0];
             const float wgt_u = NPF > 1 && (pc >> 1) ? wgt_r[NPF - 1] : wgt_r[0];
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
@@ -933,13 +944,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
               const int tp = 4 * q + 2 * i + (lane >> 4);                       // token of the piece
-              const int32_t sid = __shfl_sync(0xffffffffu, sid_u, (pc & 1) * 16 + tp);
+              const unsigned long long rowp = __shfl_sync(0xffffffffu, rowp_u, (pc & 1) * 16 + tp);
               // bf16-product order: bf16(sum) * bf16(w), rounded once more: one packed multiply per two outputs
               const __nv_bfloat162 w2 = __float2bfloat162_rn(__shfl_sync(0xffffffffu, wgt_u, (pc & 1) * 16 + tp));
               const int64_t n0 = (int64_t)nt * TILE_N + (lane & 15) * 8;
-              if (sid >= 0 && n0 < p.n_store) {
+              if (rowp != 0ull && n0 < p.n_store) {
                 const uint8_t *src = &sm.staging[(col_begin + pc * 16 + tp) * OUT_ROW_BYTES + (lane & 15) * 16];
-                __nv_bfloat16 *dst = p.C + (int64_t)sid * p.n_store + n0;
+                __nv_bfloat16 *dst = reinterpret_cast<__nv_bfloat16 *>(rowp) + n0;
                 uint4 v = *reinterpret_cast<const uint4 *>(src);
                 if (p.weight_mode == LO_WEIGHT_BF16_PRODUCT) {
                   __nv_bfloat162 *h = reinterpret_cast<__nv_bfloat162 *>(&v);
@@ -1049,7 +1060,7 @@ int launch_mode(const GemmArgs &a, cudaStream_t stream) {
   p.a_scale = a.a_scale; p.b_scale = a.b_scale;
   p.n_rows_per_expert = a.n_rows_per_expert; p.n_store = a.n_store > 0 ? a.n_store : a.n_rows_per_expert; p.KB = (int)(a.K / TILE_K); p.n_tiles = a.n_tiles;
   p.sorted_ids = a.sorted_ids; p.numel_valid = a.numel_valid;
-  p.chunks = a.chunks; p.num_chunks = a.num_chunks; p.act_q = a.act_q; p.act_s = a.act_s; p.C = a.C;
+  p.chunks = a.chunks; p.num_chunks = a.num_chunks; p.act_q = a.act_q; p.act_s = a.act_s; p.C = a.C; p.row_dst = a.row_dst;
   p.topk_weights = a.topk_weights; p.weight_mode = a.weight_mode; p.act_eps = a.act_eps; p.status = a.status;
   p.out_by_position = a.out_by_position;
   const int grid = sm_count();
@@ -1071,6 +1082,9 @@ int launch_grouped_gemm(GemmMode mode, const GemmArgs &a, cudaStream_t stream) {
                  (reinterpret_cast<uintptr_t>(a.a_scale) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.b_scale) & 15) == 0,
              "grouped gemm: operands and scales must be 16-byte aligned");
   LO_REQUIRE(a.weight_mode == LO_WEIGHT_NONE || a.topk_weights != nullptr, "grouped gemm: weight mode %d needs topk_weights", a.weight_mode);
+  LO_REQUIRE(a.row_dst == nullptr || (mode == GEMM_SINGLE && a.n_rows_per_expert % 8 == 0 && a.out_by_position == 0),
+             "grouped gemm: a table of row addresses serves the single block-scaled mode with N a multiple of 8");
+  LO_REQUIRE(mode == GEMM_GATE_UP || a.C != nullptr || a.row_dst != nullptr, "grouped gemm: no output");
   // no chunk can hold more rows than max_chunk_rows (a bound the caller derives from the token count)
   const int cap = a.max_chunk_rows <= 0 ? T_MAX : a.max_chunk_rows;
   if (mode == GEMM_GATE_UP) {

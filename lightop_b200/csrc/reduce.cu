@@ -297,16 +297,58 @@ __global__ void __launch_bounds__(128) ep_pack_rows_kernel(const int8_t *__restr
   }
 }
 
+// The same record, stored straight into the destination rank's receive buffer: seg_dst[d] is the address (in this
+// process's address space: local memory or a peer mapping) where this rank's run of records for rank d begins,
+// seg_first[d] the packed position of the run's first record.  Plain 16-byte stores; nothing is read from a peer.
+template <typename IdT>
+__global__ void __launch_bounds__(128) ep_put_rows_kernel(const int8_t *__restrict__ aq, const float *__restrict__ as,
+                                                          const IdT *__restrict__ ids, const float *__restrict__ w,
+                                                          const int32_t *__restrict__ rank_of_expert,
+                                                          const int32_t *__restrict__ inv_perm,
+                                                          const int32_t *__restrict__ seg_first,
+                                                          const int64_t *__restrict__ seg_dst, int world, int k, int64_t H,
+                                                          int G, int64_t stride, int experts_per_rank, int64_t rows) {
+  const int64_t flat = blockIdx.x;
+  const int32_t pos = inv_perm[flat];
+  if (pos < 0 || pos >= rows) return;
+  const long long e = (long long)ids[flat];
+  const int d = rank_of_expert[e];
+  if (d < 0 || d >= world || seg_dst[d] == 0 || pos < seg_first[d]) return;
+  const int64_t t = flat / k;
+  uint8_t *rec = reinterpret_cast<uint8_t *>(seg_dst[d]) + (int64_t)(pos - seg_first[d]) * stride;
+  const uint4 *src = reinterpret_cast<const uint4 *>(aq + t * H);
+  uint4 *dp = reinterpret_cast<uint4 *>(rec);
+  for (int64_t c = threadIdx.x; c < H / 16; c += blockDim.x) dp[c] = src[c];
+  float *sc = reinterpret_cast<float *>(rec + H);
+  for (int c = threadIdx.x; c < G; c += blockDim.x) sc[c] = as[t * G + c];
+  if (threadIdx.x == 0) {
+    reinterpret_cast<int32_t *>(rec + H + 4 * (int64_t)G)[0] = (int32_t)(e % experts_per_rank);
+    reinterpret_cast<float *>(rec + H + 4 * (int64_t)G)[1] = w[flat];
+  }
+}
+
 // Expert id and routed weight of every received record into contiguous arrays (the alignment kernel wants the ids
 // as one array).
 __global__ void __launch_bounds__(256) ep_unpack_meta_kernel(const uint8_t *__restrict__ packed, int64_t rows, int64_t stride,
                                                              int64_t meta_off, int32_t *__restrict__ row_expert,
-                                                             float *__restrict__ row_weight) {
+                                                             float *__restrict__ row_weight,
+                                                             const int32_t *__restrict__ seg_first,
+                                                             const int64_t *__restrict__ seg_ret, int world,
+                                                             int64_t ret_row_bytes, int64_t *__restrict__ row_dst) {
   const int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= rows) return;
   const uint8_t *rec = packed + r * stride + meta_off;
   row_expert[r] = reinterpret_cast<const int32_t *>(rec)[0];
   row_weight[r] = reinterpret_cast<const float *>(rec)[1];
+  if (row_dst != nullptr) {
+    // Return route of the row: record r belongs to the run of source rank s with seg_first[s] <= r < seg_first[s + 1]
+    // and goes back to seg_ret[s] + (r - seg_first[s]) rows (an address in rank s's return buffer).  A row outside
+    // every run, or of a run without an address, gets 0 = "do not store".
+    int64_t dst = 0;
+    for (int s = 0; s < world; ++s)
+      if (r >= seg_first[s] && r < seg_first[s + 1] && seg_ret[s] != 0) dst = seg_ret[s] + (r - seg_first[s]) * ret_row_bytes;
+    row_dst[r] = dst;
+  }
 }
 
 template <typename IdT>
@@ -375,9 +417,11 @@ int launch_permute_rows(const int8_t *A, const float *a_scale, int64_t rows_a, i
 }
 
 int launch_ep_unpack_meta(const uint8_t *packed, int64_t rows, int64_t stride, int64_t meta_off, int32_t *row_expert,
-                          float *row_weight, cudaStream_t stream) {
+                          float *row_weight, cudaStream_t stream, const int32_t *seg_first, const int64_t *seg_ret,
+                          int world, int64_t ret_row_bytes, int64_t *row_dst) {
   if (rows <= 0) return LO_OK;
-  ep_unpack_meta_kernel<<<(unsigned)ceil_div(rows, 256), 256, 0, stream>>>(packed, rows, stride, meta_off, row_expert, row_weight);
+  ep_unpack_meta_kernel<<<(unsigned)ceil_div(rows, 256), 256, 0, stream>>>(packed, rows, stride, meta_off, row_expert, row_weight,
+                                                                          seg_first, seg_ret, world, ret_row_bytes, row_dst);
   LO_LAUNCH_OK("ep_unpack_meta_kernel");
   return LO_OK;
 }
@@ -481,6 +525,50 @@ extern "C" int lo_ep_dispatch_pack(const int8_t *aq, const float *aq_scale, cons
     ep_pack_rows_kernel<int32_t><<<(unsigned)rows, 128, 0, st>>>(aq, aq_scale, static_cast<const int32_t *>(topk_ids), topk_weights,
                                                                  inv_perm, packed, k, H, (int)(H / 128), stride, experts_per_rank, rows);
   LO_LAUNCH_OK("ep_pack_rows_kernel");
+  return LO_OK;
+}
+
+extern "C" int lo_ep_dispatch_plan(const void *topk_ids, int ids_dtype, const int32_t *rank_of_expert, int64_t T, int k,
+                                   int world, int32_t *dest_rank, int32_t *inv_perm, int32_t *counts, void *stream) {
+  using namespace lo;
+  LO_REQUIRE(world >= 1 && world <= 1024, "ep_dispatch_plan: bad sharding");
+  LO_REQUIRE(k >= 1 && T >= 0, "ep_dispatch_plan: bad shape");
+  LO_REQUIRE(topk_ids && rank_of_expert && dest_rank && inv_perm && counts, "ep_dispatch_plan: null pointer");
+  LO_REQUIRE(T * k <= 0x7fffffffLL, "ep_dispatch_plan: too many (token, slot) pairs");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t rows = T * k;
+  if (ids_dtype == LO_I64)
+    return launch_ep_plan<int64_t>(topk_ids, rows, rank_of_expert, nullptr, world, 1, dest_rank, rows, inv_perm, st, counts);
+  if (ids_dtype == LO_I32)
+    return launch_ep_plan<int32_t>(topk_ids, rows, rank_of_expert, nullptr, world, 1, dest_rank, rows, inv_perm, st, counts);
+  return fail(LO_ERR_UNSUPPORTED, "ep_dispatch_plan: unsupported id dtype code %d", ids_dtype);
+}
+
+extern "C" int lo_ep_dispatch_put(const int8_t *aq, const float *aq_scale, const void *topk_ids, int ids_dtype,
+                                  const float *topk_weights, const int32_t *rank_of_expert, const int32_t *inv_perm,
+                                  int64_t T, int k, int64_t H, int experts_per_rank, int world, const int32_t *seg_first,
+                                  const int64_t *seg_dst, void *stream) {
+  using namespace lo;
+  LO_REQUIRE(world >= 1 && world <= 1024 && experts_per_rank >= 1, "ep_dispatch_put: bad sharding");
+  LO_REQUIRE(k >= 1 && T >= 0 && H % 128 == 0, "ep_dispatch_put: bad shape");
+  LO_REQUIRE(aq && aq_scale && topk_ids && topk_weights && rank_of_expert && inv_perm && seg_first && seg_dst,
+             "ep_dispatch_put: null pointer");
+  LO_REQUIRE(T * k <= 0x7fffffffLL, "ep_dispatch_put: too many (token, slot) pairs");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t rows = T * k;
+  if (rows == 0) return LO_OK;
+  const int64_t stride = lo_ep_dispatch_row_bytes(H);
+  if (ids_dtype == LO_I64)
+    ep_put_rows_kernel<int64_t><<<(unsigned)rows, 128, 0, st>>>(aq, aq_scale, static_cast<const int64_t *>(topk_ids), topk_weights,
+                                                                rank_of_expert, inv_perm, seg_first, seg_dst, world, k, H,
+                                                                (int)(H / 128), stride, experts_per_rank, rows);
+  else if (ids_dtype == LO_I32)
+    ep_put_rows_kernel<int32_t><<<(unsigned)rows, 128, 0, st>>>(aq, aq_scale, static_cast<const int32_t *>(topk_ids), topk_weights,
+                                                                rank_of_expert, inv_perm, seg_first, seg_dst, world, k, H,
+                                                                (int)(H / 128), stride, experts_per_rank, rows);
+  else
+    return fail(LO_ERR_UNSUPPORTED, "ep_dispatch_put: unsupported id dtype code %d", ids_dtype);
+  LO_LAUNCH_OK("ep_put_rows_kernel");
   return LO_OK;
 }
 

@@ -19,12 +19,24 @@ One process per GPU.  Rank r owns experts [r*E/R, (r+1)*E/R).  A step on every r
 The reference contains only the local halves of 2 and 7 (csrc/kernels/deepgemm_moe_permute.cu;
 sequence in test/test_ep_gather_scatter_moe.py:205-296) and simulates EP on one device with an
 expert_map (test/moe_w8a8/test_kernel_moe_ep8.py:98-153); the exchange is left to the serving stack.
-Here it is torch.distributed all_to_all_single (NCCL over NVLink on GPUs, gloo on CPU for the tests of
-the bookkeeping).  The quantise / pack / expert / combine steps are hooks so that the CPU tests can run the
-same driver with torch stand-ins; the defaults are the CUDA kernels.
+Two transports carry steps 4 and 6:
+
+  * "peer" (the default on GPUs): every rank owns two landing zones in device memory that the other ranks have
+    mapped (lo_peer_alloc / lo_peer_export / lo_peer_open).  The dispatch kernel stores each record straight into
+    the destination rank's receive buffer (lo_ep_dispatch_put) and the down GEMM's epilogue stores each result row
+    straight into the source rank's return buffer (lo_expert_rows_block_int8_packed_put), both with plain stores
+    over NVLink, so the transfers ride inside the kernels that produce the data; a small all-reduce after each of
+    the two kernels tells every rank that its zone is complete.  Step 3 becomes an all-gather of the counts, from
+    which every rank derives where its runs of records begin in the other ranks' zones.
+  * "collective": torch.distributed all_to_all_single (NCCL on GPUs, gloo on CPU for the tests of the
+    bookkeeping).
+
+Both give the same bits.  The quantise / pack / expert / combine steps are hooks so that the CPU tests can run the
+collective driver with torch stand-ins; the defaults are the CUDA kernels.
 """
 from __future__ import annotations
 
+import os
 from typing import Callable, Dict, List, Optional
 
 import torch
@@ -104,18 +116,100 @@ class _CudaExperts:
         return out
 
 
+# --------------------------------------------------------------------------- peer landing zones
+
+class _PeerZones:
+    """This rank's receive and return buffers and the mappings of every other rank's.  All methods that change the
+    buffers are collective over the group and take arguments that are equal on every rank."""
+
+    def __init__(self, group, dev, rank, world):
+        from . import _lib
+        self.lib = _lib.load()
+        self.group, self.dev, self.rank, self.world = group, dev, rank, world
+        self.recv_bytes = 0
+        self.ret_bytes = 0
+        self.own = [0, 0]                                   # receive zone, return zone
+        self.peer_recv = [0] * world
+        self.peer_ret = [0] * world
+        self._opened: List[int] = []
+
+    def _check(self, st, what):
+        from . import _lib
+        _lib.check(st, what)
+
+    def ensure(self, recv_bytes: int, ret_bytes: int) -> None:
+        """Grow the zones to at least these sizes (the same numbers on every rank)."""
+        if recv_bytes <= self.recv_bytes and ret_bytes <= self.ret_bytes:
+            return
+        import ctypes
+        recv_bytes = max(self.recv_bytes, (recv_bytes * 5 // 4 + 4095) // 4096 * 4096)
+        ret_bytes = max(self.ret_bytes, (ret_bytes * 5 // 4 + 4095) // 4096 * 4096)
+        # nobody may still be writing into a zone that is about to go away
+        torch.cuda.synchronize(self.dev)
+        dist.barrier(group=self.group)
+        self.release()
+        hb = int(self.lib.lo_peer_handle_bytes())
+        mine = torch.zeros(2, hb, dtype=torch.uint8)
+        with torch.cuda.device(self.dev):
+            for i, nbytes in enumerate((recv_bytes, ret_bytes)):
+                p = ctypes.c_void_p()
+                self._check(self.lib.lo_peer_alloc(nbytes, ctypes.byref(p)), "lo_peer_alloc")
+                self.own[i] = int(p.value)
+                buf = (ctypes.c_uint8 * hb)()
+                self._check(self.lib.lo_peer_export(self.own[i], buf), "lo_peer_export")
+                mine[i] = torch.frombuffer(bytearray(buf), dtype=torch.uint8)
+            everyone = torch.empty(self.world, 2, hb, dtype=torch.uint8, device=self.dev)
+            dist.all_gather_into_tensor(everyone, mine.to(self.dev), group=self.group)
+            everyone = everyone.cpu()
+            for r in range(self.world):
+                if r == self.rank:
+                    self.peer_recv[r], self.peer_ret[r] = self.own
+                    continue
+                got = []
+                for i in range(2):
+                    raw = bytes(everyone[r, i].tolist())
+                    p = ctypes.c_void_p()
+                    self._check(self.lib.lo_peer_open(raw, ctypes.byref(p)), "lo_peer_open")
+                    got.append(int(p.value))
+                    self._opened.append(int(p.value))
+                self.peer_recv[r], self.peer_ret[r] = got
+        self.recv_bytes, self.ret_bytes = recv_bytes, ret_bytes
+        dist.barrier(group=self.group)
+
+    def release(self) -> None:
+        """Unmap the peers' zones, then (after everyone has) free this rank's.  Collective."""
+        if not self.own[0] and not self._opened:
+            return
+        with torch.cuda.device(self.dev):
+            for p in self._opened:
+                self.lib.lo_peer_close(p)
+            self._opened = []
+            dist.barrier(group=self.group)
+            for i in range(2):
+                if self.own[i]:
+                    self.lib.lo_peer_free(self.own[i])
+                    self.own[i] = 0
+        self.peer_recv = [0] * self.world
+        self.peer_ret = [0] * self.world
+        self.recv_bytes = self.ret_bytes = 0
+
+
 # --------------------------------------------------------------------------- driver
 
 STAGES = ("quantise", "pack", "counts", "dispatch", "experts", "combine", "gather")
 
 
 class ExpertParallelMoE:
-    """Block-INT8 MoE layer with the experts of this rank; ``forward`` is collective over ``group``."""
+    """Block-INT8 MoE layer with the experts of this rank; ``forward`` is collective over ``group``.
+
+    transport: "peer", "collective" or None = peer on CUDA with the built-in hooks (LIGHTOP_B200_EP_TRANSPORT overrides
+    the default), collective otherwise."""
 
     def __init__(self, w1_local: torch.Tensor, w2_local: torch.Tensor, w1_scale: torch.Tensor,
                  w2_scale: torch.Tensor, num_experts_global: int, group=None,
                  quant_fn: Optional[Callable] = None, pack_fn: Optional[Callable] = None,
-                 expert_fn: Optional[Callable] = None, combine_fn: Optional[Callable] = None):
+                 expert_fn: Optional[Callable] = None, combine_fn: Optional[Callable] = None,
+                 transport: Optional[str] = None):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -124,7 +218,16 @@ class ExpertParallelMoE:
             raise ValueError(f"{num_experts_global} experts do not split into {self.world} shards of {self.E_local}")
         self.E = num_experts_global
         dev = w1_local.device
+        self.dev = dev
         self.rank_of_expert = (torch.arange(self.E, device=dev) // self.E_local).to(torch.int32)
+        builtin = pack_fn is None and expert_fn is None and combine_fn is None and quant_fn is None
+        if transport is None:
+            transport = os.environ.get("LIGHTOP_B200_EP_TRANSPORT") or ("peer" if builtin and dev.type == "cuda" else "collective")
+        if transport not in ("peer", "collective"):
+            raise ValueError(f"unknown transport {transport!r}")
+        if transport == "peer" and not (builtin and dev.type == "cuda"):
+            raise ValueError("the peer transport runs the built-in CUDA kernels only")
+        self.transport = transport
         self.quant_fn = quant_fn or _cuda_quant
         self.pack_fn = pack_fn or _cuda_pack
         self.expert_fn = expert_fn or _CudaExperts(w1_local, w2_local, w1_scale, w2_scale)
@@ -132,6 +235,14 @@ class ExpertParallelMoE:
         self.last_counts = None            # (send_counts, recv_counts) of the last step, for inspection
         self.profile = False               # record a CUDA event after every stage of forward()
         self._events: List[torch.cuda.Event] = []
+        self._zones = _PeerZones(group, dev, self.rank, self.world) if transport == "peer" else None
+        self._flag = torch.zeros(1, dtype=torch.int32, device=dev) if transport == "peer" else None
+
+    def close(self) -> None:
+        """Give the landing zones back (collective; only the peer transport holds any)."""
+        if self._zones is not None:
+            torch.cuda.synchronize(self.dev)
+            self._zones.release()
 
     def _all_to_all(self, send: torch.Tensor, send_counts: List[int], recv_counts: List[int]) -> torch.Tensor:
         recv = torch.empty((sum(recv_counts),) + tuple(send.shape[1:]), dtype=send.dtype, device=send.device)
@@ -153,6 +264,8 @@ class ExpertParallelMoE:
 
     def forward(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
         """Collective over the group: every rank calls it with its own tokens."""
+        if self.transport == "peer":
+            return self._forward_peer(x, topk_weights, topk_ids)
         T, k = topk_ids.shape
         self._events = []
         self._mark()
@@ -178,4 +291,96 @@ class ExpertParallelMoE:
         self._mark()
         y = self.combine_fn(back, topk_ids, inv)
         self._mark()
+        return y
+
+    def _everyone_done(self):
+        """Every rank's kernels queued so far have completed (their stores to this rank's zones have landed) before
+        anything queued after this call runs: a one-word all-reduce in stream order."""
+        dist.all_reduce(self._flag, group=self.group)
+
+    def _forward_peer(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
+        from . import _lib, device_status_word
+        lib = _lib.load()
+        T, k = topk_ids.shape
+        H = x.shape[1]
+        dev, R, me = self.dev, self.world, self.rank
+        ex = self.expert_fn
+        stride = int(lib.lo_ep_dispatch_row_bytes(H))
+        self._events = []
+        self._mark()
+        xq, xs = self.quant_fn(x)
+        self._mark()
+        ids = topk_ids.contiguous()
+        w = topk_weights.to(torch.float32).contiguous()
+        dest = torch.empty(T * k, dtype=torch.int32, device=dev)
+        inv = torch.empty(T, k, dtype=torch.int32, device=dev)
+        counts = torch.empty(R, dtype=torch.int32, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(lib.lo_ep_dispatch_plan(_lib.ptr(ids), _lib.dtype_code(ids.dtype), _lib.ptr(self.rank_of_expert), T, k, R,
+                                               _lib.ptr(dest), _lib.ptr(inv), _lib.ptr(counts), _lib.current_stream(dev)),
+                       "lo_ep_dispatch_plan")
+        self._mark()
+        # the whole R x R matrix of record counts on every rank (the step's one host read): it fixes where every
+        # run of records begins in every zone
+        mat_t = torch.empty(R, R, dtype=torch.int32, device=dev)
+        dist.all_gather_into_tensor(mat_t, counts, group=self.group)
+        mat = mat_t.tolist()                                   # mat[s][d]: records rank s sends to rank d
+        send_counts = [int(v) for v in mat[me]]
+        recv_counts = [int(mat[s][me]) for s in range(R)]
+        if sum(send_counts) != T * k:
+            raise RuntimeError("dispatch bookkeeping lost rows")
+        self.last_counts = (send_counts, recv_counts)
+        rows_recv = sum(recv_counts)
+        need_recv = max(sum(mat[s][d] for s in range(R)) for d in range(R))
+        need_ret = max(sum(mat[s]) for s in range(R))
+        self._zones.ensure(max(need_recv, 1) * stride, max(need_ret, 1) * 2 * H)
+        z = self._zones
+        # my run for rank d starts behind the runs of the lower ranks; my result rows for rank s go behind those that
+        # the lower ranks return to s (the order in which s packed its records)
+        first_out, first_in, seg_dst, seg_ret = [], [], [], []
+        run = 0
+        for d in range(R):
+            first_out.append(run)
+            run += send_counts[d]
+            before = sum(mat[s][d] for s in range(me))
+            seg_dst.append(z.peer_recv[d] + before * stride if send_counts[d] else 0)
+        run = 0
+        for s_ in range(R):
+            first_in.append(run)
+            run += recv_counts[s_]
+            before = sum(mat[s_][d] for d in range(me))
+            seg_ret.append(z.peer_ret[s_] + before * 2 * H if recv_counts[s_] else 0)
+        first_in.append(run)
+        i32 = torch.tensor(first_out + first_in, dtype=torch.int32, device=dev)
+        i64 = torch.tensor(seg_dst + seg_ret, dtype=torch.int64, device=dev)
+        self._mark()
+        with torch.cuda.device(dev):
+            _lib.check(lib.lo_ep_dispatch_put(_lib.ptr(xq), _lib.ptr(xs), _lib.ptr(ids), _lib.dtype_code(ids.dtype), _lib.ptr(w),
+                                              _lib.ptr(self.rank_of_expert), _lib.ptr(inv), T, k, H, self.E_local, R,
+                                              i32.data_ptr(), i64.data_ptr(), _lib.current_stream(dev)), "lo_ep_dispatch_put")
+        self._everyone_done()
+        self._mark()
+        if rows_recv:
+            E, N, _ = ex.w1.shape
+            I = N // 2
+            nbytes = lib.lo_expert_rows_packed_workspace_bytes(rows_recv, E, H, I)
+            if ex._ws is None or ex._ws.numel() < nbytes:
+                ex._ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+            with torch.cuda.device(dev):
+                _lib.check(lib.lo_expert_rows_block_int8_packed_put(
+                    z.own[0], rows_recv, _lib.ptr(ex.w1), _lib.ptr(ex.w2), _lib.ptr(ex.w1_s), _lib.ptr(ex.w2_s), E, H, I,
+                    i32.data_ptr() + 4 * R, i64.data_ptr() + 8 * R, R, _lib.ptr(ex._ws), ex._ws.numel(),
+                    _lib.ptr(device_status_word(dev)), _lib.current_stream(dev)), "lo_expert_rows_block_int8_packed_put")
+        self._mark()
+        self._everyone_done()
+        self._mark()
+        y = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+        if T:
+            ones = torch.ones(T, k, dtype=torch.float32, device=dev)
+            with torch.cuda.device(dev):
+                _lib.check(lib.lo_ep_gather(z.own[1], _lib.ptr(ids), _lib.dtype_code(ids.dtype), _lib.ptr(ones), _lib.ptr(inv), 0,
+                                            _lib.ptr(y), T, k, H, _lib.current_stream(dev)), "lo_ep_gather")
+        self._mark()
+        # keep the small tables alive until the kernels that read them have run
+        self._keep = (i32, i64, ones if T else None, dest)
         return y

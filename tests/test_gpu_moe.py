@@ -286,8 +286,10 @@ def test_fused_zipf_imbalance(lo):
 
 # ------------------------------ expert parallelism on one device -----------------------
 
-def test_expert_rows_entry_point_and_ep_driver_world1(lo):
-    """The EP driver with a single rank (NCCL, world size 1) must give the bits of the fused layer."""
+@pytest.mark.parametrize("transport", ["peer", "collective"])
+def test_expert_rows_entry_point_and_ep_driver_world1(lo, transport):
+    """The EP driver with a single rank (NCCL, world size 1) must give the bits of the fused layer, with the records
+    and result rows carried by stores into landing zones ("peer") and by all-to-all ("collective")."""
     import socket
     import torch.distributed as dist
     from lightop_b200.ep import ExpertParallelMoE
@@ -301,17 +303,25 @@ def test_expert_rows_entry_point_and_ep_driver_world1(lo):
         port = s.getsockname()[1]
     dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1)
     try:
-        layer = ExpertParallelMoE(w1.to(DEV), w2.to(DEV), w1_s.to(DEV), w2_s.to(DEV), E)
+        layer = ExpertParallelMoE(w1.to(DEV), w2.to(DEV), w1_s.to(DEV), w2_s.to(DEV), E, transport=transport)
+        assert layer.transport == transport
         y = layer.forward(x.to(DEV), w.to(DEV), ids.to(DEV))
         layer.profile = True
         y3 = layer.forward(x.to(DEV), w.to(DEV), ids.to(DEV))
         stages = layer.stage_ms()
+        layer.profile = False
+        # a larger batch makes the peer transport grow its landing zones
+        x2, logits2 = synthetic.make_activations(3 * M, H, E, seed=23)
+        w_2, ids_2 = _route(logits2, k)
+        y4 = layer.forward(x2.to(DEV), w_2.to(DEV), ids_2.to(DEV))
         torch.cuda.synchronize()
         lo.check_device_status()
+        layer.close()
     finally:
         dist.destroy_process_group()
     assert torch.equal(y, base)
     assert torch.equal(y3, base)
+    assert torch.equal(y4, _run_fused(lo, x2, w1, w2, w1_s, w2_s, w_2, ids_2))
     assert set(stages) == {"quantise", "pack", "counts", "dispatch", "experts", "combine", "gather"}
     assert_out_close(y, O.fused_moe_block_int8(x, w1, w2, w1_s, w2_s, w, ids), "ep world 1")
 
