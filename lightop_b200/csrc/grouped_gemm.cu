@@ -61,6 +61,26 @@
 namespace lo {
 namespace {
 
+// Interval between two polls of a barrier, in nanoseconds, by role.  A polling warp competes for issue slots with the
+// promotion warps that share its scheduler, so everybody who can afford the reaction time polls slowly: the
+// producers (their rings cover several K blocks), the scale warp (a step ahead), and promotion warps with fewer
+// pieces than their neighbours.
+#ifndef LO_SLEEP_PRODUCER
+#define LO_SLEEP_PRODUCER 128u
+#endif
+#ifndef LO_SLEEP_SCALE
+#define LO_SLEEP_SCALE 128u
+#endif
+#ifndef LO_SLEEP_MMA
+#define LO_SLEEP_MMA 20u
+#endif
+#ifndef LO_SLEEP_PROMO
+#define LO_SLEEP_PROMO 32u
+#endif
+#ifndef LO_SLEEP_PROMO_SLACK
+#define LO_SLEEP_PROMO_SLACK 32u
+#endif
+
 constexpr int TILE_N = 128;      // weight rows per accumulator (MMA M)
 constexpr int TILE_K = 128;      // int8 elements (= bytes) per K block
 constexpr int T_MAX = 128;       // default bound of the rows of a chunk
@@ -170,22 +190,23 @@ constexpr long long WAIT_LIMIT_CYCLES = 3000000000ll;
 // instructions between two K blocks took several hundred cycles).  Waiters far off the critical path
 // (producers that run stages ahead, promotion warps without columns in a narrow chunk) sleep longer.
 template <class S>
-__device__ __forceinline__ bool mbar_wait(S &sm, uint64_t *bar, uint32_t parity, int32_t *status, int code, uint32_t sleep_ns = 32u) {
+__device__ __forceinline__ bool mbar_wait(S &sm, uint64_t *bar, uint32_t parity, int32_t *status, int code, uint32_t sleep_ns = LO_SLEEP_PROMO) {
   if (mbar_try_wait(bar, parity)) return true;
   long long t0 = 0;
-  uint32_t spins = 0;
   while (true) {
-    __nanosleep(sleep_ns);
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++spins & 255u) == 0u) {
-      if (sm.abort_flag) return false;
-      const long long now = clock64();
-      if (t0 == 0) t0 = now;
-      if (now - t0 > WAIT_LIMIT_CYCLES) {
-        sm.abort_flag = 1;
-        if (status) atomicCAS(status, 0, code);
-        return false;
-      }
+    // the polls between two looks at the clock carry no bookkeeping but their count
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i) {
+      __nanosleep(sleep_ns);
+      if (mbar_try_wait(bar, parity)) return true;
+    }
+    if (sm.abort_flag) return false;
+    const long long now = clock64();
+    if (t0 == 0) t0 = now;
+    if (now - t0 > WAIT_LIMIT_CYCLES) {
+      sm.abort_flag = 1;
+      if (status) atomicCAS(status, 0, code);
+      return false;
     }
   }
 }
@@ -203,22 +224,22 @@ __device__ __forceinline__ bool mbar_try_wait_addr(uint32_t bar, uint32_t parity
   return ok != 0;
 }
 template <class S>
-__device__ __forceinline__ bool mbar_wait_addr(S &sm, uint32_t bar, uint32_t parity, int32_t *status, int code, uint32_t sleep_ns = 32u) {
+__device__ __forceinline__ bool mbar_wait_addr(S &sm, uint32_t bar, uint32_t parity, int32_t *status, int code, uint32_t sleep_ns = LO_SLEEP_PROMO) {
   if (mbar_try_wait_addr(bar, parity)) return true;
   long long t0 = 0;
-  uint32_t spins = 0;
   while (true) {
-    __nanosleep(sleep_ns);
-    if (mbar_try_wait_addr(bar, parity)) return true;
-    if ((++spins & 255u) == 0u) {
-      if (sm.abort_flag) return false;
-      const long long now = clock64();
-      if (t0 == 0) t0 = now;
-      if (now - t0 > WAIT_LIMIT_CYCLES) {
-        sm.abort_flag = 1;
-        if (status) atomicCAS(status, 0, code);
-        return false;
-      }
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i) {
+      __nanosleep(sleep_ns);
+      if (mbar_try_wait_addr(bar, parity)) return true;
+    }
+    if (sm.abort_flag) return false;
+    const long long now = clock64();
+    if (t0 == 0) t0 = now;
+    if (now - t0 > WAIT_LIMIT_CYCLES) {
+      sm.abort_flag = 1;
+      if (status) atomicCAS(status, 0, code);
+      return false;
     }
   }
 }
@@ -336,18 +357,22 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
 // One promotion step on N (8 or 16) tokens of this thread's output channel: acc = fma(float(raw), scale product, acc).
 // The 128-long int8 dot is below 2^21 in magnitude, so the conversion is exact; one rounding per K block.
 // `sc_addr` is the shared-memory address of the N scale products.
+// The sums stay packed two to a 64-bit register over the whole K loop (tokens 2i and 2i + 1 in acc2[i]), so that a
+// step neither assembles nor takes apart register pairs.
 template <int N>
-__device__ __forceinline__ void promote(const uint32_t *raw, float *acc, uint32_t sc_addr) {
+__device__ __forceinline__ void promote(const uint32_t *raw, uint64_t *acc2, uint32_t sc_addr) {
+#ifdef LO_EXP_NO_ARITH
+  acc2[0] ^= (uint64_t)raw[0];      // timing experiment: no conversions, no multiply-adds, no scale loads
+  return;
+#endif
 #pragma unroll
   for (int j4 = 0; j4 < N / 4; ++j4) {
     uint64_t sc01, sc23;               // scale products of four tokens
     lds_2x64(sc_addr + 16u * j4, sc01, sc23);
     const uint64_t f01 = pack2(__int2float_rn((int32_t)raw[j4 * 4 + 0]), __int2float_rn((int32_t)raw[j4 * 4 + 1]));
     const uint64_t f23 = pack2(__int2float_rn((int32_t)raw[j4 * 4 + 2]), __int2float_rn((int32_t)raw[j4 * 4 + 3]));
-    const uint64_t a01 = fma2(f01, sc01, pack2(acc[j4 * 4 + 0], acc[j4 * 4 + 1]));
-    const uint64_t a23 = fma2(f23, sc23, pack2(acc[j4 * 4 + 2], acc[j4 * 4 + 3]));
-    unpack2(a01, acc[j4 * 4 + 0], acc[j4 * 4 + 1]);
-    unpack2(a23, acc[j4 * 4 + 2], acc[j4 * 4 + 3]);
+    acc2[j4 * 2 + 0] = fma2(f01, sc01, acc2[j4 * 2 + 0]);
+    acc2[j4 * 2 + 1] = fma2(f23, sc23, acc2[j4 * 2 + 1]);
   }
 }
 
@@ -482,7 +507,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
             const int32_t row_g = (int32_t)(ch.expert * p.n_rows_per_expert + (int64_t)(ph * p.n_tiles + nt) * TILE_N);
             for (int kb = 0; kb < KB; ++kb, ++it) {
               // slot s was read by step it - NW
-              if (it >= (uint32_t)NW && !mbar_wait(sm, &sm.done[(it - NW) % ND], ((it - NW) / ND) & 1u, p.status, 1, 128u)) { ok = false; break; }
+              if (it >= (uint32_t)NW && !mbar_wait(sm, &sm.done[(it - NW) % ND], ((it - NW) / ND) & 1u, p.status, 1, LO_SLEEP_PRODUCER)) { ok = false; break; }
               mbar_arrive_expect_tx(&sm.full_w[s], W_TILE_BYTES);
               tma_load_2d(sm.w[s], &w_map, kb * TILE_K, row_g, &sm.full_w[s], pol_w);
               s = s + 1 == NW ? 0 : s + 1;
@@ -507,7 +532,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           const uint32_t a_bytes = (16u << mi) * TILE_K + (mi2 >= 0 ? (16u << mi2) * TILE_K : 0u);
           for (int ph = 0; ph < PHASES && ok; ++ph) {
             for (int kb = 0; kb < KB; ++kb, ++it) {
-              if (it >= (uint32_t)NA && !mbar_wait(sm, &sm.done[(it - NA) % ND], ((it - NA) / ND) & 1u, p.status, 6, 128u)) { ok = false; break; }
+              if (it >= (uint32_t)NA && !mbar_wait(sm, &sm.done[(it - NA) % ND], ((it - NA) / ND) & 1u, p.status, 6, LO_SLEEP_PRODUCER)) { ok = false; break; }
               mbar_arrive_expect_tx(&sm.full_a[s], a_bytes);
               tma_load_2d(sm.a[s], &a_maps.m[mi], kb * TILE_K, ch.row0, &sm.full_a[s], pol_a);
               if constexpr (A_ROWS > 128) {
@@ -550,7 +575,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           for (uint32_t u = it - it_base; u < steps; u += NISS, it += NISS) {
             // per-channel mode: the accumulator buffer is waited for at the item's first step only
             const bool poll = lane < 2 || (lane == 2 && (MODE != GEMM_CHANNEL || u == 0));
-            const bool mine = poll ? mbar_wait_addr(sm, my_base + 8u * my_slot, my_par, p.status, 3 + lane, 20u) : true;
+            const bool mine = poll ? mbar_wait_addr(sm, my_base + 8u * my_slot, my_par, p.status, 3 + lane, LO_SLEEP_MMA) : true;
             if (!__all_sync(0xffffffffu, mine)) { ok = false; break; }
             const uint32_t sw = __shfl_sync(0xffffffffu, my_slot, 0);
             const uint32_t sa = __shfl_sync(0xffffffffu, my_slot, 1);
@@ -621,7 +646,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
             }
             // the slot of this step is free once the weight stage is (see SC_SLOTS)
             if (it >= (uint32_t)NW &&
-                !__all_sync(0xffffffffu, mbar_wait(sm, &sm.done[(it - NW) % ND], ((it - NW) / ND) & 1u, p.status, 4, 128u))) { ok = false; break; }
+                !__all_sync(0xffffffffu, mbar_wait(sm, &sm.done[(it - NW) % ND], ((it - NW) / ND) & 1u, p.status, 4, LO_SLEEP_SCALE))) { ok = false; break; }
 #pragma unroll
             for (int u = 0; u < NU; ++u) {
               const int t = g + u * 32;
@@ -761,14 +786,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         // a piece beyond the chunk's width is skipped), so tensor memory holds nothing but partial buffers and a
         // K block costs one tensor-memory load per piece.
         constexpr int NP = (A_ROWS / 16 + NCG - 1) / NCG;
-        float acc[NP][16];
+        uint64_t acc2[NP][8];
         // Addresses of this item, formed once: the loops below only add constants to them.  Ring positions
         // (scale slot, partial buffer and its phase) are carried as counters instead of being divided out of
         // the step numbers.
         const uint32_t part0 = tmem_base + lane_off + (uint32_t)col_begin;
         const uint32_t sc0 = smem_u32(&sm.sc[0][0]) + (uint32_t)col_begin * 4u;
         const uint32_t done0 = smem_u32(&sm.done[0]), empty0 = smem_u32(&sm.tmem_empty[0]);
-        const uint32_t wait_ns = my_p > 0 ? 32u : 256u;   // a warp without columns only has to keep step
+        // a warp with fewer pieces than the busiest group of the item has that much slack per step and polls at a
+        // longer interval; a warp without columns only has to keep step
+        const int max_p = (n_pieces + NCG - 1) / NCG;
+        const uint32_t wait_ns = my_p == 0 ? 256u : (my_p < max_p ? LO_SLEEP_PROMO_SLACK : LO_SLEEP_PROMO);
         // this thread's column of the staging tile: row = token, 2 bytes per output channel.  Plain loads and
         // stores (no volatile asm), so that the compiler can overlap the sixteen tokens of a piece; the barrier
         // operations between the phases are compiler barriers as well.
@@ -778,7 +806,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
 #pragma unroll
           for (int pc = 0; pc < NP; ++pc)
 #pragma unroll
-            for (int j = 0; j < 16; ++j) acc[pc][j] = 0.f;
+            for (int j = 0; j < 8; ++j) acc2[pc][j] = 0ull;
 #pragma unroll 1
           for (int kb = 0; kb < KB; ++kb) {
             const uint32_t sc_step = sc0 + sc_slot * (uint32_t)(A_ROWS * 4);
@@ -802,7 +830,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
                 uint32_t r16[16];
                 tmem_ld16(part + pc * 16, r16);
                 tmem_ld_wait();
-                promote<16>(r16, &acc[pc][0], sc_step + (uint32_t)(pc * 64));
+                promote<16>(r16, &acc2[pc][0], sc_step + (uint32_t)(pc * 64));
               }
             }
             ready = __all_sync(0xffffffffu, next_done);
@@ -824,9 +852,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
 #pragma unroll
             for (int pc = 0; pc < NP; ++pc) {
               if (pc < my_p) {
+                float gsum[16];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) unpack2(acc2[pc][j], gsum[2 * j], gsum[2 * j + 1]);
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                  float gte = acc[pc][j];
+                  float gte = gsum[j];
                   if (p.weight_mode == LO_WEIGHT_FP32)
                     gte *= __shfl_sync(0xffffffffu, NPF > 1 && (pc >> 1) ? wgt_r[NPF - 1] : wgt_r[0], (pc & 1) * 16 + j);
                   stg_mine[(pc * 16 + j) * TILE_N] = __float2bfloat16_rn(gte);
@@ -848,7 +879,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           uint32_t(*amax_tab)[A_ROWS] = sm.amax[item_par];
 #pragma unroll 1
           for (int pc = 0; pc < my_p; ++pc) {
-            float *av = &acc[0][0];
+            float av[16];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) unpack2(acc2[0][j], av[2 * j], av[2 * j + 1]);
             const __nv_bfloat16 *gs = stg_mine + pc * 16 * TILE_N;
             // Pass A: act = bf16(bf16(silu(bf16(gate))) * bf16(up)) in place of the up sums; maximum of |act|
             // over this warp's 32 output columns, lane j keeps the one of token j.
@@ -913,7 +946,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
 #pragma unroll
             for (int pp = 0; pp + 1 < NP; ++pp)
 #pragma unroll
-              for (int j = 0; j < 16; ++j) acc[pp][j] = acc[pp + 1][j];
+              for (int j = 0; j < 8; ++j) acc2[pp][j] = acc2[pp + 1][j];
           }
           if (!ok) break;
           item_par ^= 1u;
@@ -927,7 +960,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           const bool vec_ok = (p.n_store & 7) == 0;
 #pragma unroll 1
           for (int pc = 0; pc < my_p; ++pc) {
-            const float *av = &acc[0][0];
+            float av[16];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) unpack2(acc2[0][j], av[2 * j], av[2 * j + 1]);
             __nv_bfloat16 *os = stg_mine + pc * 16 * TILE_N;
             const unsigned long long rowp_u = NPF > 1 && (pc >> 1) ? rowp_r[NPF - 1] : rowp_r[0];
             const float wgt_u = NPF > 1 && (pc >> 1) ? wgt_r[NPF - 1] : wgt_r[0];
@@ -967,7 +1002,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
 #pragma unroll
             for (int pp = 0; pp + 1 < NP; ++pp)
 #pragma unroll
-              for (int j = 0; j < 16; ++j) acc[pp][j] = acc[pp + 1][j];
+              for (int j = 0; j < 8; ++j) acc2[pp][j] = acc2[pp + 1][j];
           }
           if (!ok) break;
         }

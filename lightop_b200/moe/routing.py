@@ -117,10 +117,15 @@ def moe_sum(input: torch.Tensor, output: torch.Tensor, bias: Optional[torch.Tens
             factor: float = 1.0, expect_m: int = -1) -> None:
     """``output[t] = factor * sum_j input[t, j] (+ bias[t])`` (reference: python/lightop/moe_align_sum.py:12-29).
 
-    fp32 accumulation and one rounding, as the reference kernel
+    fp32 accumulation and one rounding, as the reference's bf16 kernel
     (csrc/kernels/moe_align_sum_kernels.cu:604-760).  ``expert_mask`` (bool ``[M, topk]``)
     skips slots; ``num_local_tokens`` (int32 ``[1]``) limits the tokens written; ``expect_m``
     is a launch hint of the reference and is ignored.
+
+    Deviation: fp16 and fp32 inputs follow the same rule (``sum * factor + bias``).  The reference's kernels for
+    those dtypes invert the factor and scale the bias instead (``x * (1/factor)``, ``x + bias * (1/factor)``,
+    moe_align_sum_kernels.cu:558-571, 680-686), which its bf16 kernel and its Python wrapper's description do not;
+    parity with the reference is therefore pinned for bf16 only.
     """
     _lib.require_cuda(input, output, bias, expert_mask, num_local_tokens)
     if input.dim() != 3:
