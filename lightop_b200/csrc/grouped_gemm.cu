@@ -361,10 +361,6 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
 // step neither assembles nor takes apart register pairs.
 template <int N>
 __device__ __forceinline__ void promote(const uint32_t *raw, uint64_t *acc2, uint32_t sc_addr) {
-#ifdef LO_EXP_NO_ARITH
-  acc2[0] ^= (uint64_t)raw[0];      // timing experiment: no conversions, no multiply-adds, no scale loads
-  return;
-#endif
 #pragma unroll
   for (int j4 = 0; j4 < N / 4; ++j4) {
     uint64_t sc01, sc23;               // scale products of four tokens
