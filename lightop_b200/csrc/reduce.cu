@@ -532,8 +532,12 @@ extern "C" int lo_ep_dispatch_plan(const void *topk_ids, int ids_dtype, const in
                                    int world, int32_t *dest_rank, int32_t *inv_perm, int32_t *counts, void *stream) {
   using namespace lo;
   LO_REQUIRE(world >= 1 && world <= 1024, "ep_dispatch_plan: bad sharding");
-  LO_REQUIRE(k >= 1 && T >= 0, "ep_dispatch_plan: bad shape");
-  LO_REQUIRE(topk_ids && rank_of_expert && dest_rank && inv_perm && counts, "ep_dispatch_plan: null pointer");
+  LO_REQUIRE(k >= 1 && T >= 0 && counts != nullptr, "ep_dispatch_plan: bad shape");
+  if (T == 0) {      // a rank without tokens sends nothing
+    LO_CUDA_OK(cudaMemsetAsync(counts, 0, sizeof(int32_t) * (size_t)world, static_cast<cudaStream_t>(stream)));
+    return LO_OK;
+  }
+  LO_REQUIRE(topk_ids && rank_of_expert && dest_rank && inv_perm, "ep_dispatch_plan: null pointer");
   LO_REQUIRE(T * k <= 0x7fffffffLL, "ep_dispatch_plan: too many (token, slot) pairs");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int64_t rows = T * k;
@@ -551,6 +555,7 @@ extern "C" int lo_ep_dispatch_put(const int8_t *aq, const float *aq_scale, const
   using namespace lo;
   LO_REQUIRE(world >= 1 && world <= 1024 && experts_per_rank >= 1, "ep_dispatch_put: bad sharding");
   LO_REQUIRE(k >= 1 && T >= 0 && H % 128 == 0, "ep_dispatch_put: bad shape");
+  if (T == 0) return LO_OK;
   LO_REQUIRE(aq && aq_scale && topk_ids && topk_weights && rank_of_expert && inv_perm && seg_first && seg_dst,
              "ep_dispatch_put: null pointer");
   LO_REQUIRE(T * k <= 0x7fffffffLL, "ep_dispatch_put: too many (token, slot) pairs");

@@ -116,6 +116,35 @@ class _CudaExperts:
         return out
 
 
+def peer_routes(mat, me: int, record_bytes: int, row_bytes: int, peer_recv, peer_ret):
+    """Where rank ``me`` writes, from the R x R matrix of record counts (``mat[s][d]`` = records rank s sends to rank d).
+
+    Returns ``(first_out, seg_dst, first_in, seg_ret)``:
+    ``first_out[d]``  packed position of this rank's first record for rank d (its records are grouped by destination);
+    ``seg_dst[d]``    address of that record in rank d's receive zone: the runs of the lower ranks come first;
+    ``first_in[s]``   index of the first record received from rank s (R + 1 entries, the last one the total);
+    ``seg_ret[s]``    address, in rank s's return zone, of the result row of that record: rank s keeps its rows in the
+                      order it packed them, so the rows for the ranks below ``me`` come first.
+    An address of 0 stands for an empty run.  ``peer_recv`` / ``peer_ret`` are the zones' base addresses as this rank
+    sees them."""
+    R = len(mat)
+    first_out, seg_dst, first_in, seg_ret = [], [], [], []
+    run = 0
+    for d in range(R):
+        first_out.append(run)
+        run += mat[me][d]
+        before = sum(mat[s][d] for s in range(me))
+        seg_dst.append(peer_recv[d] + before * record_bytes if mat[me][d] else 0)
+    run = 0
+    for s in range(R):
+        first_in.append(run)
+        run += mat[s][me]
+        before = sum(mat[s][d] for d in range(me))
+        seg_ret.append(peer_ret[s] + before * row_bytes if mat[s][me] else 0)
+    first_in.append(run)
+    return first_out, seg_dst, first_in, seg_ret
+
+
 # --------------------------------------------------------------------------- peer landing zones
 
 class _PeerZones:
@@ -308,7 +337,11 @@ class ExpertParallelMoE:
         stride = int(lib.lo_ep_dispatch_row_bytes(H))
         self._events = []
         self._mark()
-        xq, xs = self.quant_fn(x)
+        if T:
+            xq, xs = self.quant_fn(x)
+        else:               # a rank without tokens still takes part in the step
+            xq = torch.empty(0, H, dtype=torch.int8, device=dev)
+            xs = torch.empty(0, H // 128, dtype=torch.float32, device=dev)
         self._mark()
         ids = topk_ids.contiguous()
         w = topk_weights.to(torch.float32).contiguous()
@@ -335,22 +368,7 @@ class ExpertParallelMoE:
         need_ret = max(sum(mat[s]) for s in range(R))
         self._zones.ensure(max(need_recv, 1) * stride, max(need_ret, 1) * 2 * H)
         z = self._zones
-        # my run for rank d starts behind the runs of the lower ranks; my result rows for rank s go behind those that
-        # the lower ranks return to s (the order in which s packed its records)
-        first_out, first_in, seg_dst, seg_ret = [], [], [], []
-        run = 0
-        for d in range(R):
-            first_out.append(run)
-            run += send_counts[d]
-            before = sum(mat[s][d] for s in range(me))
-            seg_dst.append(z.peer_recv[d] + before * stride if send_counts[d] else 0)
-        run = 0
-        for s_ in range(R):
-            first_in.append(run)
-            run += recv_counts[s_]
-            before = sum(mat[s_][d] for d in range(me))
-            seg_ret.append(z.peer_ret[s_] + before * 2 * H if recv_counts[s_] else 0)
-        first_in.append(run)
+        first_out, seg_dst, first_in, seg_ret = peer_routes(mat, me, stride, 2 * H, z.peer_recv, z.peer_ret)
         i32 = torch.tensor(first_out + first_in, dtype=torch.int32, device=dev)
         i64 = torch.tensor(seg_dst + seg_ret, dtype=torch.int64, device=dev)
         self._mark()

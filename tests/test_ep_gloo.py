@@ -130,3 +130,37 @@ def test_ep_two_ranks_match_single_process_oracle():
 def test_ep_rejects_inconsistent_sharding_on_the_host():
     res = _run("mismatch")
     assert [r[1] for r in res] == ["ValueError", "ValueError"]
+
+
+def test_peer_routes_tile_the_zones_exactly():
+    """Host bookkeeping of the peer transport: over all ranks, the runs written into a receive zone tile it without gap
+    or overlap in source-rank order, and the return routes send every result row back to the packed position it came
+    from."""
+    from lightop_b200.ep import peer_routes
+    import random
+    rnd = random.Random(3)
+    for R in (1, 2, 3, 8):
+        mat = [[rnd.choice([0, 0, 1, 5, 17, 200]) for _ in range(R)] for _ in range(R)]
+        rec, row = 7408, 14336
+        recv_base = [1_000_000_000 * (r + 1) for r in range(R)]
+        ret_base = [50_000_000_000 + 1_000_000_000 * r for r in range(R)]
+        routes = [peer_routes(mat, me, rec, row, recv_base, ret_base) for me in range(R)]
+        for d in range(R):
+            # receive zone of rank d: runs of rank 0, 1, ... back to back
+            at = recv_base[d]
+            for s in range(R):
+                first_out, seg_dst, first_in, seg_ret = routes[s]
+                if mat[s][d]:
+                    assert seg_dst[d] == at
+                    at += mat[s][d] * rec
+                else:
+                    assert seg_dst[d] == 0
+            # ... which is exactly how rank d indexes what it received
+            assert routes[d][2] == [sum(mat[s][d] for s in range(i)) for i in range(R + 1)]
+        for s in range(R):
+            # the rows rank d returns to rank s land where s packed its records for d
+            first_out = routes[s][0]
+            assert first_out == [sum(mat[s][:d]) for d in range(R)]
+            for d in range(R):
+                seg_ret = routes[d][3]
+                assert seg_ret[s] == (ret_base[s] + first_out[d] * row if mat[s][d] else 0)
