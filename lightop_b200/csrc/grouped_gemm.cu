@@ -258,11 +258,6 @@ __device__ __forceinline__ bool mbar_test_addr(uint32_t bar, uint32_t parity) {
 __device__ __forceinline__ void mbar_arrive_addr(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// Two 64-bit words from shared memory (16-byte aligned address in the shared window).
-__device__ __forceinline__ void lds_2x64(uint32_t addr, uint64_t &a, uint64_t &b) {
-  asm volatile("ld.shared.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "r"(addr));
-}
-
 __device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -339,36 +334,22 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-// Packed fp32 pair arithmetic (two IEEE round-to-nearest operations per instruction).
-__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
-  return r;
-}
-__device__ __forceinline__ void unpack2(uint64_t v, float &lo, float &hi) {
-  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
-}
-__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
-  uint64_t r;
-  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
-  return r;
-}
 
 // One promotion step on N (8 or 16) tokens of this thread's output channel: acc = fma(float(raw), scale product, acc).
 // The 128-long int8 dot is below 2^21 in magnitude, so the conversion is exact; one rounding per K block.
 // `sc_addr` is the shared-memory address of the N scale products.
-// The sums stay packed two to a 64-bit register over the whole K loop (tokens 2i and 2i + 1 in acc2[i]), so that a
-// step neither assembles nor takes apart register pairs.
+// Plain fp32 multiply-adds: the packed f32x2 form needs its operands in aligned register pairs, and assembling the
+// pairs from the converted values cost more than the packed instruction saved (measured: -6 % on the gate_up launch).
 template <int N>
-__device__ __forceinline__ void promote(const uint32_t *raw, uint64_t *acc2, uint32_t sc_addr) {
+__device__ __forceinline__ void promote(const uint32_t *raw, float *acc, uint32_t sc_addr) {
 #pragma unroll
   for (int j4 = 0; j4 < N / 4; ++j4) {
-    uint64_t sc01, sc23;               // scale products of four tokens
-    lds_2x64(sc_addr + 16u * j4, sc01, sc23);
-    const uint64_t f01 = pack2(__int2float_rn((int32_t)raw[j4 * 4 + 0]), __int2float_rn((int32_t)raw[j4 * 4 + 1]));
-    const uint64_t f23 = pack2(__int2float_rn((int32_t)raw[j4 * 4 + 2]), __int2float_rn((int32_t)raw[j4 * 4 + 3]));
-    acc2[j4 * 2 + 0] = fma2(f01, sc01, acc2[j4 * 2 + 0]);
-    acc2[j4 * 2 + 1] = fma2(f23, sc23, acc2[j4 * 2 + 1]);
+    float s0, s1, s2, s3;               // scale products of four tokens
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(s0), "=f"(s1), "=f"(s2), "=f"(s3) : "r"(sc_addr + 16u * j4));
+    acc[j4 * 4 + 0] = __fmaf_rn(__int2float_rn((int32_t)raw[j4 * 4 + 0]), s0, acc[j4 * 4 + 0]);
+    acc[j4 * 4 + 1] = __fmaf_rn(__int2float_rn((int32_t)raw[j4 * 4 + 1]), s1, acc[j4 * 4 + 1]);
+    acc[j4 * 4 + 2] = __fmaf_rn(__int2float_rn((int32_t)raw[j4 * 4 + 2]), s2, acc[j4 * 4 + 2]);
+    acc[j4 * 4 + 3] = __fmaf_rn(__int2float_rn((int32_t)raw[j4 * 4 + 3]), s3, acc[j4 * 4 + 3]);
   }
 }
 
@@ -782,7 +763,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
         // a piece beyond the chunk's width is skipped), so tensor memory holds nothing but partial buffers and a
         // K block costs one tensor-memory load per piece.
         constexpr int NP = (A_ROWS / 16 + NCG - 1) / NCG;
-        uint64_t acc2[NP][8];
+        float acc[NP][16];
         // Addresses of this item, formed once: the loops below only add constants to them.  Ring positions
         // (scale slot, partial buffer and its phase) are carried as counters instead of being divided out of
         // the step numbers.
@@ -802,7 +783,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
 #pragma unroll
           for (int pc = 0; pc < NP; ++pc)
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc2[pc][j] = 0ull;
+            for (int j = 0; j < 16; ++j) acc[pc][j] = 0.f;
 #pragma unroll 1
           for (int kb = 0; kb < KB; ++kb) {
             const uint32_t sc_step = sc0 + sc_slot * (uint32_t)(A_ROWS * 4);
@@ -826,7 +807,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
                 uint32_t r16[16];
                 tmem_ld16(part + pc * 16, r16);
                 tmem_ld_wait();
-                promote<16>(r16, &acc2[pc][0], sc_step + (uint32_t)(pc * 64));
+                promote<16>(r16, &acc[pc][0], sc_step + (uint32_t)(pc * 64));
               }
             }
             ready = __all_sync(0xffffffffu, next_done);
@@ -848,12 +829,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
 #pragma unroll
             for (int pc = 0; pc < NP; ++pc) {
               if (pc < my_p) {
-                float gsum[16];
-#pragma unroll
-                for (int j = 0; j < 8; ++j) unpack2(acc2[pc][j], gsum[2 * j], gsum[2 * j + 1]);
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
-                  float gte = gsum[j];
+                  float gte = acc[pc][j];
                   if (p.weight_mode == LO_WEIGHT_FP32)
                     gte *= __shfl_sync(0xffffffffu, NPF > 1 && (pc >> 1) ? wgt_r[NPF - 1] : wgt_r[0], (pc & 1) * 16 + j);
                   stg_mine[(pc * 16 + j) * TILE_N] = __float2bfloat16_rn(gte);
@@ -875,9 +853,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           uint32_t(*amax_tab)[A_ROWS] = sm.amax[item_par];
 #pragma unroll 1
           for (int pc = 0; pc < my_p; ++pc) {
-            float av[16];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) unpack2(acc2[0][j], av[2 * j], av[2 * j + 1]);
+            float *av = &acc[0][0];
             const __nv_bfloat16 *gs = stg_mine + pc * 16 * TILE_N;
             // Pass A: act = bf16(bf16(silu(bf16(gate))) * bf16(up)) in place of the up sums; maximum of |act|
             // over this warp's 32 output columns, lane j keeps the one of token j.
@@ -942,7 +918,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
 #pragma unroll
             for (int pp = 0; pp + 1 < NP; ++pp)
 #pragma unroll
-              for (int j = 0; j < 8; ++j) acc2[pp][j] = acc2[pp + 1][j];
+              for (int j = 0; j < 16; ++j) acc[pp][j] = acc[pp + 1][j];
           }
           if (!ok) break;
           item_par ^= 1u;
@@ -956,9 +932,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
           const bool vec_ok = (p.n_store & 7) == 0;
 #pragma unroll 1
           for (int pc = 0; pc < my_p; ++pc) {
-            float av[16];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) unpack2(acc2[0][j], av[2 * j], av[2 * j + 1]);
+            const float *av = &acc[0][0];
             __nv_bfloat16 *os = stg_mine + pc * 16 * TILE_N;
             const unsigned long long rowp_u = NPF > 1 && (pc >> 1) ? rowp_r[NPF - 1] : rowp_r[0];
             const float wgt_u = NPF > 1 && (pc >> 1) ? wgt_r[NPF - 1] : wgt_r[0];
@@ -998,7 +972,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap w_map, const __grid_cons
 #pragma unroll
             for (int pp = 0; pp + 1 < NP; ++pp)
 #pragma unroll
-              for (int j = 0; j < 8; ++j) acc2[pp][j] = acc2[pp + 1][j];
+              for (int j = 0; j < 16; ++j) acc[pp][j] = acc[pp + 1][j];
           }
           if (!ok) break;
         }
