@@ -216,7 +216,10 @@ class E2ERunner:
         in_done = [torch.cuda.Event() for _ in range(steps)]
         comp_done = [torch.cuda.Event() for _ in range(steps)]
         out_done = [torch.cuda.Event() for _ in range(steps)]
-        keep = []
+        # y of step i stays referenced until step i+2 is enqueued, i.e. until the compute stream has been told to wait
+        # for its copy-out: its memory then goes back to the allocator's cache in stream order, and a steady-state step
+        # allocates nothing new from the driver
+        keep = [None, None]
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
         t0.record(stream)
@@ -233,7 +236,7 @@ class E2ERunner:
             if i >= 2:
                 stream.wait_event(out_done[i - 2])               # y of step i-2 has left the device
             y = self.compute(self.x_d[b], self.l_d[b], b)
-            keep.append(y)
+            keep[b] = y
             comp_done[i].record(stream)
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(comp_done[i])

@@ -467,6 +467,9 @@ int lo_ep_dispatch_put(const int8_t *aq, const float *aq_scale, const void *topk
  * its own handle: it uses the pointer.  No counterpart in the reference.
  */
 int lo_peer_alloc(size_t bytes, void **ptr);
+/* n 32-bit words from device memory into page-locked, device-addressable host memory, by a kernel rather than a copy
+ * engine (a small read does not queue behind a large device-to-host copy of another stream).  Stream-ordered. */
+int lo_words_to_host(const int32_t *src, int32_t *dst_host, int64_t n, void *stream);
 int lo_peer_free(void *ptr);
 int lo_peer_handle_bytes(void);
 int lo_peer_export(const void *ptr, uint8_t *handle);

@@ -61,6 +61,7 @@ PROTOTYPES = {
                                                      c_int64, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_size_t,
                                                      c_void_p, c_void_p]),
     "lo_peer_alloc": (c_int, [c_size_t, c_void_p]),
+    "lo_words_to_host": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
     "lo_peer_free": (c_int, [c_void_p]),
     "lo_peer_handle_bytes": (c_int, []),
     "lo_peer_export": (c_int, [c_void_p, c_void_p]),

@@ -32,7 +32,7 @@
 //                 column group; the chunk's tokens are dealt to the groups in pieces of 16.  A
 //                 thread keeps the fp32 running sums of its output column for its pieces in
 //                 registers: per K block it loads 16 int32 partials, converts and does one
-//                 fused multiply-add per value with the scale product (packed f32x2).
+//                 fused multiply-add per value with the scale product.
 // Pipelines: the two shared-memory rings (full_w / full_a, refilled when done[] says the MMAs
 // that read a slot have completed) and NBUF tensor-memory partial buffers (done[] as "full",
 // tmem_empty as "free") between the issuers and the promotion warps.

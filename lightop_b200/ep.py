@@ -147,6 +147,10 @@ def peer_routes(mat, me: int, record_bytes: int, row_bytes: int, peer_recv, peer
 
 # --------------------------------------------------------------------------- peer landing zones
 
+class PeerUnavailable(RuntimeError):
+    """The landing zones of the peer transport could not be set up on some rank (raised on every rank)."""
+
+
 class _PeerZones:
     """This rank's receive and return buffers and the mappings of every other rank's.  All methods that change the
     buffers are collective over the group and take arguments that are equal on every rank."""
@@ -161,13 +165,16 @@ class _PeerZones:
         self.peer_recv = [0] * world
         self.peer_ret = [0] * world
         self._opened: List[int] = []
+        self._held = False          # set while a (possibly partial) set-up is in place, so that release() is collective
 
     def _check(self, st, what):
         from . import _lib
         _lib.check(st, what)
 
     def ensure(self, recv_bytes: int, ret_bytes: int) -> None:
-        """Grow the zones to at least these sizes (the same numbers on every rank)."""
+        """Grow the zones to at least these sizes (the same numbers on every rank).  Collective; raises
+        PeerUnavailable on EVERY rank when any rank could not allocate, export or map a zone (the ranks agree on the
+        outcome before anybody leaves, so no rank is left waiting in a collective)."""
         if recv_bytes <= self.recv_bytes and ret_bytes <= self.ret_bytes:
             return
         import ctypes
@@ -179,14 +186,19 @@ class _PeerZones:
         self.release()
         hb = int(self.lib.lo_peer_handle_bytes())
         mine = torch.zeros(2, hb, dtype=torch.uint8)
+        ok, why = True, ""
+        self._held = True
         with torch.cuda.device(self.dev):
             for i, nbytes in enumerate((recv_bytes, ret_bytes)):
                 p = ctypes.c_void_p()
-                self._check(self.lib.lo_peer_alloc(nbytes, ctypes.byref(p)), "lo_peer_alloc")
-                self.own[i] = int(p.value)
-                buf = (ctypes.c_uint8 * hb)()
-                self._check(self.lib.lo_peer_export(self.own[i], buf), "lo_peer_export")
-                mine[i] = torch.frombuffer(bytearray(buf), dtype=torch.uint8)
+                if ok and self.lib.lo_peer_alloc(nbytes, ctypes.byref(p)) == 0:
+                    self.own[i] = int(p.value)
+                    buf = (ctypes.c_uint8 * hb)()
+                    if self.lib.lo_peer_export(self.own[i], buf) == 0:
+                        mine[i] = torch.frombuffer(bytearray(buf), dtype=torch.uint8)
+                        continue
+                if ok:
+                    ok, why = False, (self.lib.lo_last_error() or b"").decode()
             everyone = torch.empty(self.world, 2, hb, dtype=torch.uint8, device=self.dev)
             dist.all_gather_into_tensor(everyone, mine.to(self.dev), group=self.group)
             everyone = everyone.cpu()
@@ -194,21 +206,29 @@ class _PeerZones:
                 if r == self.rank:
                     self.peer_recv[r], self.peer_ret[r] = self.own
                     continue
-                got = []
+                got = [0, 0]
                 for i in range(2):
                     raw = bytes(everyone[r, i].tolist())
                     p = ctypes.c_void_p()
-                    self._check(self.lib.lo_peer_open(raw, ctypes.byref(p)), "lo_peer_open")
-                    got.append(int(p.value))
-                    self._opened.append(int(p.value))
+                    if ok and any(raw) and self.lib.lo_peer_open(raw, ctypes.byref(p)) == 0:
+                        got[i] = int(p.value)
+                        self._opened.append(int(p.value))
+                    elif ok:
+                        ok, why = False, (self.lib.lo_last_error() or b"").decode() or f"rank {r} exported no zone"
                 self.peer_recv[r], self.peer_ret[r] = got
+            verdict = torch.tensor([1 if ok else 0], dtype=torch.int32, device=self.dev)
+            dist.all_reduce(verdict, op=dist.ReduceOp.MIN, group=self.group)
+        if int(verdict.item()) != 1:
+            self.release()
+            raise PeerUnavailable(why or "another rank could not set up its landing zones")
         self.recv_bytes, self.ret_bytes = recv_bytes, ret_bytes
         dist.barrier(group=self.group)
 
     def release(self) -> None:
         """Unmap the peers' zones, then (after everyone has) free this rank's.  Collective."""
-        if not self.own[0] and not self._opened:
+        if not any(self.own) and not self._opened and not self._held:
             return
+        self._held = False
         with torch.cuda.device(self.dev):
             for p in self._opened:
                 self.lib.lo_peer_close(p)
@@ -257,6 +277,7 @@ class ExpertParallelMoE:
         if transport == "peer" and not (builtin and dev.type == "cuda"):
             raise ValueError("the peer transport runs the built-in CUDA kernels only")
         self.transport = transport
+        self.transport_note = ""           # why the peer transport was given up, if it was
         self.quant_fn = quant_fn or _cuda_quant
         self.pack_fn = pack_fn or _cuda_pack
         self.expert_fn = expert_fn or _CudaExperts(w1_local, w2_local, w1_scale, w2_scale)
@@ -266,6 +287,7 @@ class ExpertParallelMoE:
         self._events: List[torch.cuda.Event] = []
         self._zones = _PeerZones(group, dev, self.rank, self.world) if transport == "peer" else None
         self._flag = torch.zeros(1, dtype=torch.int32, device=dev) if transport == "peer" else None
+        self._mat_host = None
 
     def close(self) -> None:
         """Give the landing zones back (collective; only the peer transport holds any)."""
@@ -357,7 +379,17 @@ class ExpertParallelMoE:
         # run of records begins in every zone
         mat_t = torch.empty(R, R, dtype=torch.int32, device=dev)
         dist.all_gather_into_tensor(mat_t, counts, group=self.group)
-        mat = mat_t.tolist()                                   # mat[s][d]: records rank s sends to rank d
+        # read through page-locked memory that a kernel writes, not through a copy engine: the engine may be busy
+        # with a caller's large device-to-host transfer, behind which a small copy would wait
+        if self._mat_host is None:
+            self._mat_host = torch.empty(R * R, dtype=torch.int32).pin_memory()
+        with torch.cuda.device(dev):
+            _lib.check(lib.lo_words_to_host(_lib.ptr(mat_t), self._mat_host.data_ptr(), R * R, _lib.current_stream(dev)),
+                       "lo_words_to_host")
+        seen = torch.cuda.Event()
+        seen.record()
+        seen.synchronize()
+        mat = self._mat_host.view(R, R).tolist()               # mat[s][d]: records rank s sends to rank d
         send_counts = [int(v) for v in mat[me]]
         recv_counts = [int(mat[s][me]) for s in range(R)]
         if sum(send_counts) != T * k:
@@ -366,7 +398,15 @@ class ExpertParallelMoE:
         rows_recv = sum(recv_counts)
         need_recv = max(sum(mat[s][d] for s in range(R)) for d in range(R))
         need_ret = max(sum(mat[s]) for s in range(R))
-        self._zones.ensure(max(need_recv, 1) * stride, max(need_ret, 1) * 2 * H)
+        try:
+            self._zones.ensure(max(need_recv, 1) * stride, max(need_ret, 1) * 2 * H)
+        except PeerUnavailable as e:
+            # every rank got the same exception: all of them switch to the all-to-all transport, for good
+            if self.rank == 0:
+                import sys
+                print(f"lightop_b200.ep: peer transport unavailable ({e}); using all-to-all collectives", file=sys.stderr)
+            self.transport, self._zones, self.transport_note = "collective", None, str(e)
+            return self.forward(x, topk_weights, topk_ids)
         z = self._zones
         first_out, seg_dst, first_in, seg_ret = peer_routes(mat, me, stride, 2 * H, z.peer_recv, z.peer_ret)
         i32 = torch.tensor(first_out + first_in, dtype=torch.int32, device=dev)

@@ -326,6 +326,46 @@ def test_expert_rows_entry_point_and_ep_driver_world1(lo, transport):
     assert_out_close(y, O.fused_moe_block_int8(x, w1, w2, w1_s, w2_s, w, ids), "ep world 1")
 
 
+def test_ep_driver_falls_back_when_no_landing_zone_can_be_had(lo):
+    """A rank that cannot allocate its landing zones makes every rank switch to the all-to-all transport; the failure
+    is made on the host (a stand-in for the allocation call that reports an error)."""
+    import socket
+    import torch.distributed as dist
+    from lightop_b200.ep import ExpertParallelMoE
+    E, k, M, H, I = 8, 2, 40, 256, 256
+    w1, w2, w1_s, w2_s = synthetic.make_weights(E, H, I, seed=24)
+    x, logits = synthetic.make_activations(M, H, E, seed=25)
+    w, ids = _route(logits, k)
+    base = _run_fused(lo, x, w1, w2, w1_s, w2_s, w, ids)
+
+    class NoAlloc:
+        def __init__(self, lib):
+            self._lib = lib
+
+        def __getattr__(self, name):
+            return getattr(self._lib, name)
+
+        def lo_peer_alloc(self, nbytes, out):
+            return 3
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    dist.init_process_group("nccl", init_method=f"tcp://127.0.0.1:{port}", rank=0, world_size=1)
+    try:
+        layer = ExpertParallelMoE(w1.to(DEV), w2.to(DEV), w1_s.to(DEV), w2_s.to(DEV), E, transport="peer")
+        layer._zones.lib = NoAlloc(layer._zones.lib)
+        y = layer.forward(x.to(DEV), w.to(DEV), ids.to(DEV))
+        torch.cuda.synchronize()
+        assert layer.transport == "collective" and layer.transport_note
+        y2 = layer.forward(x.to(DEV), w.to(DEV), ids.to(DEV))
+        torch.cuda.synchronize()
+        layer.close()
+    finally:
+        dist.destroy_process_group()
+    assert torch.equal(y, base) and torch.equal(y2, base)
+
+
 # ------------------------------ dense block-INT8 linear -------------------------------
 
 @pytest.mark.parametrize("m,n,k", [(1, 576, 7168), (7, 2048, 512), (48, 256, 1024), (128, 7168, 128), (300, 1536, 1536), (1024, 2304, 1152 + 128)])
