@@ -65,6 +65,9 @@ namespace {
 // promotion warps that share its scheduler, so everybody who can afford the reaction time polls slowly: the
 // producers (their rings cover several K blocks), the scale warp (a step ahead), and promotion warps with fewer
 // pieces than their neighbours.
+#ifndef LO_NCG_WIDE
+#define LO_NCG_WIDE 5      // column groups of the instantiations for chunks above 64 rows
+#endif
 #ifndef LO_SLEEP_PRODUCER
 #define LO_SLEEP_PRODUCER 128u
 #endif
@@ -103,7 +106,7 @@ template <int MODE, int A_ROWS> struct Cfg {
   // warp per lane quarter of tensor memory).  Five groups keep a group at two pieces for chunks of up to 160
   // tokens (the group with the most pieces paces the K loop); the CTA then has 24 warps and 80 registers per
   // thread.  Narrow chunks use four groups: more warps would only add idle ones that have to keep step.
-  static constexpr int NCG = A_ROWS > 64 ? 5 : 4;
+  static constexpr int NCG = A_ROWS > 64 ? LO_NCG_WIDE : 4;
   static constexpr int EPI_WARPS = 4 * NCG;
   static constexpr int NUM_THREADS = (FIRST_EPI_WARP + EPI_WARPS) * 32;
   static constexpr int A_TILE_BYTES = A_ROWS * TILE_K;
