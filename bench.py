@@ -41,7 +41,7 @@ if ROOT not in sys.path:
 
 METRIC = "fused_moe_w8a8_block_int8_tokens_per_s"
 UNIT = "tokens/s"
-DECODE_SWEEP = (1, 8, 16, 32, 64, 128, 256)
+DECODE_SWEEP = (1, 2, 4, 8, 16, 32, 64, 128, 256)
 
 
 def load_synthetic():
