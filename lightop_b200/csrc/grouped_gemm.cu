@@ -61,13 +61,13 @@
 namespace lo {
 namespace {
 
-// Interval between two polls of a barrier, in nanoseconds, by role.  A polling warp competes for issue slots with the
-// promotion warps that share its scheduler, so everybody who can afford the reaction time polls slowly: the
-// producers (their rings cover several K blocks), the scale warp (a step ahead), and promotion warps with fewer
-// pieces than their neighbours.
+// Build parameters (the defaults are the measured best; the others exist so that a variant can be built and compared).
+// Column groups of the instantiations for chunks above 64 rows: five keep a group at two pieces of 16 tokens.
 #ifndef LO_NCG_WIDE
-#define LO_NCG_WIDE 5      // column groups of the instantiations for chunks above 64 rows
+#define LO_NCG_WIDE 5
 #endif
+// Interval between two polls of a barrier, in nanoseconds, by role.  A polling warp competes for issue slots with the
+// promotion warps that share its scheduler; longer intervals for the waiters with slack measured no different.
 #ifndef LO_SLEEP_PRODUCER
 #define LO_SLEEP_PRODUCER 128u
 #endif
