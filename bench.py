@@ -490,14 +490,17 @@ def run_ours(args, rank: int, world: int, local_rank: int):
 
         def entry(wname, Mx, xs, ls, weights, Ex, Hx, Ix):
             st, ti_s, _ = make_step(xs, ls, *weights, dict(use_int8_w8a8=True, block_shape=[128, 128]))
+            own = ClockSampler(local_rank, period_s=0.001)       # clocks seen during this entry's replays
+            own.start()
             med, best = graph_median_ms(st, replays=max(50, args.graph_replays))
+            own_clocks = own.stop()
             hit = int(torch.unique(ti_s).numel())
             sm = stage_times(lightop_b200, _lib, st, 5)
             lb = synthetic.alg_bytes(Mx, Ex, Hx, Ix, hit)
             g1 = gate_up_alg_bytes(Mx, k, Hx, Ix, hit) / (sm["gemm_gate_up"] * 1e-3) / 1e9
             return {"workload": wname, "M": Mx, "ms_per_step": med, "ms_best": best, "tokens_per_s": Mx / (med * 1e-3),
                     "experts_hit": hit, "layer_alg_gbs": lb / (med * 1e-3) / 1e9, "layer_frac": lb / (med * 1e-3) / 1e9 / hbm_peak,
-                    "gate_up_frac": g1 / hbm_peak, "stage_ms": sm,
+                    "gate_up_frac": g1 / hbm_peak, "stage_ms": sm, "clocks": own_clocks,
                     "timing": f"median of {max(50, args.graph_replays)} CUDA-graph replays"}
 
         for Mx in DECODE_SWEEP:
