@@ -54,22 +54,22 @@ FusedLayout carve_fused(void *ws, int64_t M, int num_experts_for_align, int topk
   return L;
 }
 
-// Chunk sizes of the block-scaled layer.  An M=128, K=32 MMA costs the same ~96 cycles for any N <= 128 (128 cycles
-// up to N = 256), so chunks smaller than 128 only multiply the MMA count.  Once experts get 64 rows or more on average
-// the table is cut into chunks of up to 160 rows, the widest whose partial buffers still number three: at 128 rows per
-// expert about half of the experts have a few rows more than 128, and a second chunk means a second pass over the
-// expert's weights.
+// Chunk sizes of the block-scaled layer, by the rows an expert gets on average (rows / experts), measured at the
+// DeepSeek-V3 shape.  The GEMM is instantiated per chunk cap and the caps differ in what fits beside the operands:
+// chunks of <= 64 rows leave room for 12 weight slots and 8 partial buffers, <= 128 rows for 7 and 4, <= 160 rows for 5
+// and 3.
+//   <= 48 rows per expert : 64-row chunks.  A weight-streaming call wants the deep rings, and the few experts that do
+//                           get more rows simply have a second chunk (-8 % from 96 to 512 tokens, -4 % at 1536).
+//   49 .. 119             : 128-row chunks (-9 % at 64 rows per expert, -2 % at 112 against the 160-row table).
+//   >= 120                : 160-row chunks, the widest whose partial buffers still number three: at 128 rows per expert
+//                           half of the experts have a few rows more than 128, and a second chunk means a second pass
+//                           over the expert's weights (-17 % at 128 rows per expert against the 128-row table).
 constexpr int CHUNK_ROWS = 128;
 constexpr int CHUNK_ROWS_WIDE = 160;
-// With 48 rows per expert or fewer on average the table is cut at 64 rows instead: the GEMM instantiation for
-// chunks of up to 64 rows keeps 12 weight slots and 8 partial buffers (7 and 4 at 128) and 20 warps, which is what
-// a weight-streaming call wants, and the few experts that do get more rows than that simply have a second chunk
-// (measured at the DeepSeek-V3 shape: -8 % from 96 to 512 tokens, -5 % at 1024, -4 % at 1536; at 56 rows per expert
-// the 128-row table is ahead again).
 constexpr int CHUNK_ROWS_SMALL = 64;
 inline int chunk_rows_for(int64_t rows, int experts) {
   const int64_t avg = rows / experts;
-  return avg >= 64 ? CHUNK_ROWS_WIDE : (avg <= 48 ? CHUNK_ROWS_SMALL : CHUNK_ROWS);
+  return avg >= 120 ? CHUNK_ROWS_WIDE : (avg <= 48 ? CHUNK_ROWS_SMALL : CHUNK_ROWS);
 }
 
 // Optional per-stage timing of the fused call (cudaEvents recorded between its five kernels).

@@ -187,10 +187,10 @@ def test_fused_many_chunks(lo):
     assert_out_close(y, y_ref, "many chunks")
 
 
-@pytest.mark.parametrize("M", [192, 196, 252, 256, 700])
+@pytest.mark.parametrize("M", [192, 196, 256, 476, 480, 700])
 def test_fused_chunk_size_rule(lo, M):
-    # rows per expert on average 48 / 49 / 63 / 64 / 175: the chunk table is cut at 64, 128, 128, 160 and 160 rows, with
-    # experts on both sides of every cut (the routing is not uniform), so every instantiation meets split experts
+    # rows per expert on average 48 / 49 / 64 / 119 / 120 / 175: the chunk table is cut at 64, 128, 128, 128, 160 and 160
+    # rows, with experts on both sides of every cut (the routing is not uniform), so every instantiation meets split experts
     E, k, H, I = 8, 2, 256, 256
     w1, w2, w1_s, w2_s = synthetic.make_weights(E, H, I, seed=15)
     x, logits = synthetic.make_activations(M, H, E, seed=16)
