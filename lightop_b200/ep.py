@@ -167,10 +167,6 @@ class _PeerZones:
         self._opened: List[int] = []
         self._held = False          # set while a (possibly partial) set-up is in place, so that release() is collective
 
-    def _check(self, st, what):
-        from . import _lib
-        _lib.check(st, what)
-
     def ensure(self, recv_bytes: int, ret_bytes: int) -> None:
         """Grow the zones to at least these sizes (the same numbers on every rank).  Collective; raises
         PeerUnavailable on EVERY rank when any rank could not allocate, export or map a zone (the ranks agree on the
