@@ -95,3 +95,27 @@ def test_peer_transport_with_emulated_ranks(lo, R, E, k, H, I, tokens):
         torch.cuda.synchronize()
         assert torch.equal(y, local), f"rank {r}: max diff {(y.float() - local.float()).abs().max().item()}"
     lo.check_device_status()
+
+
+def test_peer_buffer_entry_points_and_words_to_host(lo):
+    """lo_peer_alloc / lo_peer_export / lo_peer_free on one device (a process does not open its own handle), and the
+    kernel-written read of a few words into page-locked memory."""
+    import ctypes
+    from lightop_b200 import _lib
+    lib = _lib.load()
+    with torch.cuda.device(DEV):
+        p = ctypes.c_void_p()
+        _lib.check(lib.lo_peer_alloc(1 << 20, ctypes.byref(p)), "alloc")
+        assert p.value
+        hb = int(lib.lo_peer_handle_bytes())
+        assert hb == 64
+        buf = (ctypes.c_uint8 * hb)()
+        _lib.check(lib.lo_peer_export(p.value, buf), "export")
+        assert any(buf)
+        assert lib.lo_peer_alloc(0, ctypes.byref(ctypes.c_void_p())) != 0          # bad size is an error, not a crash
+        _lib.check(lib.lo_peer_free(p.value), "free")
+        src = torch.arange(37, dtype=torch.int32, device=DEV) * 3 - 5
+        dst = torch.zeros(37, dtype=torch.int32).pin_memory()
+        _lib.check(lib.lo_words_to_host(_lib.ptr(src), dst.data_ptr(), 37, _lib.current_stream(torch.device(DEV))), "words")
+        torch.cuda.synchronize()
+    assert torch.equal(dst, src.cpu())
